@@ -1,0 +1,189 @@
+/*
+ * tbk.h -- C ABI of the B200 tree-ensemble inference kernels.
+ *
+ * This is the inner boundary of the library: the place where, in the reference,
+ * the inference runner calls into the generated module (Init_* uploads,
+ * Prediction_Function, Dealloc_Buffers -- resolved by name in
+ * src/mlir/ExecutionHelpers.cpp:37-51 and src/gpu/GPUModelSerializers.cpp:21-262).
+ * Every entry point takes plain pointers and sizes, returns an int status
+ * (0 = success) and never aborts; the message of the last failure on the calling
+ * thread is available from tbk_last_error().
+ *
+ * Device pointers are raw CUDA device addresses; `stream` is a cudaStream_t passed
+ * as void* (NULL = the legacy default stream).
+ */
+#ifndef TBK_H
+#define TBK_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TBK_EXPORT __attribute__((visibility("default")))
+
+/* status codes */
+enum {
+  TBK_OK = 0,
+  TBK_ERR_INVALID = 1,     /* bad argument / malformed forest */
+  TBK_ERR_CUDA = 2,        /* a CUDA runtime call failed */
+  TBK_ERR_UNSUPPORTED = 3, /* valid request outside what the kernels cover */
+  TBK_ERR_DEVICE_WAIT = 4, /* a bounded device-side wait expired */
+  TBK_ERR_IO = 5           /* file could not be read / parsed */
+};
+
+/* prediction transformations (src/include/DecisionForest.h:26) */
+enum { TBK_IDENTITY = 0, TBK_SIGMOID = 1, TBK_SOFTMAX = 2 };
+
+/* packed-forest representations
+ * (factory names in src/mlir/Representations.h:364-380 and
+ *  src/gpu/GPURepresentations.cpp:1238,1982, src/gpu/ReorgForestRepresentation.cpp:390) */
+enum { TBK_REP_SPARSE = 0, TBK_REP_ARRAY = 1, TBK_REP_REORG = 2 };
+
+/* output element kinds: fp32 prediction, or int8 class id for a multiclass forest
+ * (the reference's multiclass return type, test/python/gpu_tests.py:133-136) */
+enum { TBK_OUT_F32 = 0, TBK_OUT_I8 = 1 };
+
+/*
+ * Host-side forest as flat arrays: tree t owns nodes [tree_off[t], tree_off[t+1]);
+ * left/right are node indices inside the tree, -1/-1 marks a leaf; thr is the split
+ * threshold or, for a leaf, the leaf value (the reference keeps leaf values in the
+ * threshold field too: src/include/DecisionForest.h:35-54).  Replaces the in-memory
+ * model the reference's front end builds (src/json/xgboostparser.h:116-219).
+ */
+typedef struct tbk_forest_arrays {
+  int64_t num_trees;
+  const int64_t *tree_off;
+  const int32_t *left;
+  const int32_t *right;
+  const int32_t *feat;
+  const float *thr;
+  const int32_t *class_id; /* per tree; may be NULL when num_classes == 0 */
+  int32_t num_classes;     /* 0 = single output */
+  int32_t transform;       /* TBK_IDENTITY / TBK_SIGMOID / TBK_SOFTMAX */
+  double initial_value;
+  int32_t num_features;
+} tbk_forest_arrays;
+
+/*
+ * Schedule: the knobs of the reference's GPU auto-schedule options
+ * (src/include/TreebeardContext.h:138-162) mapped onto the fixed kernel family.
+ * A zero in any field means "let the selector choose".
+ */
+typedef struct tbk_schedule {
+  int32_t representation;  /* TBK_REP_* */
+  int32_t tile_size;       /* nodes per tile, 1..4 (0 = 1) */
+  int32_t rows_per_block;  /* numRowsPerTB */
+  int32_t rows_per_thread; /* numRowsPerThread: rows walked in lock-step by a lane */
+  int32_t tree_threads;    /* numTreeThreads: warps sharing a row tile, each on
+                              its own subset of trees */
+  int32_t tree_chunks;     /* grid.y: independent tree ranges whose partial sums are
+                              combined by an atomic-free second pass */
+  int32_t cache_trees;     /* 1 = stage tree groups in shared memory with bulk
+                              async copies, 2 = read nodes from global memory,
+                              0 = auto */
+  int32_t reserved[5];
+} tbk_schedule;
+
+typedef struct tbk_forest tbk_forest; /* opaque: packed forest resident on a device */
+
+typedef struct tbk_forest_info {
+  int64_t num_trees, num_nodes, num_groups;
+  int64_t packed_bytes;      /* bytes of node tiles resident on the device */
+  int32_t max_depth;         /* decision levels on the deepest root-to-leaf path */
+  int32_t num_features, num_classes, transform;
+  int32_t device;
+  tbk_schedule schedule;     /* the schedule the selector settled on */
+  int32_t staged;            /* 1 if tree groups are staged through shared memory */
+  int32_t smem_bytes;        /* dynamic shared memory per block of the walk kernel */
+  int32_t threads_per_block;
+  int32_t reserved[8];
+} tbk_forest_info;
+
+/* Packs the forest in the requested representation and uploads it to `device`.
+ * Replaces Init_Model / Init_Offsets / Init_Lengths / Init_ClassIds / Init_LUT /
+ * Init_Thresholds / Init_FeatureIndices (src/gpu/GPURepresentations.cpp:22-256,
+ * src/gpu/ReorgForestRepresentation.cpp:400-487) and the host-side lowering that
+ * feeds them (src/utils/TreeTilingUtils.cpp:427-556).  `schedule` may be NULL. */
+TBK_EXPORT int tbk_forest_create(const tbk_forest_arrays *forest, const tbk_schedule *schedule,
+                                 int32_t device, int64_t batch_hint, tbk_forest **out);
+
+/* Frees the device buffers (Dealloc_Buffers, src/gpu/GPUModelSerializers.cpp:231-262). */
+TBK_EXPORT int tbk_forest_free(tbk_forest *forest);
+
+TBK_EXPORT int tbk_forest_get_info(const tbk_forest *forest, tbk_forest_info *info);
+
+/* Replaces the kernel inside Prediction_Function (loop nest built by
+ * src/mlir/GPUAutoSchedule.cpp:318-472; walk src/mlir/CodeGenStateMachine.cpp:149-243;
+ * reduction src/reduction/LowerReduceOps.cpp:921-1003; initial value and sigmoid
+ * src/mlir/LowerToMidLevelIR.cpp:596-648; class argmax
+ * src/reduction/LowerReduceOps.cpp:148-189).  Rows are row-major with `ld` floats
+ * between rows; inputs and outputs are device-resident; stream-ordered.
+ * out_kind TBK_OUT_F32: n_rows floats (class id as a float for multiclass);
+ * TBK_OUT_I8: n_rows int8 class ids (multiclass only). */
+TBK_EXPORT int tbk_predict(tbk_forest *forest, const float *d_rows, int64_t n_rows, int64_t ld,
+                           void *d_out, int32_t out_kind, void *stream);
+
+/* Raw per-row sums of leaf values (n_rows x max(1, num_classes) floats, row-major):
+ * no initial value, no transformation.  This is what a tree shard contributes before
+ * the cross-device sum; tbk_finalize() turns summed partials into predictions. */
+TBK_EXPORT int tbk_predict_partial(tbk_forest *forest, const float *d_rows, int64_t n_rows,
+                                   int64_t ld, float *d_partial, void *stream);
+TBK_EXPORT int tbk_finalize(tbk_forest *forest, const float *d_partial, int64_t n_rows,
+                            void *d_out, int32_t out_kind, void *stream);
+
+/* Selected leaf per (row, tree): n_rows x num_trees int32, the leaf's node index in
+ * the numbering of the tbk_forest_arrays the forest was created from (the quantity
+ * the reference's tests observe through DecisionTree::PredictTree,
+ * src/include/DecisionForest.h:347-379). */
+TBK_EXPORT int tbk_predict_leaf_ids(tbk_forest *forest, const float *d_rows, int64_t n_rows,
+                                    int64_t ld, int32_t *d_leaf_ids, void *stream);
+
+/* Host-buffer variant of tbk_predict: the per-call H2D copy of the batch, the kernel
+ * and the D2H copy of the results that the reference's generated host code performs
+ * around its launch (src/gpu/GPUSupportUtils.cpp:150-343), here chunked and
+ * overlapped on two streams.  Blocks until the results are in h_out. */
+TBK_EXPORT int tbk_predict_host(tbk_forest *forest, const float *h_rows, int64_t n_rows,
+                                int64_t ld, void *h_out, int32_t out_kind);
+
+/* Device time of the walk (+ second pass) of the most recent tbk_predict* call on
+ * this forest, in microseconds, measured with CUDA events when enabled; the
+ * reference's counterpart is a host clock around the launch
+ * (src/gpu/GPUSupportUtils.cpp:66-104, src/debug-helpers/TreePrintRoutines.cpp:203-220). */
+TBK_EXPORT int tbk_set_timing(tbk_forest *forest, int32_t enable);
+TBK_EXPORT int64_t tbk_last_kernel_time_us(tbk_forest *forest);
+
+/* Reads the device status word (synchronises with the device): TBK_ERR_DEVICE_WAIT if
+ * a bounded wait inside a kernel expired since the last check, else TBK_OK. */
+TBK_EXPORT int tbk_check_status(tbk_forest *forest);
+
+/* Number of kernel launches issued on behalf of this forest since creation. */
+TBK_EXPORT int64_t tbk_launch_count(const tbk_forest *forest);
+
+/* Host-only check of the forest-to-buffer lowering: packs the forest exactly as
+ * tbk_forest_create would and interprets the packed buffers on the CPU with the slot
+ * arithmetic the kernels use.  leaf_ids (n_rows x num_trees) and sums
+ * (n_rows x max(1, num_classes)) may be NULL; rows may be NULL to pack only.  info, when
+ * given, receives sizes (reserved[0] = tile shapes, reserved[1] = look-up-table bytes,
+ * reserved[2] = bytes of the largest tree group).  No device is touched and no
+ * prediction entry point uses this routine: it exists for the layout known-answer
+ * tests that the reference runs on its serialised buffers (src/test/TestMain.cpp:903-1129). */
+TBK_EXPORT int tbk_host_layout_check(const tbk_forest_arrays *forest, const tbk_schedule *schedule,
+                                     const float *rows, int64_t n_rows, int64_t ld, int32_t *leaf_ids,
+                                     float *sums, tbk_forest_info *info);
+
+/* Host-only view of the launch-shape selector for a forest of the given shape (what the
+ * reference's auto-scheduler decides in src/mlir/GPUAutoSchedule.cpp:318-472).  info
+ * receives the schedule, shared-memory bytes and threads per block (reserved[0] = rows
+ * cached in shared memory, reserved[1] = grid.x, reserved[2] = groups per tree chunk). */
+TBK_EXPORT int tbk_plan_launch(int32_t num_features, int32_t num_classes, int64_t num_groups,
+                               int64_t max_group_bytes, int32_t lut_bytes, const tbk_schedule *schedule,
+                               int64_t n_rows, int32_t smem_limit, int32_t num_sms, tbk_forest_info *info);
+
+TBK_EXPORT const char *tbk_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TBK_H */

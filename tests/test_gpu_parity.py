@@ -1,0 +1,198 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bars: the selected leaf per (row, tree) is bit-exact; fp32 predictions are within
+1e-5 relative / 1e-6 absolute of the oracle (summation order differs); class ids are
+exact except where the two best class sums tie within rounding."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests.helpers import (SMALL, assert_predictions_close, golden_forest, small_config)
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def _dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+REPS = [("sparse", 1), ("array", 1), ("reorg", 1), ("sparse", 2), ("sparse", 3), ("sparse", 4),
+        ("array", 3), ("array", 4)]
+
+
+@pytest.mark.parametrize("name", list(SMALL))
+@pytest.mark.parametrize("rep,ts", REPS)
+def test_config_parity(name, rep, ts):
+    from treebeard_b200 import kernels
+    if name == "c5" and rep == "array" and ts > 1:
+        pytest.skip("array layout of deep unbalanced trees is too large by construction")
+    forest, X = small_config(name)
+    want, want_ids, sums = oracle.predict(forest, X, leaf_ids=True, class_sums=True)
+    df = kernels.DeviceForest(forest, representation=rep, tile_size=ts, batch_hint=len(X))
+    dX = _dev(X)
+    ids = df.predict_leaf_ids(dX).cpu().numpy()
+    assert np.array_equal(ids, want_ids), f"{(ids != want_ids).sum()} leaf ids differ"
+    got = df.predict(dX).cpu().numpy()
+    df.check_status()
+    assert_predictions_close(got, want, forest, sums)
+    if forest.num_classes > 0:
+        got8 = df.predict(dX, int8=True).cpu().numpy()
+        assert np.array_equal(got8.astype(np.float32), got)
+
+
+@pytest.mark.parametrize("name", ["c2", "c4", "c5"])
+@pytest.mark.parametrize("sched", [dict(tree_threads=4), dict(tree_chunks=3), dict(rows_per_thread=2),
+                                   dict(tree_threads=16, tree_chunks=2), dict(cache_trees=2),
+                                   dict(rows_per_block=64, tree_threads=2)])
+def test_schedule_variants(name, sched):
+    from treebeard_b200 import kernels
+    forest, X = small_config(name)
+    want, sums = oracle.predict(forest, X, class_sums=True)
+    df = kernels.DeviceForest(forest, representation="sparse", batch_hint=len(X), **sched)
+    got = df.predict(_dev(X)).cpu().numpy()
+    df.check_status()
+    assert_predictions_close(got, want, forest, sums)
+
+
+@pytest.mark.parametrize("n", [1, 31, 33, 100, 1025])
+def test_ragged_batches_and_strides(n):
+    from treebeard_b200 import kernels
+    forest, X = small_config("c2", rows=n)
+    want = oracle.predict(forest, X)
+    df = kernels.DeviceForest(forest, representation="sparse")
+    # padded row stride that breaks 16-byte alignment of rows: the scalar staging path
+    wide = torch.zeros((n, forest.num_features + 3), device="cuda")
+    wide[:, :forest.num_features] = _dev(X)
+    got = df.predict(wide[:, :forest.num_features]).cpu().numpy()
+    assert_predictions_close(got, want)
+    got2 = df.predict(_dev(X)).cpu().numpy()
+    assert_predictions_close(got2, want)
+
+
+def test_empty_batch_and_errors():
+    from treebeard_b200 import kernels
+    forest, X = small_config("c1", rows=8)
+    df = kernels.DeviceForest(forest)
+    out = df.predict(torch.empty((0, forest.num_features), device="cuda"))
+    assert out.numel() == 0
+    with pytest.raises(kernels.TbkError):
+        df.predict(_dev(X), int8=True)  # int8 output needs a multiclass forest
+
+
+def test_nan_and_ties_go_right():
+    from treebeard_b200 import kernels
+    forest, X = small_config("c4", rows=512)  # integer features: x == threshold is common
+    X = X.copy()
+    X[::7, ::3] = np.nan
+    X[::11, 1] = np.inf
+    X[::13, 2] = -np.inf
+    want, want_ids = oracle.predict(forest, X, leaf_ids=True)
+    df = kernels.DeviceForest(forest)
+    ids = df.predict_leaf_ids(_dev(X)).cpu().numpy()
+    assert np.array_equal(ids, want_ids)
+
+
+def test_partial_and_finalize_match_predict():
+    from treebeard_b200 import kernels
+    for name in ("c2", "c4"):
+        forest, X = small_config(name)
+        want, sums = oracle.predict(forest, X, class_sums=True)
+        half = forest.num_trees // 2
+        a = kernels.DeviceForest(forest.tree_slice(0, half))
+        b = kernels.DeviceForest(forest.tree_slice(half, forest.num_trees), tree_chunks=2)
+        dX = _dev(X)
+        total = a.predict_partial(dX) + b.predict_partial(dX)
+        got = a.finalize(total).cpu().numpy()
+        assert_predictions_close(got, want, forest, sums)
+
+
+def test_host_pipeline_matches_device_path():
+    from treebeard_b200 import kernels
+    forest, X = small_config("c2", rows=70000)
+    df = kernels.DeviceForest(forest)
+    dev = df.predict(_dev(X)).cpu().numpy()
+    host = df.predict_host(X)
+    assert np.array_equal(dev, host)
+    pinned = torch.from_numpy(X).pin_memory()
+    out = torch.empty(len(X), dtype=torch.float32).pin_memory()
+    df.predict_host(pinned.numpy(), out.numpy())
+    assert np.array_equal(out.numpy(), dev)
+
+
+@pytest.mark.parametrize("model", ["higgs", "airline", "year_prediction_msd"])
+def test_golden_benchmark_models(model, golden_dir):
+    from treebeard_b200 import kernels
+    z = np.load(os.path.join(golden_dir, model + ".npz"))
+    forest = golden_forest(z)
+    for rep in ("sparse", "array", "reorg"):
+        df = kernels.DeviceForest(forest, representation=rep)
+        got = df.predict(_dev(z["rows"])).cpu().numpy()
+        # the reference's own tolerance against XGBoost's predictions
+        assert oracle.fp_equal(got, z["expected"]).all()
+        assert_predictions_close(got, oracle.predict(forest, z["rows"]))
+
+
+@pytest.mark.parametrize("stem", ["TestModel_Size1_1", "TestModel_Size1_8", "TestModel_Size2_1",
+                                  "TestModel_Size2_13", "TestModel_Size4_1", "TestModel_Size4_10",
+                                  "leftheavy_xgb_model", "rightheavy_xgb_model",
+                                  "rightandleftheavy_xgb_model"])
+@pytest.mark.parametrize("rep", ["gpu_sparse", "gpu_array", "gpu_reorg"])
+def test_runner_api_on_golden_json(stem, rep, golden_dir):
+    """The reference-shaped flow: options -> context -> representation -> GPU runner."""
+    from treebeard_b200 import treebeard
+    z = np.load(os.path.join(golden_dir, stem + ".npz"))
+    rows, expected = z["rows"], z["expected"]
+    batch = 64
+    options = treebeard.CompilerOptions(batch, 1)
+    ctx = treebeard.TreebeardContext(os.path.join(golden_dir, stem + ".json"), "", options)
+    ctx.SetInputFiletype("xgboost_json")
+    ctx.SetRepresentationType(rep)
+    runner = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx)
+    assert runner.batchSize == batch and runner.rowSize == rows.shape[1]
+    got = runner.RunInference(np.ascontiguousarray(rows[:batch]))
+    assert oracle.fp_equal(got, expected[:batch]).all()
+    many = runner.RunInferenceOnMultipleBatches(np.ascontiguousarray(rows[:4 * batch]))
+    assert oracle.fp_equal(many, expected[:4 * batch]).all()
+    on_dev = runner.RunInference(_dev(rows[:batch])).cpu().numpy()
+    assert np.array_equal(on_dev, got)
+
+
+def test_runner_multiclass_int8(tmp_path):
+    from treebeard_b200 import synth, treebeard
+    forest, X = small_config("c4", rows=256)
+    path = str(tmp_path / "c4.json")
+    synth.save_xgboost_json(forest, path)
+    want, sums = oracle.predict(forest, X, class_sums=True)
+    options = treebeard.CompilerOptions(256, 1)
+    options.SetReturnTypeWidth(8)
+    options.SetReturnTypeIsFloatType(False)
+    ctx = treebeard.TreebeardContext(path, "", options,
+                                     treebeard.GPUAutoScheduleOptions.Construct(64, 1, 4))
+    ctx.SetRepresentationType("gpu_sparse")
+    runner = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx)
+    got = runner.RunInference(X, np.int8)
+    assert_predictions_close(got.astype(np.float32), want, forest, sums)
+
+
+def test_kernel_timing_api(tmp_path):
+    from treebeard_b200 import synth, treebeard
+    forest, X = small_config("c1")
+    path = str(tmp_path / "c1.json")
+    synth.save_xgboost_json(forest, path)
+    treebeard.SetEnableMeasureGpuKernelTime(True)
+    treebeard.SetNumberOfKernelRuns(3)
+    try:
+        options = treebeard.CompilerOptions(1024, 1)
+        ctx = treebeard.TreebeardContext(path, "", options)
+        ctx.SetRepresentationType("gpu_array")
+        runner = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx)
+        got = runner.RunInference(X)
+        assert treebeard.GetGPUKernelExecutionTime(runner) > 0
+        assert_predictions_close(got, oracle.predict(forest, X))
+    finally:
+        treebeard.SetEnableMeasureGpuKernelTime(False)
+        treebeard.SetNumberOfKernelRuns(1)

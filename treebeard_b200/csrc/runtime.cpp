@@ -1,0 +1,672 @@
+// The compile-then-run inference-runner API (see include/tbruntime.h), implemented over
+// the kernel library's C ABI (include/tbk.h).  "Compiling" a model here means: load the
+// model file into the host forest (front end), pack it in the chosen representation and
+// upload it, and bind the launch-shape options; "running" dispatches the walk kernels.
+// Reference: src/runtime/runtime.cpp (entry points), src/mlir/ExecutionHelpers.{h,cpp}
+// and src/gpu/GPUExecutionHelper.{h,cpp} (runner objects).
+#include "../../include/tbruntime.h"
+#include "../../include/tbk.h"
+#include "forest.h"
+#include "loaders.h"
+
+#include <cuda_runtime_api.h>
+
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <set>
+#include <sstream>
+#include <string>
+#include <vector>
+
+namespace {
+
+thread_local int32_t g_status = 0;
+thread_local std::string g_error;
+int32_t g_device = 0;
+bool g_use_sparse = false;  // process-wide default representation (src/mlir/Dialect.cpp:104-110)
+bool g_peeled_codegen = false;
+bool g_measure_kernel_time = false;
+int32_t g_kernel_runs = 1;
+
+void set_error(int32_t status, const std::string &msg) {
+  g_status = status;
+  g_error = msg;
+}
+void clear_error() {
+  g_status = 0;
+  g_error.clear();
+}
+
+// src/include/TreebeardContext.h:64-136
+struct CompilerOptions {
+  int32_t numberOfFeatures = -1;
+  int32_t batchSize = 0;
+  int32_t tileSize = 1;
+  int32_t thresholdTypeWidth = 32;
+  int32_t returnTypeWidth = 32;
+  bool returnTypeFloatType = true;
+  int32_t featureIndexTypeWidth = 16;
+  int32_t nodeIndexTypeWidth = 16;
+  int32_t inputElementTypeWidth = 32;
+  int32_t tileShapeBitWidth = 16;
+  int32_t childIndexBitWidth = 16;
+  int32_t tilingType = 0;
+  bool makeAllLeavesSameDepth = false;
+  bool reorderTreesByDepth = false;
+  int32_t pipelineSize = -1;
+  std::string statsProfileCSVPath;
+  int32_t numberOfCores = -1;
+  int32_t numParallelTreeBatches = -1;
+  bool oneTreeAtATime = false;
+};
+
+// src/include/TreebeardContext.h:138-162
+struct GPUAutoScheduleOptions {
+  int32_t numRowsPerTB = 0;
+  int32_t numRowsPerThread = 0;
+  int32_t rowTileSize = 0;
+  int32_t numTreeThreads = 0;
+  int32_t numTreesAtATime = 0;
+  bool cacheRows = false;
+  bool cacheTrees = false;
+  bool unrollTreeWalks = false;
+  int32_t treeWalkInterleaveFactor = -1;
+  bool sharedMemoryReduce = false;
+};
+
+struct Schedule;
+struct IndexVariable {
+  std::string name;
+  Schedule *owner = nullptr;
+  int32_t gpuConstruct = -1, gpuDim = -1;
+};
+
+// Loop-nest description object.  The kernels implement one fixed loop nest, so
+// directives are only recorded (and printed); see include/tbruntime.h.
+struct Schedule {
+  int32_t batchSize = 0, forestSize = 0;
+  std::vector<std::unique_ptr<IndexVariable>> vars;
+  IndexVariable *batch = nullptr, *tree = nullptr;
+  std::vector<std::string> directives;
+  bool touched = false;
+  Schedule(int32_t b, int32_t t) : batchSize(b), forestSize(t) {
+    batch = add("batch");
+    tree = add("tree");
+  }
+  IndexVariable *add(const std::string &n) {
+    vars.emplace_back(new IndexVariable{n, this});
+    return vars.back().get();
+  }
+  void note(const std::string &d) {
+    directives.push_back(d);
+    touched = true;
+  }
+};
+
+struct TreebeardContext {
+  std::string modelPath, globalsPath;
+  CompilerOptions options;
+  bool hasGpuOptions = false;
+  GPUAutoScheduleOptions gpuOptions;
+  std::string creatorType = "xgboost_json";
+  std::string representation; // empty: process default
+  tb::Forest forest;
+  bool forestLoaded = false;
+  std::unique_ptr<Schedule> schedule;
+};
+
+struct InferenceRunner {
+  tbk_forest *forest = nullptr;
+  int32_t batchSize = 0, rowSize = 0;
+  int32_t inputWidth = 32, returnWidth = 32;
+  bool returnFloat = true;
+  int32_t numClasses = 0;
+  int64_t kernelMicros = 0;
+};
+
+std::mutex g_live_mu;
+std::set<void *> g_representations;
+
+const char *name_of(const IndexVariable *v) { return v ? v->name.c_str() : "?"; }
+
+int rep_from_name(const std::string &name) {
+  if (name == "gpu_array" || name == "array") return TBK_REP_ARRAY;
+  if (name == "gpu_sparse" || name == "sparse") return TBK_REP_SPARSE;
+  if (name == "gpu_reorg") return TBK_REP_REORG;
+  return -1;
+}
+
+bool load_forest(const std::string &creator, const std::string &path, tb::Forest *f) {
+  std::string err;
+  if (creator == "xgboost_json") err = tb::load_xgboost_json(path, f);
+  else if (creator == "onnx_file") err = tb::load_onnx_file(path, f);
+  else err = "unknown forest creator \"" + creator + "\"";
+  if (!err.empty()) {
+    set_error(TBK_ERR_IO, err);
+    return false;
+  }
+  return true;
+}
+
+InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &opt,
+                              const GPUAutoScheduleOptions *gpu, const std::string &repName) {
+  if (opt.batchSize <= 0) {
+    set_error(TBK_ERR_INVALID, "batch size must be positive");
+    return nullptr;
+  }
+  if (opt.thresholdTypeWidth != 32 || opt.inputElementTypeWidth != 32) {
+    set_error(TBK_ERR_UNSUPPORTED, "only fp32 thresholds and fp32 inputs are supported");
+    return nullptr;
+  }
+  if (opt.tilingType != 0) {
+    set_error(TBK_ERR_UNSUPPORTED, "only uniform tiling is supported on the GPU path");
+    return nullptr;
+  }
+  const bool int8_out = !opt.returnTypeFloatType && opt.returnTypeWidth == 8;
+  if (!int8_out && !(opt.returnTypeFloatType && opt.returnTypeWidth == 32)) {
+    set_error(TBK_ERR_UNSUPPORTED, "return type must be fp32 or (multiclass) int8");
+    return nullptr;
+  }
+  if (int8_out && forest.num_classes == 0) {
+    set_error(TBK_ERR_INVALID, "int8 return type needs a multiclass model");
+    return nullptr;
+  }
+  int rep = repName.empty() ? (g_use_sparse ? TBK_REP_SPARSE : TBK_REP_ARRAY) : rep_from_name(repName);
+  if (rep < 0) {
+    set_error(TBK_ERR_INVALID, "unknown representation \"" + repName + "\"");
+    return nullptr;
+  }
+  tbk_schedule sched{};
+  sched.representation = rep;
+  sched.tile_size = opt.tileSize <= 0 ? 1 : opt.tileSize;
+  if (gpu) {
+    sched.rows_per_block = gpu->numRowsPerTB;
+    sched.rows_per_thread = gpu->numRowsPerThread;
+    sched.tree_threads = gpu->numTreeThreads;
+    sched.cache_trees = gpu->cacheTrees ? 1 : 0;
+  }
+  tbk_forest_arrays fa{};
+  fa.num_trees = forest.num_trees();
+  fa.tree_off = forest.tree_off.data();
+  fa.left = forest.left.data();
+  fa.right = forest.right.data();
+  fa.feat = forest.feat.data();
+  fa.thr = forest.thr.data();
+  fa.class_id = forest.num_classes > 0 ? forest.class_id.data() : nullptr;
+  fa.num_classes = forest.num_classes;
+  fa.transform = forest.transform;
+  fa.initial_value = forest.initial_value;
+  fa.num_features = opt.numberOfFeatures > 0 ? std::max(opt.numberOfFeatures, forest.num_features)
+                                              : forest.num_features;
+  tbk_forest *kf = nullptr;
+  const int rc = tbk_forest_create(&fa, &sched, g_device, opt.batchSize, &kf);
+  if (rc != TBK_OK) {
+    set_error(rc, tbk_last_error());
+    return nullptr;
+  }
+  auto *r = new InferenceRunner();
+  r->forest = kf;
+  r->batchSize = opt.batchSize;
+  r->rowSize = fa.num_features;
+  r->inputWidth = opt.inputElementTypeWidth;
+  r->returnWidth = opt.returnTypeWidth;
+  r->returnFloat = opt.returnTypeFloatType;
+  r->numClasses = forest.num_classes;
+  if (g_measure_kernel_time) tbk_set_timing(kf, 1);
+  return r;
+}
+
+InferenceRunner *runner_from_context(TreebeardContext *ctx) {
+  if (!ctx) {
+    set_error(TBK_ERR_INVALID, "null context");
+    return nullptr;
+  }
+  if (!ctx->forestLoaded) {
+    if (!load_forest(ctx->creatorType, ctx->modelPath, &ctx->forest)) return nullptr;
+    ctx->forestLoaded = true;
+  }
+  return build_runner(ctx->forest, ctx->options, ctx->hasGpuOptions ? &ctx->gpuOptions : nullptr,
+                      ctx->representation);
+}
+
+void run_batch(InferenceRunner *r, void *inputs, void *results, int64_t rows) {
+  const int32_t kind = (!r->returnFloat && r->returnWidth == 8) ? TBK_OUT_I8 : TBK_OUT_F32;
+  cudaPointerAttributes attr{};
+  const bool on_device = cudaPointerGetAttributes(&attr, inputs) == cudaSuccess &&
+                         (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged);
+  cudaGetLastError();
+  int rc = TBK_OK;
+  const int runs = g_measure_kernel_time ? std::max(1, g_kernel_runs) : 1;
+  if (on_device) {
+    for (int i = 0; i < runs && rc == TBK_OK; ++i) {
+      rc = tbk_predict(r->forest, static_cast<const float *>(inputs), rows, r->rowSize, results, kind, nullptr);
+      if (rc == TBK_OK && g_measure_kernel_time) {
+        const int64_t us = tbk_last_kernel_time_us(r->forest);
+        if (us > 0) r->kernelMicros += us;
+      }
+    }
+    if (rc == TBK_OK && cudaDeviceSynchronize() != cudaSuccess) {
+      rc = TBK_ERR_CUDA;
+      set_error(rc, "cudaDeviceSynchronize failed after the walk");
+      return;
+    }
+    if (rc == TBK_OK) rc = tbk_check_status(r->forest);
+  } else if (g_measure_kernel_time) {
+    // timed mode: copy once, then time the kernel alone, as the reference's
+    // generated host code does around its launch
+    float *d_in = nullptr;
+    void *d_out = nullptr;
+    const size_t in_bytes = (size_t)rows * r->rowSize * 4, out_bytes = (size_t)rows * (kind == TBK_OUT_I8 ? 1 : 4);
+    if (cudaMalloc(reinterpret_cast<void **>(&d_in), in_bytes) != cudaSuccess || cudaMalloc(&d_out, out_bytes) != cudaSuccess ||
+        cudaMemcpy(d_in, inputs, in_bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+      cudaFree(d_in);
+      cudaFree(d_out);
+      set_error(TBK_ERR_CUDA, "device staging for the timed run failed");
+      return;
+    }
+    for (int i = 0; i < runs && rc == TBK_OK; ++i) {
+      rc = tbk_predict(r->forest, d_in, rows, r->rowSize, d_out, kind, nullptr);
+      if (rc == TBK_OK) {
+        const int64_t us = tbk_last_kernel_time_us(r->forest);
+        if (us > 0) r->kernelMicros += us;
+      }
+    }
+    if (rc == TBK_OK && cudaMemcpy(results, d_out, out_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) rc = TBK_ERR_CUDA;
+    cudaFree(d_in);
+    cudaFree(d_out);
+    if (rc == TBK_OK) rc = tbk_check_status(r->forest);
+  } else {
+    rc = tbk_predict_host(r->forest, static_cast<const float *>(inputs), rows, r->rowSize, results, kind);
+  }
+  if (rc != TBK_OK) set_error(rc, tbk_last_error());
+}
+
+} // namespace
+
+extern "C" {
+
+int32_t TB_GetLastStatus(void) { return g_status; }
+const char *TB_GetLastError(void) { return g_error.c_str(); }
+void TB_SetDevice(int32_t device) { g_device = device; }
+
+// ---- execution ----
+
+intptr_t InitializeInferenceRunner(const char *, const char *) {
+  set_error(TBK_ERR_UNSUPPORTED, "loading a precompiled model is not available in this build");
+  return 0;
+}
+
+void RunInference(intptr_t runner, void *inputs, void *results) {
+  clear_error();
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  if (!r || !inputs || !results) return set_error(TBK_ERR_INVALID, "null argument");
+  run_batch(r, inputs, results, r->batchSize);
+}
+
+void RunInferenceOnMultipleBatches(intptr_t runner, void *inputs, void *results, int32_t numRows) {
+  clear_error();
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  if (!r || !inputs || !results) return set_error(TBK_ERR_INVALID, "null argument");
+  if (numRows < 0 || numRows % r->batchSize != 0)
+    return set_error(TBK_ERR_INVALID, "the number of rows must be a multiple of the batch size");
+  // batches are independent and contiguous: one pipelined pass covers them all
+  run_batch(r, inputs, results, numRows);
+}
+
+int32_t GetBatchSize(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  return r ? r->batchSize : 0;
+}
+int32_t GetRowSize(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  return r ? r->rowSize : 0;
+}
+int32_t TB_GetInputTypeBitWidth(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  return r ? r->inputWidth : 0;
+}
+int32_t TB_GetReturnTypeBitWidth(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  return r ? r->returnWidth : 0;
+}
+void DeleteInferenceRunner(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  if (!r) return;
+  tbk_forest_free(r->forest);
+  delete r;
+}
+void *TB_GetKernelForest(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  return r ? r->forest : nullptr;
+}
+int64_t GetGPUKernelExecutionTime(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  return (r && g_measure_kernel_time) ? r->kernelMicros : 0;
+}
+
+// ---- compiler options ----
+
+intptr_t CreateCompilerOptions(void) { return reinterpret_cast<intptr_t>(new CompilerOptions()); }
+void DeleteCompilerOptions(intptr_t o) { delete reinterpret_cast<CompilerOptions *>(o); }
+
+#define OPTION_SETTER(name, type, expr)                                      \
+  void Set_##name(intptr_t o, type val) {                                    \
+    auto *opt = reinterpret_cast<CompilerOptions *>(o);                      \
+    if (opt) opt->name = (expr);                                             \
+  }
+OPTION_SETTER(numberOfFeatures, int32_t, val)
+OPTION_SETTER(batchSize, int32_t, val)
+OPTION_SETTER(tileSize, int32_t, val)
+OPTION_SETTER(thresholdTypeWidth, int32_t, val)
+OPTION_SETTER(returnTypeWidth, int32_t, val)
+OPTION_SETTER(returnTypeFloatType, int32_t, val != 0)
+OPTION_SETTER(featureIndexTypeWidth, int32_t, val)
+OPTION_SETTER(nodeIndexTypeWidth, int32_t, val)
+OPTION_SETTER(inputElementTypeWidth, int32_t, val)
+OPTION_SETTER(tileShapeBitWidth, int32_t, val)
+OPTION_SETTER(childIndexBitWidth, int32_t, val)
+OPTION_SETTER(makeAllLeavesSameDepth, int32_t, val != 0)
+OPTION_SETTER(reorderTreesByDepth, int32_t, val != 0)
+OPTION_SETTER(statsProfileCSVPath, const char *, std::string(val ? val : ""))
+OPTION_SETTER(pipelineSize, int32_t, val)
+OPTION_SETTER(numberOfCores, int32_t, val)
+OPTION_SETTER(numParallelTreeBatches, int32_t, val)
+OPTION_SETTER(tilingType, int32_t, val)
+#undef OPTION_SETTER
+
+void SetOneTreeAtATimeSchedule(intptr_t o) {
+  auto *opt = reinterpret_cast<CompilerOptions *>(o);
+  if (opt) opt->oneTreeAtATime = true; // the kernels already walk one tree group at a time
+}
+
+// ---- GPU auto-schedule options ----
+
+intptr_t CreateGPUAutoScheduleOptions(void) { return reinterpret_cast<intptr_t>(new GPUAutoScheduleOptions()); }
+void DeleteGPUAutoScheduleOptions(intptr_t o) { delete reinterpret_cast<GPUAutoScheduleOptions *>(o); }
+#define GPU_OPTION_SETTER(name, expr)                                        \
+  void Set_##name(intptr_t o, int32_t val) {                                 \
+    auto *opt = reinterpret_cast<GPUAutoScheduleOptions *>(o);               \
+    if (opt) opt->name = (expr);                                             \
+  }
+GPU_OPTION_SETTER(numRowsPerTB, val)
+GPU_OPTION_SETTER(numRowsPerThread, val)
+GPU_OPTION_SETTER(rowTileSize, val)
+GPU_OPTION_SETTER(numTreeThreads, val)
+GPU_OPTION_SETTER(numTreesAtATime, val)
+GPU_OPTION_SETTER(cacheRows, val != 0)
+GPU_OPTION_SETTER(cacheTrees, val != 0)
+GPU_OPTION_SETTER(unrollTreeWalks, val != 0)
+GPU_OPTION_SETTER(treeWalkInterleaveFactor, val)
+GPU_OPTION_SETTER(sharedMemoryReduce, val != 0)
+#undef GPU_OPTION_SETTER
+
+// ---- one-call construction ----
+
+void GenerateLLVMIRForXGBoostModel(const char *, const char *, const char *, intptr_t) {
+  set_error(TBK_ERR_UNSUPPORTED, "this library has no LLVM back end; build a runner instead");
+}
+void CreateLLVMIRForONNXModel(const char *, const char *, const char *, intptr_t) {
+  set_error(TBK_ERR_UNSUPPORTED, "this library has no LLVM back end; build a runner instead");
+}
+
+intptr_t CreateInferenceRunner(const char *modelJSONPath, const char *, intptr_t options) {
+  clear_error();
+  auto *opt = reinterpret_cast<CompilerOptions *>(options);
+  if (!modelJSONPath || !opt) {
+    set_error(TBK_ERR_INVALID, "null argument");
+    return 0;
+  }
+  tb::Forest forest;
+  if (!load_forest("xgboost_json", modelJSONPath, &forest)) return 0;
+  return reinterpret_cast<intptr_t>(build_runner(forest, *opt, nullptr, ""));
+}
+
+intptr_t CreateInferenceRunnerForONNXModel(const char *modelPath, intptr_t options) {
+  clear_error();
+  auto *opt = reinterpret_cast<CompilerOptions *>(options);
+  if (!modelPath || !opt) {
+    set_error(TBK_ERR_INVALID, "null argument");
+    return 0;
+  }
+  tb::Forest forest;
+  if (!load_forest("onnx_file", modelPath, &forest)) return 0;
+  return reinterpret_cast<intptr_t>(build_runner(forest, *opt, nullptr, ""));
+}
+
+intptr_t TB_CreateInferenceRunnerFromArrays(const void *forestArrays, intptr_t options, intptr_t gpuOptions,
+                                            const char *representation) {
+  clear_error();
+  auto *fa = static_cast<const tbk_forest_arrays *>(forestArrays);
+  auto *opt = reinterpret_cast<CompilerOptions *>(options);
+  if (!fa || !opt || fa->num_trees <= 0) {
+    set_error(TBK_ERR_INVALID, "null or empty argument");
+    return 0;
+  }
+  tb::Forest f;
+  const int64_t T = fa->num_trees, N = fa->tree_off[T];
+  f.tree_off.assign(fa->tree_off, fa->tree_off + T + 1);
+  f.left.assign(fa->left, fa->left + N);
+  f.right.assign(fa->right, fa->right + N);
+  f.feat.assign(fa->feat, fa->feat + N);
+  f.thr.assign(fa->thr, fa->thr + N);
+  if (fa->class_id) f.class_id.assign(fa->class_id, fa->class_id + T);
+  else f.class_id.assign(T, 0);
+  f.num_classes = fa->num_classes;
+  f.transform = fa->transform;
+  f.initial_value = fa->initial_value;
+  f.num_features = fa->num_features;
+  return reinterpret_cast<intptr_t>(build_runner(f, *opt, reinterpret_cast<GPUAutoScheduleOptions *>(gpuOptions),
+                                                 representation ? representation : ""));
+}
+
+// ---- process-wide switches ----
+
+void SetEnableSparseRepresentation(int32_t val) { g_use_sparse = val != 0; }
+int32_t IsSparseRepresentationEnabled(void) { return g_use_sparse; }
+void SetPeeledCodeGenForProbabilityBasedTiling(int32_t val) { g_peeled_codegen = val != 0; }
+int32_t IsPeeledCodeGenForProbabilityBasedTilingEnabled(void) { return g_peeled_codegen; }
+void SetEnableMeasureGpuKernelTime(bool val) { g_measure_kernel_time = val; }
+void SetNumberOfKernelRuns(int32_t val) { g_kernel_runs = val; }
+
+// ---- representation objects ----
+
+void *ConstructRepresentation(const char *repName) {
+  clear_error();
+  if (!repName || rep_from_name(repName) < 0) {
+    set_error(TBK_ERR_INVALID, "unknown representation");
+    return nullptr;
+  }
+  auto *s = new std::string(repName);
+  std::lock_guard<std::mutex> lock(g_live_mu);
+  g_representations.insert(s);
+  return s;
+}
+void DestroyRepresentation(void *rep) {
+  std::lock_guard<std::mutex> lock(g_live_mu);
+  if (g_representations.erase(rep)) delete static_cast<std::string *>(rep);
+}
+
+// ---- context ----
+
+intptr_t ConstructTreebeardContext(const char *modelPath, const char *globalsPath, intptr_t options) {
+  clear_error();
+  auto *opt = reinterpret_cast<CompilerOptions *>(options);
+  if (!modelPath || !opt) {
+    set_error(TBK_ERR_INVALID, "null argument");
+    return 0;
+  }
+  auto *ctx = new TreebeardContext();
+  ctx->modelPath = modelPath;
+  ctx->globalsPath = globalsPath ? globalsPath : "";
+  ctx->options = *opt;
+  return reinterpret_cast<intptr_t>(ctx);
+}
+
+intptr_t ConstructTreebeardContextFromGPUAutoscheduleOptions(const char *modelPath, const char *globalsPath,
+                                                             intptr_t options, intptr_t gpuOptions) {
+  intptr_t h = ConstructTreebeardContext(modelPath, globalsPath, options);
+  auto *ctx = reinterpret_cast<TreebeardContext *>(h);
+  auto *gpu = reinterpret_cast<GPUAutoScheduleOptions *>(gpuOptions);
+  if (ctx && gpu) {
+    ctx->gpuOptions = *gpu;
+    ctx->hasGpuOptions = true;
+    // unrolled walks need every leaf at the same depth (src/runtime/runtime.cpp:784-785);
+    // the kernels always walk a fixed depth, so this only records the request
+    if (gpu->unrollTreeWalks) ctx->options.makeAllLeavesSameDepth = true;
+  }
+  return h;
+}
+
+void DestroyTreebeardContext(intptr_t c) { delete reinterpret_cast<TreebeardContext *>(c); }
+
+void SetForestCreatorType(intptr_t c, const char *creatorType) {
+  clear_error();
+  auto *ctx = reinterpret_cast<TreebeardContext *>(c);
+  if (!ctx || !creatorType) return set_error(TBK_ERR_INVALID, "null argument");
+  const std::string name = creatorType;
+  if (name != "xgboost_json" && name != "onnx_file")
+    return set_error(TBK_ERR_INVALID, "unknown forest creator \"" + name + "\"");
+  ctx->creatorType = name;
+  ctx->forestLoaded = false;
+}
+
+void SetRepresentationAndSerializer(intptr_t c, const char *repType) {
+  clear_error();
+  auto *ctx = reinterpret_cast<TreebeardContext *>(c);
+  if (!ctx || !repType) return set_error(TBK_ERR_INVALID, "null argument");
+  if (rep_from_name(repType) < 0) return set_error(TBK_ERR_INVALID, std::string("unknown representation \"") + repType + "\"");
+  ctx->representation = repType;
+}
+
+void BuildHIRRepresentation(void *c) {
+  clear_error();
+  auto *ctx = static_cast<TreebeardContext *>(c);
+  if (!ctx) return set_error(TBK_ERR_INVALID, "null context");
+  if (!ctx->forestLoaded) {
+    if (!load_forest(ctx->creatorType, ctx->modelPath, &ctx->forest)) return;
+    ctx->forestLoaded = true;
+  }
+  if (!ctx->schedule)
+    ctx->schedule.reset(new Schedule(ctx->options.batchSize, (int32_t)ctx->forest.num_trees()));
+}
+
+void *GetScheduleFromTBContext(intptr_t c) {
+  auto *ctx = reinterpret_cast<TreebeardContext *>(c);
+  if (!ctx) return nullptr;
+  if (!ctx->schedule) BuildHIRRepresentation(ctx);
+  return ctx->schedule.get();
+}
+
+bool LowerToLLVMAndDumpIR(void *, const char *) {
+  set_error(TBK_ERR_UNSUPPORTED, "this library has no LLVM back end");
+  return false;
+}
+
+void *ConstructInferenceRunnerFromHIR(void *c) {
+  clear_error();
+  return runner_from_context(static_cast<TreebeardContext *>(c));
+}
+void *ConstructGPUInferenceRunnerFromHIR(void *c) {
+  clear_error();
+  return runner_from_context(static_cast<TreebeardContext *>(c));
+}
+void *ConstructGPUInferenceRunnerFromTBContext(void *c) {
+  clear_error();
+  return runner_from_context(static_cast<TreebeardContext *>(c));
+}
+void *findBestGPUScheduleAndCompileModel(void *c) {
+  clear_error();
+  auto *ctx = static_cast<TreebeardContext *>(c);
+  if (!ctx) {
+    set_error(TBK_ERR_INVALID, "null context");
+    return nullptr;
+  }
+  // the selector replaces the timed search: drop any pinned launch shape and let it choose
+  ctx->hasGpuOptions = false;
+  if (ctx->representation.empty()) ctx->representation = "gpu_sparse";
+  return runner_from_context(ctx);
+}
+
+// ---- schedule objects ----
+
+#define SCHED(p) reinterpret_cast<Schedule *>(p)
+#define IDX(p) reinterpret_cast<IndexVariable *>(p)
+
+intptr_t Schedule_NewIndexVariable(intptr_t s, const char *name) {
+  return s ? reinterpret_cast<intptr_t>(SCHED(s)->add(name ? name : "")) : 0;
+}
+intptr_t Schedule_NewIndexVariable2(intptr_t s, intptr_t v) {
+  return (s && v) ? reinterpret_cast<intptr_t>(SCHED(s)->add(IDX(v)->name)) : 0;
+}
+void Schedule_Tile(intptr_t s, intptr_t i, intptr_t o, intptr_t in, int32_t tileSize) {
+  if (!s) return;
+  std::ostringstream os;
+  os << "tile(" << name_of(IDX(i)) << " -> " << name_of(IDX(o)) << ", " << name_of(IDX(in)) << ", " << tileSize << ")";
+  SCHED(s)->note(os.str());
+}
+void Schedule_Reorder(intptr_t s, intptr_t indices, int32_t n) {
+  if (!s) return;
+  std::ostringstream os;
+  os << "reorder(";
+  auto **arr = reinterpret_cast<IndexVariable **>(indices);
+  for (int32_t k = 0; arr && k < n; ++k) os << (k ? ", " : "") << name_of(arr[k]);
+  os << ")";
+  SCHED(s)->note(os.str());
+}
+void Schedule_Split(intptr_t s, intptr_t i, intptr_t a, intptr_t b, int32_t at, intptr_t) {
+  if (!s) return;
+  std::ostringstream os;
+  os << "split(" << name_of(IDX(i)) << " -> " << name_of(IDX(a)) << ", " << name_of(IDX(b)) << " at " << at << ")";
+  SCHED(s)->note(os.str());
+}
+intptr_t Schedule_Specialize(intptr_t s, intptr_t i) {
+  if (s) SCHED(s)->note(std::string("specialize(") + name_of(IDX(i)) + ")");
+  return 0;
+}
+int64_t GetSpecializationInfoNumIterations(intptr_t) { return 0; }
+int64_t GetSpecializationInfoNumEntries(intptr_t) { return 0; }
+void GetSpecializationInfoEntries(intptr_t, intptr_t, intptr_t) {}
+void Schedule_Pipeline(intptr_t s, intptr_t i, int32_t step) {
+  if (s) SCHED(s)->note(std::string("pipeline(") + name_of(IDX(i)) + ", " + std::to_string(step) + ")");
+}
+void Schedule_Simdize(intptr_t s, intptr_t i) { if (s) SCHED(s)->note(std::string("simdize(") + name_of(IDX(i)) + ")"); }
+void Schedule_Parallel(intptr_t s, intptr_t i) { if (s) SCHED(s)->note(std::string("parallel(") + name_of(IDX(i)) + ")"); }
+void Schedule_Unroll(intptr_t s, intptr_t i) { if (s) SCHED(s)->note(std::string("unroll(") + name_of(IDX(i)) + ")"); }
+void Schedule_PeelWalk(intptr_t s, intptr_t i, int32_t n) {
+  if (s) SCHED(s)->note(std::string("peelWalk(") + name_of(IDX(i)) + ", " + std::to_string(n) + ")");
+}
+void Schedule_Cache(intptr_t s, intptr_t i) { if (s) SCHED(s)->note(std::string("cache(") + name_of(IDX(i)) + ")"); }
+intptr_t Schedule_GetRootIndex(intptr_t s) { return s ? reinterpret_cast<intptr_t>(SCHED(s)->batch) : 0; }
+intptr_t Schedule_GetBatchIndex(intptr_t s) { return s ? reinterpret_cast<intptr_t>(SCHED(s)->batch) : 0; }
+intptr_t Schedule_GetTreeIndex(intptr_t s) { return s ? reinterpret_cast<intptr_t>(SCHED(s)->tree) : 0; }
+int32_t Schedule_PrintToString(intptr_t s, intptr_t str, int32_t len) {
+  if (!s) return -1;
+  std::ostringstream os;
+  os << "for batch in [0, " << SCHED(s)->batchSize << ") x tree in [0, " << SCHED(s)->forestSize << ")";
+  for (auto &d : SCHED(s)->directives) os << "; " << d;
+  const std::string text = os.str();
+  // as the reference: -1 when the buffer is too small, else the text length
+  if (!str || len < (int32_t)text.size() + 1) return -1;
+  std::memcpy(reinterpret_cast<char *>(str), text.c_str(), text.size() + 1);
+  return (int32_t)text.size();
+}
+int32_t Schedule_GetBatchSize(intptr_t s) { return s ? SCHED(s)->batchSize : 0; }
+int32_t Schedule_GetForestSize(intptr_t s) { return s ? SCHED(s)->forestSize : 0; }
+bool Schedule_IsDefaultSchedule(intptr_t s) { return s ? !SCHED(s)->touched : true; }
+void Schedule_Finalize(intptr_t) {}
+void Schedule_AtomicReduce(intptr_t s, intptr_t i) { if (s) SCHED(s)->note(std::string("atomicReduce(") + name_of(IDX(i)) + ")"); }
+void Schedule_VectorReduce(intptr_t s, intptr_t i, int32_t w) {
+  if (s) SCHED(s)->note(std::string("vectorReduce(") + name_of(IDX(i)) + ", " + std::to_string(w) + ")");
+}
+void Schedule_SharedReduce(intptr_t s, intptr_t i) { if (s) SCHED(s)->note(std::string("sharedReduce(") + name_of(IDX(i)) + ")"); }
+void IndexVariable_SetGPUThreadDim(intptr_t v, int32_t construct, int32_t dim) {
+  if (!v) return;
+  IDX(v)->gpuConstruct = construct;
+  IDX(v)->gpuDim = dim;
+}
+#undef SCHED
+#undef IDX
+
+} // extern "C"

@@ -1,0 +1,591 @@
+// C ABI of the kernel library (see include/tbk.h): packed-forest upload, launch-shape
+// selection, kernel dispatch, the second pass, and the host-buffer pipeline.
+#include "../../include/tbk.h"
+#include "pack.h"
+#include "schedule.h"
+#include "walk_kernels.cuh"
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                     \
+  do {                                                                                     \
+    cudaError_t e__ = (expr);                                                              \
+    if (e__ != cudaSuccess)                                                                \
+      return fail(TBK_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__),   \
+                  __FILE__, __LINE__);                                                     \
+  } while (0)
+
+} // namespace
+
+struct tbk_forest {
+  tb::PackedForest packed; // host copy (orig_node kept for lazy upload)
+  int device = 0;
+  tbk_schedule user{};     // what the caller asked for (zeros = auto)
+  tb::LaunchPlan last_plan{};
+  int64_t batch_hint = 0;
+  int max_smem_optin = 0;
+  int num_sms = 0;
+  // device buffers
+  uint8_t *d_blob = nullptr;
+  tb::DevGroupMeta *d_groups = nullptr;
+  int16_t *d_tree_class = nullptr;
+  int32_t *d_tree_index = nullptr;
+  int32_t *d_orig_node = nullptr;
+  unsigned long long *d_orig_off = nullptr;
+  int8_t *d_lut = nullptr;
+  int32_t *d_status = nullptr;
+  float *d_scratch = nullptr; // tree-chunk partials
+  size_t scratch_bytes = 0;
+  // host pipeline
+  float *d_in[2] = {nullptr, nullptr};
+  unsigned char *d_res[2] = {nullptr, nullptr};
+  float *h_pin[2] = {nullptr, nullptr};
+  unsigned char *h_res = nullptr;
+  size_t pipe_rows = 0, pipe_ld = 0, h_res_bytes = 0;
+  cudaStream_t streams[2] = {nullptr, nullptr};
+  cudaEvent_t in_free[2] = {nullptr, nullptr};
+  // timing
+  bool timing = false;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  bool ev_pending = false;
+  int64_t launches = 0;
+  std::mutex mu;
+};
+
+namespace {
+
+using KernelFn = void (*)(const tb::WalkParams);
+
+template <int REP, int TS> KernelFn pick3(int rpl, bool staged, bool cached) {
+  if (!cached) return staged ? tb::tb_walk_kernel<REP, TS, 1, true, false> : tb::tb_walk_kernel<REP, TS, 1, false, false>;
+  if (rpl == 2) return staged ? tb::tb_walk_kernel<REP, TS, 2, true, true> : tb::tb_walk_kernel<REP, TS, 2, false, true>;
+  return staged ? tb::tb_walk_kernel<REP, TS, 1, true, true> : tb::tb_walk_kernel<REP, TS, 1, false, true>;
+}
+
+KernelFn pick_kernel(int rep, int ts, int rpl, bool staged, bool cached) {
+  if (rep == tb::kReorg) return pick3<2, 1>(rpl, staged, cached);
+  if (rep == tb::kSparse) {
+    switch (ts) {
+    case 1: return pick3<0, 1>(rpl, staged, cached);
+    case 2: return pick3<0, 2>(rpl, staged, cached);
+    case 3: return pick3<0, 3>(rpl, staged, cached);
+    default: return pick3<0, 4>(rpl, staged, cached);
+    }
+  }
+  switch (ts) {
+  case 1: return pick3<1, 1>(rpl, staged, cached);
+  case 2: return pick3<1, 2>(rpl, staged, cached);
+  case 3: return pick3<1, 3>(rpl, staged, cached);
+  default: return pick3<1, 4>(rpl, staged, cached);
+  }
+}
+
+int ensure_scratch(tbk_forest *f, size_t bytes) {
+  if (bytes <= f->scratch_bytes) return TBK_OK;
+  if (f->d_scratch) CUDA_TRY(cudaFree(f->d_scratch));
+  f->d_scratch = nullptr;
+  f->scratch_bytes = 0;
+  CUDA_TRY(cudaMalloc(&f->d_scratch, bytes));
+  f->scratch_bytes = bytes;
+  return TBK_OK;
+}
+
+int ensure_orig(tbk_forest *f) {
+  if (f->d_orig_node) return TBK_OK;
+  const auto &p = f->packed;
+  CUDA_TRY(cudaMalloc(&f->d_orig_node, std::max<size_t>(4, p.orig_node.size() * 4)));
+  CUDA_TRY(cudaMemcpy(f->d_orig_node, p.orig_node.data(), p.orig_node.size() * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMalloc(&f->d_orig_off, std::max<size_t>(8, p.orig_off.size() * 8)));
+  CUDA_TRY(cudaMemcpy(f->d_orig_off, p.orig_off.data(), p.orig_off.size() * 8, cudaMemcpyHostToDevice));
+  return TBK_OK;
+}
+
+enum Mode { kPredict, kPartial, kLeafIds };
+
+// One prediction over device-resident rows.
+int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
+        int32_t out_kind, float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot = 0) {
+  const auto &pk = f->packed;
+  if (n_rows < 0 || ld < pk.num_features) return fail(TBK_ERR_INVALID, "ld (%lld) is smaller than the row size (%d)", (long long)ld, pk.num_features);
+  if (n_rows == 0) return TBK_OK;
+  if (!d_rows) return fail(TBK_ERR_INVALID, "null input pointer");
+  if (mode == kPredict) {
+    if (!d_out) return fail(TBK_ERR_INVALID, "null output pointer");
+    if (out_kind == TBK_OUT_I8 && pk.num_classes == 0) return fail(TBK_ERR_INVALID, "int8 output needs a multiclass forest");
+    if (out_kind != TBK_OUT_F32 && out_kind != TBK_OUT_I8) return fail(TBK_ERR_INVALID, "unknown output kind %d", out_kind);
+  }
+  CUDA_TRY(cudaSetDevice(f->device));
+
+  tb::ForestShape shape{pk.num_features, pk.num_classes, (int64_t)pk.groups.size(), pk.max_group_bytes,
+                        (int32_t)pk.lut.size(), pk.representation, pk.tile_size};
+  tb::LaunchPlan plan;
+  std::string why = tb::select_launch(shape, f->user, n_rows, f->max_smem_optin, f->num_sms, mode == kLeafIds, &plan);
+  if (!why.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", why.c_str());
+  f->last_plan = plan;
+
+  const int W = std::max(1, pk.num_classes);
+  const bool need_partials = mode == kPartial || (mode == kPredict && plan.chunks > 1);
+  float *partial_dst = nullptr;
+  if (mode == kLeafIds) {
+    int rc = ensure_orig(f);
+    if (rc) return rc;
+  } else if (need_partials) {
+    if (mode == kPartial && plan.chunks == 1) {
+      partial_dst = d_partial;
+    } else {
+      // two slots, so that the two streams of the host pipeline never share partials
+      const size_t need = ((size_t)plan.chunks * n_rows * W * sizeof(float) + 255) & ~(size_t)255;
+      int rc = ensure_scratch(f, 2 * need);
+      if (rc) return rc;
+      partial_dst = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(f->d_scratch) + (size_t)slot * (f->scratch_bytes / 2));
+    }
+  }
+
+  tb::WalkParams p{};
+  p.blob = f->d_blob;
+  p.groups = f->d_groups;
+  p.tree_class = f->d_tree_class;
+  p.tree_index = f->d_tree_index;
+  p.orig_node = f->d_orig_node;
+  p.orig_off = f->d_orig_off;
+  p.lut = f->d_lut;
+  p.lut_bytes = (int32_t)pk.lut.size();
+  p.rows = d_rows;
+  p.n_rows = n_rows;
+  p.ld = ld;
+  p.partial = partial_dst;
+  p.out = d_out;
+  p.out_kind = out_kind;
+  p.write_partial = need_partials ? 1 : 0;
+  p.leaf_ids = mode == kLeafIds ? d_leaf_ids : nullptr;
+  p.num_trees = pk.num_trees;
+  p.num_groups = (int32_t)pk.groups.size();
+  p.groups_per_chunk = plan.groups_per_chunk;
+  p.num_features = pk.num_features;
+  p.num_classes = pk.num_classes;
+  p.transform = pk.transform;
+  p.initial_value = (float)pk.initial_value;
+  p.row_warps = plan.row_warps;
+  p.tree_threads = plan.tree_threads;
+  p.stage_bytes = plan.staged ? plan.stage_bytes : 0;
+  p.vec4_ok = (pk.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
+  p.status = f->d_status;
+
+  KernelFn fn = pick_kernel(pk.representation, pk.tile_size, plan.rows_per_lane, plan.staged, plan.cache_rows);
+  CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
+  if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
+  dim3 grid((unsigned)plan.grid_x, (unsigned)plan.chunks), block((unsigned)plan.threads);
+  fn<<<grid, block, plan.smem_bytes, stream>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  ++f->launches;
+  if (mode == kPredict && plan.chunks > 1) {
+    const int tpb = 256;
+    tb::tb_finalize_kernel<<<(unsigned)((n_rows + tpb - 1) / tpb), tpb, 0, stream>>>(
+        partial_dst, plan.chunks, n_rows, W, pk.num_classes, (float)pk.initial_value, pk.transform, d_out, out_kind);
+    CUDA_TRY(cudaGetLastError());
+    ++f->launches;
+  } else if (mode == kPartial && plan.chunks > 1) {
+    const int tpb = 256;
+    const long long total = n_rows * W;
+    tb::tb_sum_partials_kernel<<<(unsigned)((total + tpb - 1) / tpb), tpb, 0, stream>>>(partial_dst, plan.chunks, total, d_partial);
+    CUDA_TRY(cudaGetLastError());
+    ++f->launches;
+  }
+  if (f->timing) {
+    CUDA_TRY(cudaEventRecord(f->ev1, stream));
+    f->ev_pending = true;
+  }
+  return TBK_OK;
+}
+
+int check_status(tbk_forest *f) {
+  int32_t st = 0;
+  CUDA_TRY(cudaMemcpy(&st, f->d_status, 4, cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    int32_t zero = 0;
+    cudaMemcpy(f->d_status, &zero, 4, cudaMemcpyHostToDevice);
+    return fail(TBK_ERR_DEVICE_WAIT, "a bounded wait on a bulk copy expired inside the walk kernel (status %d)", st);
+  }
+  return TBK_OK;
+}
+
+void free_pipeline(tbk_forest *f) {
+  for (int i = 0; i < 2; ++i) {
+    if (f->d_in[i]) cudaFree(f->d_in[i]);
+    if (f->d_res[i]) cudaFree(f->d_res[i]);
+    if (f->h_pin[i]) cudaFreeHost(f->h_pin[i]);
+    f->d_in[i] = nullptr; f->d_res[i] = nullptr; f->h_pin[i] = nullptr;
+  }
+  if (f->h_res) cudaFreeHost(f->h_res);
+  f->h_res = nullptr;
+  f->pipe_rows = f->pipe_ld = f->h_res_bytes = 0;
+}
+
+} // namespace
+
+extern "C" {
+
+const char *tbk_last_error(void) { return g_last_error.c_str(); }
+
+int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, int32_t device,
+                      int64_t batch_hint, tbk_forest **out) {
+  if (!fa || !out) return fail(TBK_ERR_INVALID, "null argument");
+  *out = nullptr;
+  if (fa->num_trees <= 0 || !fa->tree_off || !fa->left || !fa->right || !fa->feat || !fa->thr)
+    return fail(TBK_ERR_INVALID, "forest arrays are incomplete");
+  tb::Forest host;
+  const int64_t T = fa->num_trees, N = fa->tree_off[T];
+  if (N <= 0) return fail(TBK_ERR_INVALID, "forest has no nodes");
+  host.tree_off.assign(fa->tree_off, fa->tree_off + T + 1);
+  host.left.assign(fa->left, fa->left + N);
+  host.right.assign(fa->right, fa->right + N);
+  host.feat.assign(fa->feat, fa->feat + N);
+  host.thr.assign(fa->thr, fa->thr + N);
+  if (fa->num_classes > 0) {
+    if (!fa->class_id) return fail(TBK_ERR_INVALID, "multiclass forest without class ids");
+    host.class_id.assign(fa->class_id, fa->class_id + T);
+  }
+  host.num_classes = fa->num_classes;
+  host.transform = fa->transform;
+  host.initial_value = fa->initial_value;
+  host.num_features = fa->num_features;
+  if (fa->num_classes > 0 && fa->num_classes > 127) return fail(TBK_ERR_UNSUPPORTED, "more than 127 classes");
+
+  auto *f = new tbk_forest();
+  if (schedule) f->user = *schedule;
+  f->batch_hint = batch_hint;
+  f->device = device;
+  tb::PackOptions opt;
+  opt.representation = f->user.representation;
+  opt.tile_size = f->user.tile_size <= 0 ? 1 : f->user.tile_size;
+  std::string err = tb::pack_forest(host, opt, &f->packed);
+  if (!err.empty()) {
+    delete f;
+    return fail(TBK_ERR_INVALID, "%s", err.c_str());
+  }
+  const auto &p = f->packed;
+  auto bail = [&](int rc) {
+    tbk_forest_free(f);
+    return rc;
+  };
+#define CUDA_TRY_F(expr)                                                                   \
+  do {                                                                                     \
+    cudaError_t e__ = (expr);                                                              \
+    if (e__ != cudaSuccess)                                                                \
+      return bail(fail(TBK_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)));    \
+  } while (0)
+  CUDA_TRY_F(cudaSetDevice(device));
+  CUDA_TRY_F(cudaDeviceGetAttribute(&f->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  CUDA_TRY_F(cudaDeviceGetAttribute(&f->num_sms, cudaDevAttrMultiProcessorCount, device));
+  CUDA_TRY_F(cudaMalloc(&f->d_blob, std::max<size_t>(16, p.blob.size())));
+  CUDA_TRY_F(cudaMemcpy(f->d_blob, p.blob.data(), p.blob.size(), cudaMemcpyHostToDevice));
+  static_assert(sizeof(tb::GroupMeta) == sizeof(tb::DevGroupMeta), "group metadata layout");
+  CUDA_TRY_F(cudaMalloc(&f->d_groups, p.groups.size() * sizeof(tb::GroupMeta)));
+  CUDA_TRY_F(cudaMemcpy(f->d_groups, p.groups.data(), p.groups.size() * sizeof(tb::GroupMeta), cudaMemcpyHostToDevice));
+  CUDA_TRY_F(cudaMalloc(&f->d_tree_class, p.tree_class.size() * 2));
+  CUDA_TRY_F(cudaMemcpy(f->d_tree_class, p.tree_class.data(), p.tree_class.size() * 2, cudaMemcpyHostToDevice));
+  CUDA_TRY_F(cudaMalloc(&f->d_tree_index, p.tree_index.size() * 4));
+  CUDA_TRY_F(cudaMemcpy(f->d_tree_index, p.tree_index.data(), p.tree_index.size() * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY_F(cudaMalloc(&f->d_lut, std::max<size_t>(16, p.lut.size())));
+  CUDA_TRY_F(cudaMemcpy(f->d_lut, p.lut.data(), p.lut.size(), cudaMemcpyHostToDevice));
+  CUDA_TRY_F(cudaMalloc(&f->d_status, 4));
+  CUDA_TRY_F(cudaMemset(f->d_status, 0, 4));
+  CUDA_TRY_F(cudaEventCreate(&f->ev0));
+  CUDA_TRY_F(cudaEventCreate(&f->ev1));
+  // the packed blob is only needed on the device from here on
+  std::vector<uint8_t>().swap(f->packed.blob);
+  // settle the plan for the hinted batch so that get_info can report it
+  tb::ForestShape shape{p.num_features, p.num_classes, (int64_t)p.groups.size(), p.max_group_bytes,
+                        (int32_t)p.lut.size(), p.representation, p.tile_size};
+  std::string why = tb::select_launch(shape, f->user, batch_hint > 0 ? batch_hint : 65536, f->max_smem_optin,
+                                      f->num_sms, false, &f->last_plan);
+  if (!why.empty()) return bail(fail(TBK_ERR_UNSUPPORTED, "%s", why.c_str()));
+  *out = f;
+  return TBK_OK;
+}
+
+int tbk_forest_free(tbk_forest *f) {
+  if (!f) return TBK_OK;
+  cudaSetDevice(f->device);
+  free_pipeline(f);
+  for (int i = 0; i < 2; ++i) {
+    if (f->streams[i]) cudaStreamDestroy(f->streams[i]);
+    if (f->in_free[i]) cudaEventDestroy(f->in_free[i]);
+  }
+  cudaFree(f->d_blob);
+  cudaFree(f->d_groups);
+  cudaFree(f->d_tree_class);
+  cudaFree(f->d_tree_index);
+  cudaFree(f->d_orig_node);
+  cudaFree(f->d_orig_off);
+  cudaFree(f->d_lut);
+  cudaFree(f->d_status);
+  cudaFree(f->d_scratch);
+  if (f->ev0) cudaEventDestroy(f->ev0);
+  if (f->ev1) cudaEventDestroy(f->ev1);
+  delete f;
+  return TBK_OK;
+}
+
+int tbk_forest_get_info(const tbk_forest *f, tbk_forest_info *info) {
+  if (!f || !info) return fail(TBK_ERR_INVALID, "null argument");
+  std::memset(info, 0, sizeof *info);
+  const auto &p = f->packed;
+  info->num_trees = p.num_trees;
+  info->num_nodes = p.num_nodes;
+  info->num_groups = (int64_t)p.groups.size();
+  info->packed_bytes = p.groups.empty() ? 0 : (int64_t)(p.groups.back().byte_off +
+      (((uint64_t)p.groups.back().slots * tb::kGroupTrees * p.tile_bytes + 15) & ~15ull));
+  info->max_depth = p.max_depth;
+  info->num_features = p.num_features;
+  info->num_classes = p.num_classes;
+  info->transform = p.transform;
+  info->device = f->device;
+  const tb::LaunchPlan &pl = f->last_plan;
+  info->schedule.representation = p.representation;
+  info->schedule.tile_size = p.tile_size;
+  info->schedule.rows_per_block = pl.row_warps * 32 * pl.rows_per_lane;
+  info->schedule.rows_per_thread = pl.rows_per_lane;
+  info->schedule.tree_threads = pl.tree_threads;
+  info->schedule.tree_chunks = pl.chunks;
+  info->schedule.cache_trees = pl.staged ? 1 : 2;
+  info->staged = pl.staged;
+  info->smem_bytes = pl.smem_bytes;
+  info->threads_per_block = pl.threads;
+  return TBK_OK;
+}
+
+int tbk_predict(tbk_forest *f, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
+                int32_t out_kind, void *stream) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  std::lock_guard<std::mutex> lock(f->mu);
+  return run(f, kPredict, d_rows, n_rows, ld, d_out, out_kind, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+int tbk_predict_partial(tbk_forest *f, const float *d_rows, int64_t n_rows, int64_t ld, float *d_partial,
+                        void *stream) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  if (!d_partial && n_rows > 0) return fail(TBK_ERR_INVALID, "null output pointer");
+  std::lock_guard<std::mutex> lock(f->mu);
+  return run(f, kPartial, d_rows, n_rows, ld, nullptr, TBK_OUT_F32, d_partial, nullptr, (cudaStream_t)stream);
+}
+
+int tbk_finalize(tbk_forest *f, const float *d_partial, int64_t n_rows, void *d_out, int32_t out_kind,
+                 void *stream) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  if (n_rows == 0) return TBK_OK;
+  if (!d_partial || !d_out) return fail(TBK_ERR_INVALID, "null pointer");
+  const auto &p = f->packed;
+  if (out_kind == TBK_OUT_I8 && p.num_classes == 0) return fail(TBK_ERR_INVALID, "int8 output needs a multiclass forest");
+  std::lock_guard<std::mutex> lock(f->mu);
+  CUDA_TRY(cudaSetDevice(f->device));
+  const int tpb = 256;
+  tb::tb_finalize_kernel<<<(unsigned)((n_rows + tpb - 1) / tpb), tpb, 0, (cudaStream_t)stream>>>(
+      d_partial, 1, n_rows, std::max(1, p.num_classes), p.num_classes, (float)p.initial_value, p.transform, d_out, out_kind);
+  CUDA_TRY(cudaGetLastError());
+  ++f->launches;
+  return TBK_OK;
+}
+
+int tbk_predict_leaf_ids(tbk_forest *f, const float *d_rows, int64_t n_rows, int64_t ld,
+                         int32_t *d_leaf_ids, void *stream) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  if (!d_leaf_ids && n_rows > 0) return fail(TBK_ERR_INVALID, "null output pointer");
+  std::lock_guard<std::mutex> lock(f->mu);
+  return run(f, kLeafIds, d_rows, n_rows, ld, nullptr, TBK_OUT_F32, nullptr, d_leaf_ids, (cudaStream_t)stream);
+}
+
+int tbk_predict_host(tbk_forest *f, const float *h_rows, int64_t n_rows, int64_t ld, void *h_out,
+                     int32_t out_kind) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  if (n_rows == 0) return TBK_OK;
+  if (!h_rows || !h_out) return fail(TBK_ERR_INVALID, "null pointer");
+  std::lock_guard<std::mutex> lock(f->mu);
+  CUDA_TRY(cudaSetDevice(f->device));
+  const size_t out_elt = out_kind == TBK_OUT_I8 ? 1 : 4;
+  // chunk size: about 64 MiB of features, a multiple of 1024 rows
+  size_t chunk = std::max<size_t>(1024, ((size_t)64 << 20) / ((size_t)ld * 4) / 1024 * 1024);
+  chunk = std::min<size_t>(chunk, ((size_t)n_rows + 1023) / 1024 * 1024);
+  if (!f->streams[0]) {
+    for (int i = 0; i < 2; ++i) {
+      CUDA_TRY(cudaStreamCreateWithFlags(&f->streams[i], cudaStreamNonBlocking));
+      CUDA_TRY(cudaEventCreateWithFlags(&f->in_free[i], cudaEventDisableTiming));
+    }
+  }
+  cudaPointerAttributes attr{};
+  const bool in_pinned = cudaPointerGetAttributes(&attr, h_rows) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+  cudaGetLastError();
+  cudaPointerAttributes oattr{};
+  const bool out_pinned = cudaPointerGetAttributes(&oattr, h_out) == cudaSuccess && oattr.type == cudaMemoryTypeHost;
+  cudaGetLastError();
+  if (f->pipe_rows < chunk || f->pipe_ld != (size_t)ld) {
+    free_pipeline(f);
+    for (int i = 0; i < 2; ++i) {
+      CUDA_TRY(cudaMalloc(&f->d_in[i], chunk * ld * 4));
+      CUDA_TRY(cudaMalloc(&f->d_res[i], chunk * 4));
+    }
+    f->pipe_rows = chunk;
+    f->pipe_ld = (size_t)ld;
+  }
+  if (!in_pinned && !f->h_pin[0])
+    for (int i = 0; i < 2; ++i) CUDA_TRY(cudaMallocHost(&f->h_pin[i], f->pipe_rows * ld * 4));
+  if (!out_pinned && f->h_res_bytes < (size_t)n_rows * out_elt) {
+    if (f->h_res) CUDA_TRY(cudaFreeHost(f->h_res));
+    f->h_res = nullptr;
+    CUDA_TRY(cudaMallocHost(&f->h_res, (size_t)n_rows * out_elt));
+    f->h_res_bytes = (size_t)n_rows * out_elt;
+  }
+  unsigned char *res_dst = out_pinned ? static_cast<unsigned char *>(h_out) : f->h_res;
+  const bool was_timing = f->timing;
+  f->timing = false; // per-chunk launches overlap on two streams; event timing does not apply
+  int rc = TBK_OK;
+  int64_t done = 0;
+  for (int it = 0; done < n_rows && rc == TBK_OK; ++it) {
+    const int s = it & 1;
+    const int64_t n = std::min<int64_t>((int64_t)chunk, n_rows - done);
+    const float *src = h_rows + done * ld;
+    if (!in_pinned) {
+      // the staging buffer is free once the copy that last read it has finished
+      cudaError_t e = cudaEventSynchronize(f->in_free[s]);
+      if (e != cudaSuccess) { rc = fail(TBK_ERR_CUDA, "cudaEventSynchronize: %s", cudaGetErrorString(e)); break; }
+      std::memcpy(f->h_pin[s], src, (size_t)n * ld * 4);
+      src = f->h_pin[s];
+    }
+    cudaError_t e = cudaMemcpyAsync(f->d_in[s], src, (size_t)n * ld * 4, cudaMemcpyHostToDevice, f->streams[s]);
+    if (e == cudaSuccess) e = cudaEventRecord(f->in_free[s], f->streams[s]);
+    if (e != cudaSuccess) { rc = fail(TBK_ERR_CUDA, "host-to-device copy: %s", cudaGetErrorString(e)); break; }
+    rc = run(f, kPredict, f->d_in[s], n, ld, f->d_res[s], out_kind, nullptr, nullptr, f->streams[s], s);
+    if (rc != TBK_OK) break;
+    e = cudaMemcpyAsync(res_dst + done * out_elt, f->d_res[s], (size_t)n * out_elt, cudaMemcpyDeviceToHost, f->streams[s]);
+    if (e != cudaSuccess) { rc = fail(TBK_ERR_CUDA, "device-to-host copy: %s", cudaGetErrorString(e)); break; }
+    done += n;
+  }
+  for (int i = 0; i < 2; ++i) {
+    cudaError_t e = cudaStreamSynchronize(f->streams[i]);
+    if (e != cudaSuccess && rc == TBK_OK) rc = fail(TBK_ERR_CUDA, "cudaStreamSynchronize: %s", cudaGetErrorString(e));
+  }
+  f->timing = was_timing;
+  if (rc != TBK_OK) return rc;
+  if (!out_pinned) std::memcpy(h_out, f->h_res, (size_t)n_rows * out_elt);
+  return check_status(f);
+}
+
+int tbk_set_timing(tbk_forest *f, int32_t enable) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  f->timing = enable != 0;
+  f->ev_pending = false;
+  return TBK_OK;
+}
+
+int64_t tbk_last_kernel_time_us(tbk_forest *f) {
+  if (!f || !f->ev_pending) return -1;
+  if (cudaEventSynchronize(f->ev1) != cudaSuccess) return -1;
+  float ms = 0.f;
+  if (cudaEventElapsedTime(&ms, f->ev0, f->ev1) != cudaSuccess) return -1;
+  return (int64_t)(ms * 1000.0f + 0.5f);
+}
+
+int64_t tbk_launch_count(const tbk_forest *f) { return f ? f->launches : 0; }
+
+int tbk_check_status(tbk_forest *f) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  return check_status(f);
+}
+
+} // extern "C"
+
+// ---------------------------------------------------------------------------
+// Host-only utilities (no device is touched).
+
+extern "C" {
+
+int tbk_host_layout_check(const tbk_forest_arrays *fa, const tbk_schedule *schedule, const float *rows,
+                          int64_t n_rows, int64_t ld, int32_t *leaf_ids, float *sums,
+                          tbk_forest_info *info) {
+  if (!fa || fa->num_trees <= 0) return fail(TBK_ERR_INVALID, "null or empty forest");
+  tb::Forest host;
+  const int64_t T = fa->num_trees, N = fa->tree_off[T];
+  host.tree_off.assign(fa->tree_off, fa->tree_off + T + 1);
+  host.left.assign(fa->left, fa->left + N);
+  host.right.assign(fa->right, fa->right + N);
+  host.feat.assign(fa->feat, fa->feat + N);
+  host.thr.assign(fa->thr, fa->thr + N);
+  if (fa->num_classes > 0 && fa->class_id) host.class_id.assign(fa->class_id, fa->class_id + T);
+  host.num_classes = fa->num_classes;
+  host.transform = fa->transform;
+  host.initial_value = fa->initial_value;
+  host.num_features = fa->num_features;
+  tb::PackOptions opt;
+  opt.representation = schedule ? schedule->representation : 0;
+  opt.tile_size = schedule && schedule->tile_size > 0 ? schedule->tile_size : 1;
+  tb::PackedForest packed;
+  std::string err = tb::pack_forest(host, opt, &packed);
+  if (!err.empty()) return fail(TBK_ERR_INVALID, "%s", err.c_str());
+  if (info) {
+    std::memset(info, 0, sizeof *info);
+    info->num_trees = packed.num_trees;
+    info->num_nodes = packed.num_nodes;
+    info->num_groups = (int64_t)packed.groups.size();
+    info->packed_bytes = (int64_t)packed.blob.size();
+    info->max_depth = packed.max_depth;
+    info->num_features = packed.num_features;
+    info->num_classes = packed.num_classes;
+    info->transform = packed.transform;
+    info->schedule.representation = packed.representation;
+    info->schedule.tile_size = packed.tile_size;
+    info->reserved[0] = packed.num_shapes;
+    info->reserved[1] = (int32_t)packed.lut.size();
+    info->reserved[2] = (int32_t)std::min<uint64_t>(packed.max_group_bytes, 0x7fffffff);
+  }
+  if (rows && n_rows > 0) tb::walk_packed_on_host(packed, rows, n_rows, ld, leaf_ids, sums);
+  return TBK_OK;
+}
+
+int tbk_plan_launch(int32_t num_features, int32_t num_classes, int64_t num_groups, int64_t max_group_bytes,
+                    int32_t lut_bytes, const tbk_schedule *schedule, int64_t n_rows, int32_t smem_limit,
+                    int32_t num_sms, tbk_forest_info *info) {
+  if (!info) return fail(TBK_ERR_INVALID, "null argument");
+  tbk_schedule user{};
+  if (schedule) user = *schedule;
+  tb::ForestShape shape{num_features, num_classes, num_groups, (uint64_t)max_group_bytes, lut_bytes,
+                        user.representation, user.tile_size > 0 ? user.tile_size : 1};
+  tb::LaunchPlan pl;
+  std::string why = tb::select_launch(shape, user, n_rows, smem_limit, num_sms, false, &pl);
+  if (!why.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", why.c_str());
+  std::memset(info, 0, sizeof *info);
+  info->schedule = user;
+  info->schedule.rows_per_block = pl.row_warps * 32 * pl.rows_per_lane;
+  info->schedule.rows_per_thread = pl.rows_per_lane;
+  info->schedule.tree_threads = pl.tree_threads;
+  info->schedule.tree_chunks = pl.chunks;
+  info->schedule.cache_trees = pl.staged ? 1 : 2;
+  info->staged = pl.staged;
+  info->smem_bytes = pl.smem_bytes;
+  info->threads_per_block = pl.threads;
+  info->reserved[0] = pl.cache_rows;
+  info->reserved[1] = (int32_t)std::min<int64_t>(pl.grid_x, 0x7fffffff);
+  info->reserved[2] = pl.groups_per_chunk;
+  return TBK_OK;
+}
+
+} // extern "C"
