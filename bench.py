@@ -315,8 +315,9 @@ def main():
                "d2h_bytes_per_step": n_rows * (1 if int8 else 4),
                "steps": reps, "ms_per_step": float(dt.item()) * 1e3,
                "via": "tbk_predict_host (chunked H2D / walk / D2H on two streams)"}
-        same = np.array_equal(rout[:4096], out[:4096].cpu().numpy())
-        e2e["matches_device_path"] = bool(same)
+        # chunked launches may group trees differently: same leaves, fp32 sums within rounding
+        e2e["max_abs_diff_vs_device_path"] = float(np.abs(
+            rout[:4096].astype(np.float64) - out[:4096].float().cpu().numpy()).max())
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

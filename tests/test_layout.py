@@ -1,0 +1,102 @@
+"""Forest-to-buffer lowering, checked on the host: the packed buffers are interpreted on
+the CPU with the kernels' slot arithmetic and must select exactly the leaves the oracle
+selects, for every representation and tile size."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests.helpers import SMALL, small_config
+from treebeard_b200 import kernels, synth
+
+REPS = [("sparse", 1), ("sparse", 2), ("sparse", 3), ("sparse", 4), ("array", 1), ("array", 2),
+        ("array", 3), ("array", 4), ("reorg", 1)]
+
+
+@pytest.mark.parametrize("name", list(SMALL))
+@pytest.mark.parametrize("rep,ts", REPS)
+def test_packed_layout_selects_oracle_leaves(name, rep, ts):
+    if name == "c5" and rep == "array" and ts > 1:
+        pytest.skip("array layout of deep unbalanced trees is too large by construction")
+    forest, X = small_config(name, rows=200)
+    _, want_ids, class_sums = oracle.predict(forest, X, leaf_ids=True, class_sums=True)
+    ids, sums, info = kernels.host_layout_check(forest, X, representation=rep, tile_size=ts)
+    assert np.array_equal(ids, want_ids)
+    g = forest.tree_off[:-1][None, :] + want_ids
+    if forest.num_classes == 0:
+        want = forest.thr[g].astype(np.float64).sum(axis=1)
+        assert np.allclose(sums[:, 0], want, rtol=1e-5, atol=1e-5)
+    else:
+        assert np.allclose(sums, class_sums - forest.initial_value, rtol=1e-5, atol=1e-5)
+    assert info.num_groups == (forest.num_trees + 15) // 16
+
+
+@pytest.mark.parametrize("ts,shapes", [(1, 1), (2, 3), (3, 8), (4, 22)])
+def test_tile_shape_count_is_the_catalan_sum(ts, shapes):
+    forest, _ = small_config("c1", rows=1)
+    _, _, info = kernels.host_layout_check(forest, None, representation="sparse", tile_size=ts)
+    # + 1: the leaf tile's own shape
+    assert info.reserved[0] == shapes + 1
+    assert info.reserved[1] == (shapes + 1) << ts
+
+
+def _tiny(left, right, feat, thr, F=3):
+    n = len(left)
+    return synth.ForestArrays(np.array([0, n], np.int64), np.array(left, np.int32),
+                              np.array(right, np.int32), np.array(feat, np.int32),
+                              np.array(thr, np.float32), np.zeros(1, np.int32), 0, 0, 0.0, F)
+
+
+def test_hand_trees_every_outcome():
+    # left-heavy chain, right-heavy chain and a balanced tree, all outcomes enumerated
+    chains = [
+        _tiny([1, 3, -1, 5, -1, -1, -1], [2, 4, -1, 6, -1, -1, -1], [0, 1, 0, 2, 0, 0, 0],
+              [0.5, 0.5, 10, 0.5, 20, 30, 40]),
+        _tiny([1, -1, 3, -1, 5, -1, -1], [2, -1, 4, -1, 6, -1, -1], [0, 0, 1, 0, 2, 0, 0],
+              [0.5, 10, 0.5, 20, 0.5, 30, 40]),
+        _tiny([1, 3, 5, -1, -1, -1, -1], [2, 4, 6, -1, -1, -1, -1], [0, 1, 2, 0, 0, 0, 0],
+              [0.5, 0.5, 0.5, 1, 2, 3, 4]),
+    ]
+    X = np.array([[a, b, c] for a in (0.0, 0.5, 1.0) for b in (0.0, 0.5, 1.0) for c in (0.0, 0.5, 1.0)],
+                 np.float32)
+    for forest in chains:
+        _, want = oracle.predict(forest, X, leaf_ids=True)
+        for rep, ts in REPS:
+            ids, _, _ = kernels.host_layout_check(forest, X, representation=rep, tile_size=ts)
+            assert np.array_equal(ids, want), (rep, ts)
+
+
+def test_single_leaf_tree_and_filler_columns():
+    forest = synth.ForestArrays(np.array([0, 1, 4], np.int64), np.array([-1, 1, -1, -1], np.int32),
+                                np.array([-1, 2, -1, -1], np.int32), np.array([0, 1, 0, 0], np.int32),
+                                np.array([7.0, 0.0, -1.0, 1.0], np.float32), np.zeros(2, np.int32),
+                                0, 0, 0.0, 2)
+    X = np.array([[0, -1], [0, 0], [0, 1]], np.float32)
+    for rep, ts in REPS:
+        ids, sums, _ = kernels.host_layout_check(forest, X, representation=rep, tile_size=ts)
+        assert ids.tolist() == [[0, 1], [0, 2], [0, 2]]
+        assert sums[:, 0].tolist() == [6.0, 8.0, 8.0]
+
+
+@pytest.mark.parametrize("breakage", ["one_child", "bad_child", "bad_feature", "two_parents", "nan",
+                                      "neg_inf_leaf", "reorg_tiled", "tile_too_big"])
+def test_malformed_forests_are_rejected(breakage):
+    forest = _tiny([1, -1, -1], [2, -1, -1], [0, 0, 0], [0.5, 1, 2])
+    kw = dict(representation="sparse", tile_size=1)
+    if breakage == "one_child":
+        forest.right[0] = -1
+    elif breakage == "bad_child":
+        forest.left[0] = 9
+    elif breakage == "bad_feature":
+        forest.feat[0] = 3
+    elif breakage == "two_parents":
+        forest.right[0] = 1
+    elif breakage == "nan":
+        forest.thr[0] = np.nan
+    elif breakage == "neg_inf_leaf":
+        forest.thr[1] = -np.inf
+    elif breakage == "reorg_tiled":
+        kw = dict(representation="reorg", tile_size=2)
+    elif breakage == "tile_too_big":
+        kw = dict(representation="sparse", tile_size=5)
+    with pytest.raises(kernels.TbkError):
+        kernels.host_layout_check(forest, None, **kw)
