@@ -212,8 +212,6 @@ def main():
 
     forest, marg, n_rows = synth.make_config(args.workload, trees=args.trees, rows=args.rows)
     rep = args.representation
-    if rep == "auto":
-        rep = "sparse"
     tree_sharded = world > 1 and args.shard == "trees"
     my_forest = forest
     if tree_sharded:

@@ -39,7 +39,7 @@ enum { TBK_IDENTITY = 0, TBK_SIGMOID = 1, TBK_SOFTMAX = 2 };
 /* packed-forest representations
  * (factory names in src/mlir/Representations.h:364-380 and
  *  src/gpu/GPURepresentations.cpp:1238,1982, src/gpu/ReorgForestRepresentation.cpp:390) */
-enum { TBK_REP_SPARSE = 0, TBK_REP_ARRAY = 1, TBK_REP_REORG = 2 };
+enum { TBK_REP_AUTO = -1, TBK_REP_SPARSE = 0, TBK_REP_ARRAY = 1, TBK_REP_REORG = 2 };
 
 /* output element kinds: fp32 prediction, or int8 class id for a multiclass forest
  * (the reference's multiclass return type, test/python/gpu_tests.py:133-136) */
@@ -72,7 +72,7 @@ typedef struct tbk_forest_arrays {
  * A zero in any field means "let the selector choose".
  */
 typedef struct tbk_schedule {
-  int32_t representation;  /* TBK_REP_* */
+  int32_t representation;  /* TBK_REP_*; TBK_REP_AUTO lets the selector choose */
   int32_t tile_size;       /* nodes per tile, 1..4 (0 = 1) */
   int32_t rows_per_block;  /* numRowsPerTB */
   int32_t rows_per_thread; /* numRowsPerThread: rows walked in lock-step by a lane */
@@ -83,7 +83,12 @@ typedef struct tbk_schedule {
   int32_t cache_trees;     /* 1 = stage tree groups in shared memory with bulk
                               async copies, 2 = read nodes from global memory,
                               0 = auto */
-  int32_t reserved[5];
+  int32_t feature_bits;    /* how rows are staged in shared memory: 32 = fp32 values,
+                              16 = order-preserving 16-bit keys with exact fp32 tie
+                              resolution (reorg layout, single-output forests, at most 8
+                              levels; meant for rows too wide for an fp32 tile),
+                              0 = auto */
+  int32_t reserved[4];
 } tbk_schedule;
 
 typedef struct tbk_forest tbk_forest; /* opaque: packed forest resident on a device */

@@ -196,3 +196,54 @@ def test_kernel_timing_api(tmp_path):
     finally:
         treebeard.SetEnableMeasureGpuKernelTime(False)
         treebeard.SetNumberOfKernelRuns(1)
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3"])
+def test_sixteen_bit_key_kernel_is_exact(name):
+    """The wide-row kernel (rows staged as 16-bit keys) must select exactly the oracle's
+    leaves, ties, NaN and infinities included."""
+    from treebeard_b200 import kernels
+    forest, X = small_config(name)
+    X = X.copy()
+    split = np.nonzero(forest.left >= 0)[0]
+    for i in range(600):
+        g = split[(i * 37) % len(split)]
+        X[i % len(X), forest.feat[g]] = forest.thr[g]
+    X[3, :] = np.nan
+    X[4, 0] = np.inf
+    X[5, 1] = -np.inf
+    want, want_ids = oracle.predict(forest, X, leaf_ids=True)
+    df = kernels.DeviceForest(forest, representation="reorg", feature_bits=16, batch_hint=len(X))
+    info = df.info()
+    assert info.schedule.feature_bits == 16 and info.threads_per_block == 1024
+    dX = _dev(X)
+    ids = df.predict_leaf_ids(dX).cpu().numpy()
+    df.check_status()
+    assert np.array_equal(ids, want_ids), f"{(ids != want_ids).sum()} leaf ids differ"
+    got = df.predict(dX).cpu().numpy()
+    df.check_status()
+    ok = ~np.isnan(want)
+    assert_predictions_close(got[ok], want[ok])
+    assert df.info().reserved[0] > 0          # key ties were hit and resolved exactly
+    # partial sums + second pass, ragged batch, unaligned rows
+    part = df.predict_partial(dX[:777])
+    again = df.finalize(part).cpu().numpy()
+    assert_predictions_close(again[ok[:777]], want[:777][ok[:777]])
+    wide = torch.zeros((len(X), forest.num_features + 1), device="cuda")
+    wide[:, :forest.num_features] = dX
+    got2 = df.predict(wide[:, :forest.num_features]).cpu().numpy()
+    assert np.array_equal(got2[ok], got[ok])
+
+
+def test_auto_representation_picks_keys_for_wide_rows_only():
+    from treebeard_b200 import kernels
+    wide, Xw = small_config("c3", rows=64)
+    narrow, Xn = small_config("c2", rows=64)
+    a = kernels.DeviceForest(wide, representation="auto")
+    b = kernels.DeviceForest(narrow, representation="auto")
+    assert a.info().schedule.feature_bits == 16
+    assert b.info().schedule.feature_bits == 32
+    assert_predictions_close(a.predict(_dev(Xw)).cpu().numpy(), oracle.predict(wide, Xw))
+    with pytest.raises(kernels.TbkError):
+        deep, _ = small_config("c5", rows=1)
+        kernels.DeviceForest(deep, representation="reorg", feature_bits=16)

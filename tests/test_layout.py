@@ -100,3 +100,33 @@ def test_malformed_forests_are_rejected(breakage):
         kw = dict(representation="sparse", tile_size=5)
     with pytest.raises(kernels.TbkError):
         kernels.host_layout_check(forest, None, **kw)
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3"])
+def test_sixteen_bit_key_layout_is_exact_including_ties(name):
+    """Wide-row layout: rows as order-preserving 16-bit keys.  Key ties (forced here by
+    copying thresholds into the rows), NaN and infinities must still select the oracle's
+    leaves, because ties are decided on the exact fp32 values."""
+    forest, X = small_config(name, rows=400)
+    X = X.copy()
+    split = np.nonzero(forest.left >= 0)[0]
+    for i in range(300):
+        g = split[(i * 37) % len(split)]
+        X[i % len(X), forest.feat[g]] = forest.thr[g]
+    X[3, :] = np.nan
+    X[4, 0] = np.inf
+    X[5, 1] = -np.inf
+    _, want = oracle.predict(forest, X, leaf_ids=True)
+    ids, sums, info = kernels.host_layout_check(forest, X, representation="reorg", feature_bits=16)
+    assert np.array_equal(ids, want)
+    assert info.schedule.feature_bits == 16 and info.reserved[0] >= 5   # ties were exercised
+    assert info.num_groups == (forest.num_trees + 31) // 32
+
+
+def test_sixteen_bit_keys_refuse_what_they_cannot_hold():
+    deep, _ = small_config("c5", rows=1)        # 12 levels: planes would not fit a stage
+    with pytest.raises(kernels.TbkError, match="deeper"):
+        kernels.host_layout_check(deep, None, representation="reorg", feature_bits=16)
+    multi, _ = small_config("c4", rows=1)
+    with pytest.raises(kernels.TbkError, match="single-output"):
+        kernels.host_layout_check(multi, None, representation="reorg", feature_bits=16)

@@ -1,0 +1,144 @@
+#include "quant_pack.h"
+
+#include <algorithm>
+#include <limits>
+#include <numeric>
+
+namespace tb {
+
+std::string pack_quant(const Forest &f, QuantForest *out) {
+  std::string err = validate(f);
+  if (!err.empty()) return err;
+  if (f.num_classes > 0) return "16-bit feature keys are implemented for single-output forests only";
+  if (f.num_features > 65534) return "more than 65534 features";
+  const int64_t T = f.num_trees();
+  const int F = f.num_features;
+
+  QuantForest &q = *out;
+  q = QuantForest();
+  q.num_features = F;
+  q.transform = f.transform;
+  q.initial_value = f.initial_value;
+  q.num_trees = T;
+  q.num_nodes = f.num_nodes();
+
+  std::vector<float> lo(F + 1, std::numeric_limits<float>::infinity());
+  std::vector<float> hi(F + 1, -std::numeric_limits<float>::infinity());
+  for (int64_t g = 0; g < f.num_nodes(); ++g) {
+    if (!std::isfinite(f.thr[g])) return "non-finite threshold or leaf value";
+    if (f.is_leaf(g)) continue;
+    lo[f.feat[g]] = std::min(lo[f.feat[g]], f.thr[g]);
+    hi[f.feat[g]] = std::max(hi[f.feat[g]], f.thr[g]);
+  }
+  q.lo.assign(F + 1, 0.f);
+  q.scale.assign(F + 1, 0.f);
+  for (int i = 0; i < F; ++i) {
+    if (!(hi[i] >= lo[i])) continue; // feature not used by any split
+    q.lo[i] = lo[i];
+    // a single threshold needs no range: any huge slope separates everything but x == t
+    // 65531 (not 65532) keeps the key of the largest threshold at >= 1 under rounding, so
+    // that it never ties with the saturated key 0 of everything above it
+    float s = hi[i] > lo[i] ? 65531.0f / (hi[i] - lo[i]) : 0x1p40f;
+    if (!std::isfinite(s) || s <= 0.f) s = 0x1p40f;
+    q.scale[i] = s;
+  }
+
+  std::vector<int32_t> depth(T);
+  for (int64_t t = 0; t < T; ++t) {
+    depth[t] = tree_depth(f, t);
+    q.max_depth = std::max(q.max_depth, depth[t]);
+  }
+  if (q.max_depth > kQuantMaxDepth)
+    return "trees deeper than " + std::to_string(kQuantMaxDepth) + " levels do not fit the key layout's stages";
+  std::vector<int64_t> order(T);
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return depth[a] < depth[b]; });
+
+  const int64_t G = (T + kQuantCols - 1) / kQuantCols;
+  q.groups.resize(G);
+  q.tree_index.assign(G * kQuantCols, -1);
+  uint64_t elems = 0;
+  for (int64_t g = 0; g < G; ++g) {
+    uint32_t d = 0;
+    for (int c = 0; c < kQuantCols && g * kQuantCols + c < T; ++c)
+      d = std::max<uint32_t>(d, depth[order[g * kQuantCols + c]]);
+    q.groups[g] = QuantGroup{elems, d, 1u << d};
+    elems += (uint64_t)(1u << d) * kQuantCols;
+  }
+  const uint32_t pass_through = (uint32_t)F << 16; // sentinel feature, key 0: always left
+  q.node_plane.assign(elems, pass_through);
+  q.leaf_plane.assign(elems, 0.f);
+  q.exact_plane.assign(elems, 0.f);
+  q.orig_leaf.assign(elems, -1);
+
+  for (int64_t g = 0; g < G; ++g) {
+    const QuantGroup &gm = q.groups[g];
+    for (int c = 0; c < kQuantCols; ++c) {
+      const int64_t k = g * kQuantCols + c;
+      if (k >= T) break;
+      const int64_t t = order[k], a = f.tree_off[t];
+      q.tree_index[k] = (int32_t)t;
+      struct Item { int32_t node; uint32_t slot, level; };
+      std::vector<Item> stack{{0, 0, 0}};
+      while (!stack.empty()) {
+        const Item it = stack.back();
+        stack.pop_back();
+        if (f.left[a + it.node] < 0) {
+          // leftmost descendant on the bottom level holds the value
+          const uint64_t bottom = ((uint64_t)it.slot + 1) * (1ull << (gm.depth - it.level)) - 1;
+          const uint64_t leaf = bottom - (gm.slots - 1);
+          q.leaf_plane[gm.elem_off + leaf * kQuantCols + c] = f.thr[a + it.node];
+          q.orig_leaf[gm.elem_off + leaf * kQuantCols + c] = it.node;
+          continue;
+        }
+        const int32_t ft = f.feat[a + it.node];
+        const float thr = f.thr[a + it.node];
+        const uint64_t e = gm.elem_off + (uint64_t)it.slot * kQuantCols + c;
+        q.node_plane[e] = ((uint32_t)ft << 16) | quant_key(thr, q.lo[ft], q.scale[ft]);
+        q.exact_plane[e] = thr;
+        stack.push_back({f.left[a + it.node], 2 * it.slot + 1, it.level + 1});
+        stack.push_back({f.right[a + it.node], 2 * it.slot + 2, it.level + 1});
+      }
+    }
+  }
+  return "";
+}
+
+void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows, int64_t ld,
+                        int32_t *leaf_ids, float *sums, int64_t *ties) {
+  int64_t tie_count = 0;
+  const int F = q.num_features;
+  std::vector<uint16_t> keys(F + 1);
+  for (int64_t r = 0; r < n_rows; ++r) {
+    const float *row = rows + r * ld;
+    for (int i = 0; i < F; ++i) keys[i] = quant_key(row[i], q.lo[i], q.scale[i]);
+    keys[F] = 65535;
+    float acc = 0.f;
+    for (size_t g = 0; g < q.groups.size(); ++g) {
+      const QuantGroup &gm = q.groups[g];
+      for (int c = 0; c < kQuantCols; ++c) {
+        const int32_t t = q.tree_index[g * kQuantCols + c];
+        if (t < 0) continue;
+        uint32_t n = 0;
+        for (uint32_t d = 0; d < gm.depth; ++d) {
+          const uint64_t e = gm.elem_off + (uint64_t)n * kQuantCols + c;
+          const uint32_t node = q.node_plane[e];
+          const uint32_t ft = node >> 16, kt = node & 0xffffu, kx = keys[ft];
+          bool right = kx < kt;
+          if (kx == kt) {
+            ++tie_count;
+            right = !(row[ft] < q.exact_plane[e]);
+          }
+          n = 2 * n + 1 + (right ? 1 : 0);
+        }
+        const uint64_t e = gm.elem_off + (uint64_t)(n - (gm.slots - 1)) * kQuantCols + c;
+        acc += q.leaf_plane[e];
+        if (leaf_ids) leaf_ids[r * q.num_trees + t] = q.orig_leaf[e];
+      }
+    }
+    if (sums) sums[r] = acc;
+  }
+  if (ties) *ties = tie_count;
+}
+
+} // namespace tb

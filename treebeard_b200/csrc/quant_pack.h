@@ -1,0 +1,77 @@
+// "Reorg with 16-bit feature keys": the packed layout for forests over WIDE rows.
+//
+// When a row is so wide that a 32-row fp32 tile does not fit in shared memory (the
+// reference simply stops caching rows beyond 1500 features,
+// src/mlir/GPUAutoSchedule.cpp:803-806, and walks from global memory), rows are staged
+// as 16-bit ORDER-PRESERVING KEYS instead, which halves the tile, and nodes shrink to
+// 4 bytes.  The layout is the reorg idea (src/gpu/ReorgForestRepresentation.cpp:186-275:
+// node-major planes, every tree padded to a complete tree, implicit children 2n+1+k)
+// per group of 32 trees:
+//
+//   node plane   u32 [2^D slots][32 columns]   (feature index << 16) | threshold key
+//   leaf plane   f32 [2^D slots][32 columns]   leaf values
+//   exact plane  f32 [2^D slots][32 columns]   fp32 thresholds (global memory only)
+//
+// Keys.  For feature f with thresholds in [lo_f, hi_f]:
+//     key(v) = sat_u16( floor( fma(v - lo_f, -a_f, 65533) ) ),  a_f = 65531 / (hi_f - lo_f)
+// a non-increasing map (NaN -> 0, +inf -> 0, -inf -> 65535).  For a row value x and a
+// threshold t of the same feature:  key(x) > key(t)  =>  x < t  (left);
+// key(x) < key(t)  =>  x > t  (right);  equal keys decide nothing, and the kernel then
+// compares the exact fp32 values.  Leaf selection is therefore exactly that of the fp32
+// walk; only speed depends on how often keys tie.
+//
+// A leaf above the bottom level becomes a chain of pass-through nodes that name the
+// sentinel feature (index num_features, staged key 65535) with key 0: always left.
+#pragma once
+#include "forest.h"
+
+#include <cmath>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+namespace tb {
+
+constexpr int kQuantCols = 32;
+constexpr int kQuantMaxDepth = 8; // pieces of at most 2^8 * 128 B = 32 KB
+
+struct QuantGroup {
+  uint64_t elem_off; // offset of the group's planes, in elements (same for all planes)
+  uint32_t depth;    // decision levels; planes have 2^depth slots
+  uint32_t slots;    // 2^depth
+};
+
+struct QuantForest {
+  int32_t num_features = 0, transform = 0;
+  double initial_value = 0.0;
+  int64_t num_trees = 0, num_nodes = 0;
+  int32_t max_depth = 0;
+  std::vector<QuantGroup> groups;
+  std::vector<uint32_t> node_plane; // key field is filled on the device at upload
+  std::vector<float> leaf_plane;
+  std::vector<float> exact_plane;
+  std::vector<int32_t> orig_leaf;   // original node id per leaf-plane element
+  std::vector<int32_t> tree_index;  // [groups*32] original tree index, -1 = filler
+  std::vector<float> lo, scale;     // per feature (+ sentinel entry)
+};
+
+// host restatement of the key function (the device computes keys with the same
+// arithmetic: one subtraction, one fused multiply-add, one floor-and-saturate)
+inline uint16_t quant_key(float v, float lo, float scale) {
+  const float y = std::fmaf(v - lo, -scale, 65533.0f);
+  if (std::isnan(y)) return 0;
+  const float fl = std::floor(y);
+  if (fl <= 0.0f) return 0;
+  if (fl >= 65535.0f) return 65535;
+  return (uint16_t)fl;
+}
+
+// Empty string on success.  Fails (so that the caller can fall back to another layout)
+// for multiclass forests, trees deeper than kQuantMaxDepth, or non-finite thresholds.
+std::string pack_quant(const Forest &f, QuantForest *out);
+
+// Host interpreter of the packed planes (layout verification only).
+void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows, int64_t ld,
+                        int32_t *leaf_ids, float *sums, int64_t *ties);
+
+} // namespace tb

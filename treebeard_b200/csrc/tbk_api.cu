@@ -2,8 +2,10 @@
 // selection, kernel dispatch, the second pass, and the host-buffer pipeline.
 #include "../../include/tbk.h"
 #include "pack.h"
+#include "quant_pack.h"
 #include "schedule.h"
 #include "walk_kernels.cuh"
+#include "walk_quant.cuh"
 
 #include <algorithm>
 #include <cstdarg>
@@ -56,6 +58,14 @@ struct tbk_forest {
   int32_t *d_status = nullptr;
   float *d_scratch = nullptr; // tree-chunk partials
   size_t scratch_bytes = 0;
+  // 16-bit-key layout (wide rows)
+  bool quant = false;
+  tb::QuantForest qf;
+  uint32_t *d_qnode = nullptr;
+  float *d_qleaf = nullptr, *d_qexact = nullptr, *d_qlo = nullptr, *d_qscale = nullptr;
+  tb::DevQuantGroup *d_qgroups = nullptr;
+  int32_t *d_qtree_index = nullptr, *d_qorig = nullptr;
+  unsigned long long *d_ties = nullptr;
   // host pipeline
   float *d_in[2] = {nullptr, nullptr};
   unsigned char *d_res[2] = {nullptr, nullptr};
@@ -122,6 +132,95 @@ int ensure_orig(tbk_forest *f) {
 
 enum Mode { kPredict, kPartial, kLeafIds };
 
+int quant_smem_bytes(int num_features) { return 128 + 3 * tb::kQStage + (num_features + 1) * 64; }
+
+// One prediction with the 16-bit-key kernel (one block per 32 rows, 32 warps).
+int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
+              float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot) {
+  const auto &q = f->qf;
+  const int64_t G = (int64_t)q.groups.size();
+  const int64_t grid_x = (n_rows + 31) / 32;
+  int64_t chunks = 1;
+  if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
+  else if (grid_x < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + grid_x - 1) / grid_x;
+  chunks = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(chunks, G), 65535));
+  const int gpc = (int)((G + chunks - 1) / chunks);
+  chunks = (G + gpc - 1) / gpc;
+  tb::LaunchPlan plan;
+  plan.row_warps = 1;
+  plan.tree_threads = 32;
+  plan.rows_per_lane = 1;
+  plan.chunks = (int32_t)chunks;
+  plan.groups_per_chunk = gpc;
+  plan.staged = 1;
+  plan.cache_rows = 1;
+  plan.stage_bytes = tb::kQStage;
+  plan.smem_bytes = quant_smem_bytes(q.num_features);
+  plan.threads = 1024;
+  plan.grid_x = grid_x;
+  f->last_plan = plan;
+
+  const bool need_partials = mode == kPartial || (mode == kPredict && chunks > 1);
+  float *partial_dst = nullptr;
+  if (need_partials) {
+    if (mode == kPartial && chunks == 1) {
+      partial_dst = d_partial;
+    } else {
+      const size_t need = ((size_t)chunks * n_rows * sizeof(float) + 255) & ~(size_t)255;
+      int rc = ensure_scratch(f, 2 * need);
+      if (rc) return rc;
+      partial_dst = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(f->d_scratch) + (size_t)slot * (f->scratch_bytes / 2));
+    }
+  }
+  tb::QuantParams p{};
+  p.node_plane = f->d_qnode;
+  p.leaf_plane = f->d_qleaf;
+  p.exact_plane = f->d_qexact;
+  p.groups = f->d_qgroups;
+  p.tree_index = f->d_qtree_index;
+  p.orig_leaf = f->d_qorig;
+  p.lo = f->d_qlo;
+  p.scale = f->d_qscale;
+  p.rows = d_rows;
+  p.n_rows = n_rows;
+  p.ld = ld;
+  p.partial = partial_dst;
+  p.out = d_out;
+  p.write_partial = need_partials ? 1 : 0;
+  p.leaf_ids = mode == kLeafIds ? d_leaf_ids : nullptr;
+  p.num_trees = q.num_trees;
+  p.num_groups = (int32_t)G;
+  p.groups_per_chunk = gpc;
+  p.num_features = q.num_features;
+  p.transform = q.transform;
+  p.initial_value = (float)q.initial_value;
+  p.vec4_ok = (q.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
+  p.status = f->d_status;
+  p.tie_count = f->d_ties;
+  CUDA_TRY(cudaFuncSetAttribute((const void *)tb::tb_walk_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
+  if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
+  dim3 grid((unsigned)grid_x, (unsigned)chunks);
+  tb::tb_walk_quant_kernel<<<grid, 1024, plan.smem_bytes, stream>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  ++f->launches;
+  const int tpb = 256;
+  if (mode == kPredict && chunks > 1) {
+    tb::tb_finalize_kernel<<<(unsigned)((n_rows + tpb - 1) / tpb), tpb, 0, stream>>>(
+        partial_dst, (int)chunks, n_rows, 1, 0, (float)q.initial_value, q.transform, d_out, TBK_OUT_F32);
+    CUDA_TRY(cudaGetLastError());
+    ++f->launches;
+  } else if (mode == kPartial && chunks > 1) {
+    tb::tb_sum_partials_kernel<<<(unsigned)((n_rows + tpb - 1) / tpb), tpb, 0, stream>>>(partial_dst, (int)chunks, n_rows, d_partial);
+    CUDA_TRY(cudaGetLastError());
+    ++f->launches;
+  }
+  if (f->timing) {
+    CUDA_TRY(cudaEventRecord(f->ev1, stream));
+    f->ev_pending = true;
+  }
+  return TBK_OK;
+}
+
 // One prediction over device-resident rows.
 int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
         int32_t out_kind, float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot = 0) {
@@ -135,6 +234,7 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
     if (out_kind != TBK_OUT_F32 && out_kind != TBK_OUT_I8) return fail(TBK_ERR_INVALID, "unknown output kind %d", out_kind);
   }
   CUDA_TRY(cudaSetDevice(f->device));
+  if (f->quant) return run_quant(f, mode, d_rows, n_rows, ld, d_out, d_partial, d_leaf_ids, stream, slot);
 
   tb::ForestShape shape{pk.num_features, pk.num_classes, (int64_t)pk.groups.size(), pk.max_group_bytes,
                         (int32_t)pk.lut.size(), pk.representation, pk.tile_size};
@@ -275,15 +375,6 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
   if (schedule) f->user = *schedule;
   f->batch_hint = batch_hint;
   f->device = device;
-  tb::PackOptions opt;
-  opt.representation = f->user.representation;
-  opt.tile_size = f->user.tile_size <= 0 ? 1 : f->user.tile_size;
-  std::string err = tb::pack_forest(host, opt, &f->packed);
-  if (!err.empty()) {
-    delete f;
-    return fail(TBK_ERR_INVALID, "%s", err.c_str());
-  }
-  const auto &p = f->packed;
   auto bail = [&](int rc) {
     tbk_forest_free(f);
     return rc;
@@ -297,6 +388,93 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
   CUDA_TRY_F(cudaSetDevice(device));
   CUDA_TRY_F(cudaDeviceGetAttribute(&f->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
   CUDA_TRY_F(cudaDeviceGetAttribute(&f->num_sms, cudaDevAttrMultiProcessorCount, device));
+  CUDA_TRY_F(cudaMalloc(&f->d_status, 4));
+  CUDA_TRY_F(cudaMemset(f->d_status, 0, 4));
+  CUDA_TRY_F(cudaEventCreate(&f->ev0));
+  CUDA_TRY_F(cudaEventCreate(&f->ev1));
+
+  // ---- choose the layout
+  const int bits = f->user.feature_bits;
+  if (bits != 0 && bits != 16 && bits != 32) return bail(fail(TBK_ERR_INVALID, "feature_bits must be 0, 16 or 32"));
+  int rep = f->user.representation;
+  const int ts = f->user.tile_size <= 0 ? 1 : f->user.tile_size;
+  // an fp32 tile of 32 rows (plus the sentinel column) must fit beside a little metadata
+  const bool fp32_tile_fits = (int64_t)(host.num_features + 1) * 128 + 1024 <= f->max_smem_optin;
+  bool want_quant = bits == 16 ||
+                    (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits);
+  if (want_quant) {
+    std::string qerr = tb::pack_quant(host, &f->qf);
+    if (qerr.empty() && quant_smem_bytes(host.num_features) > f->max_smem_optin)
+      qerr = "rows are too wide for the 16-bit key tile";
+    if (!qerr.empty()) {
+      if (bits == 16) return bail(fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str()));
+      want_quant = false;
+      f->qf = tb::QuantForest();
+    }
+  }
+  if (rep == TBK_REP_AUTO) rep = TBK_REP_SPARSE;
+  if (want_quant) {
+    const auto &q = f->qf;
+    f->quant = true;
+    f->user.representation = TBK_REP_REORG;
+    // metadata shared with the generic entry points
+    f->packed.representation = tb::kReorg;
+    f->packed.tile_size = 1;
+    f->packed.num_features = q.num_features;
+    f->packed.transform = q.transform;
+    f->packed.initial_value = q.initial_value;
+    f->packed.num_trees = q.num_trees;
+    f->packed.num_nodes = q.num_nodes;
+    f->packed.max_depth = q.max_depth;
+    const size_t n = q.node_plane.size();
+    static_assert(sizeof(tb::QuantGroup) == sizeof(tb::DevQuantGroup), "group metadata layout");
+    CUDA_TRY_F(cudaMalloc(&f->d_qnode, n * 4));
+    CUDA_TRY_F(cudaMalloc(&f->d_qleaf, n * 4));
+    CUDA_TRY_F(cudaMalloc(&f->d_qexact, n * 4));
+    CUDA_TRY_F(cudaMalloc(&f->d_qorig, n * 4));
+    CUDA_TRY_F(cudaMalloc(&f->d_qgroups, q.groups.size() * sizeof(tb::QuantGroup)));
+    CUDA_TRY_F(cudaMalloc(&f->d_qtree_index, q.tree_index.size() * 4));
+    // lo / scale are read with 16-byte loads: pad to a multiple of 4 entries
+    const size_t nf = ((size_t)q.num_features + 1 + 3) / 4 * 4;
+    CUDA_TRY_F(cudaMalloc(&f->d_qlo, nf * 4));
+    CUDA_TRY_F(cudaMalloc(&f->d_qscale, nf * 4));
+    CUDA_TRY_F(cudaMemset(f->d_qlo, 0, nf * 4));
+    CUDA_TRY_F(cudaMemset(f->d_qscale, 0, nf * 4));
+    CUDA_TRY_F(cudaMalloc(&f->d_ties, 8));
+    CUDA_TRY_F(cudaMemset(f->d_ties, 0, 8));
+    CUDA_TRY_F(cudaMemcpy(f->d_qnode, q.node_plane.data(), n * 4, cudaMemcpyHostToDevice));
+    CUDA_TRY_F(cudaMemcpy(f->d_qleaf, q.leaf_plane.data(), n * 4, cudaMemcpyHostToDevice));
+    CUDA_TRY_F(cudaMemcpy(f->d_qexact, q.exact_plane.data(), n * 4, cudaMemcpyHostToDevice));
+    CUDA_TRY_F(cudaMemcpy(f->d_qorig, q.orig_leaf.data(), n * 4, cudaMemcpyHostToDevice));
+    CUDA_TRY_F(cudaMemcpy(f->d_qgroups, q.groups.data(), q.groups.size() * sizeof(tb::QuantGroup), cudaMemcpyHostToDevice));
+    CUDA_TRY_F(cudaMemcpy(f->d_qtree_index, q.tree_index.data(), q.tree_index.size() * 4, cudaMemcpyHostToDevice));
+    CUDA_TRY_F(cudaMemcpy(f->d_qlo, q.lo.data(), q.lo.size() * 4, cudaMemcpyHostToDevice));
+    CUDA_TRY_F(cudaMemcpy(f->d_qscale, q.scale.data(), q.scale.size() * 4, cudaMemcpyHostToDevice));
+    // threshold keys come from the same device arithmetic that will quantise the rows
+    tb::tb_quant_fill_keys<<<(unsigned)((n + 255) / 256), 256>>>(f->d_qnode, f->d_qexact, f->d_qlo, f->d_qscale,
+                                                               (unsigned long long)n, q.num_features);
+    CUDA_TRY_F(cudaGetLastError());
+    CUDA_TRY_F(cudaDeviceSynchronize());
+    ++f->launches;
+    // host copies of the big planes are no longer needed
+    std::vector<uint32_t>().swap(f->qf.node_plane);
+    std::vector<float>().swap(f->qf.leaf_plane);
+    std::vector<float>().swap(f->qf.exact_plane);
+    std::vector<int32_t>().swap(f->qf.orig_leaf);
+    tb::LaunchPlan &pl = f->last_plan;
+    pl.row_warps = 1; pl.tree_threads = 32; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
+    pl.stage_bytes = tb::kQStage; pl.smem_bytes = quant_smem_bytes(q.num_features); pl.threads = 1024;
+    *out = f;
+    return TBK_OK;
+  }
+
+  tb::PackOptions opt;
+  opt.representation = rep;
+  opt.tile_size = ts;
+  f->user.representation = rep;
+  std::string err = tb::pack_forest(host, opt, &f->packed);
+  if (!err.empty()) return bail(fail(TBK_ERR_INVALID, "%s", err.c_str()));
+  const auto &p = f->packed;
   CUDA_TRY_F(cudaMalloc(&f->d_blob, std::max<size_t>(16, p.blob.size())));
   CUDA_TRY_F(cudaMemcpy(f->d_blob, p.blob.data(), p.blob.size(), cudaMemcpyHostToDevice));
   static_assert(sizeof(tb::GroupMeta) == sizeof(tb::DevGroupMeta), "group metadata layout");
@@ -308,10 +486,6 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
   CUDA_TRY_F(cudaMemcpy(f->d_tree_index, p.tree_index.data(), p.tree_index.size() * 4, cudaMemcpyHostToDevice));
   CUDA_TRY_F(cudaMalloc(&f->d_lut, std::max<size_t>(16, p.lut.size())));
   CUDA_TRY_F(cudaMemcpy(f->d_lut, p.lut.data(), p.lut.size(), cudaMemcpyHostToDevice));
-  CUDA_TRY_F(cudaMalloc(&f->d_status, 4));
-  CUDA_TRY_F(cudaMemset(f->d_status, 0, 4));
-  CUDA_TRY_F(cudaEventCreate(&f->ev0));
-  CUDA_TRY_F(cudaEventCreate(&f->ev1));
   // the packed blob is only needed on the device from here on
   std::vector<uint8_t>().swap(f->packed.blob);
   // settle the plan for the hinted batch so that get_info can report it
@@ -341,6 +515,15 @@ int tbk_forest_free(tbk_forest *f) {
   cudaFree(f->d_lut);
   cudaFree(f->d_status);
   cudaFree(f->d_scratch);
+  cudaFree(f->d_qnode);
+  cudaFree(f->d_qleaf);
+  cudaFree(f->d_qexact);
+  cudaFree(f->d_qorig);
+  cudaFree(f->d_qgroups);
+  cudaFree(f->d_qtree_index);
+  cudaFree(f->d_qlo);
+  cudaFree(f->d_qscale);
+  cudaFree(f->d_ties);
   if (f->ev0) cudaEventDestroy(f->ev0);
   if (f->ev1) cudaEventDestroy(f->ev1);
   delete f;
@@ -353,8 +536,9 @@ int tbk_forest_get_info(const tbk_forest *f, tbk_forest_info *info) {
   const auto &p = f->packed;
   info->num_trees = p.num_trees;
   info->num_nodes = p.num_nodes;
-  info->num_groups = (int64_t)p.groups.size();
-  info->packed_bytes = p.groups.empty() ? 0 : (int64_t)(p.groups.back().byte_off +
+  info->num_groups = f->quant ? (int64_t)f->qf.groups.size() : (int64_t)p.groups.size();
+  info->packed_bytes = f->quant ? (int64_t)(f->qf.groups.empty() ? 0 : 8 * (f->qf.groups.back().elem_off + (uint64_t)f->qf.groups.back().slots * tb::kQuantCols)) :
+                       p.groups.empty() ? 0 : (int64_t)(p.groups.back().byte_off +
       (((uint64_t)p.groups.back().slots * tb::kGroupTrees * p.tile_bytes + 15) & ~15ull));
   info->max_depth = p.max_depth;
   info->num_features = p.num_features;
@@ -369,9 +553,18 @@ int tbk_forest_get_info(const tbk_forest *f, tbk_forest_info *info) {
   info->schedule.tree_threads = pl.tree_threads;
   info->schedule.tree_chunks = pl.chunks;
   info->schedule.cache_trees = pl.staged ? 1 : 2;
+  info->schedule.feature_bits = f->quant ? 16 : 32;
   info->staged = pl.staged;
   info->smem_bytes = pl.smem_bytes;
   info->threads_per_block = pl.threads;
+  if (f->quant && f->d_ties) {
+    // key ties resolved on exact values so far (statistics; synchronises with the device)
+    unsigned long long ties = 0;
+    if (cudaMemcpy(&ties, f->d_ties, 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
+      info->reserved[0] = (int32_t)(ties & 0x7fffffff);
+      info->reserved[1] = (int32_t)(ties >> 31);
+    }
+  }
   return TBK_OK;
 }
 
@@ -535,8 +728,30 @@ int tbk_host_layout_check(const tbk_forest_arrays *fa, const tbk_schedule *sched
   host.transform = fa->transform;
   host.initial_value = fa->initial_value;
   host.num_features = fa->num_features;
+  if (schedule && schedule->feature_bits == 16) {
+    tb::QuantForest q;
+    std::string qerr = tb::pack_quant(host, &q);
+    if (!qerr.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str());
+    int64_t ties = 0;
+    if (rows && n_rows > 0) tb::walk_quant_on_host(q, rows, n_rows, ld, leaf_ids, sums, &ties);
+    if (info) {
+      std::memset(info, 0, sizeof *info);
+      info->num_trees = q.num_trees;
+      info->num_nodes = q.num_nodes;
+      info->num_groups = (int64_t)q.groups.size();
+      info->packed_bytes = (int64_t)q.node_plane.size() * 8;
+      info->max_depth = q.max_depth;
+      info->num_features = q.num_features;
+      info->transform = q.transform;
+      info->schedule.representation = TBK_REP_REORG;
+      info->schedule.tile_size = 1;
+      info->schedule.feature_bits = 16;
+      info->reserved[0] = (int32_t)std::min<int64_t>(ties, 0x7fffffff);
+    }
+    return TBK_OK;
+  }
   tb::PackOptions opt;
-  opt.representation = schedule ? schedule->representation : 0;
+  opt.representation = schedule && schedule->representation >= 0 ? schedule->representation : 0;
   opt.tile_size = schedule && schedule->tile_size > 0 ? schedule->tile_size : 1;
   tb::PackedForest packed;
   std::string err = tb::pack_forest(host, opt, &packed);

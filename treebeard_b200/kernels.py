@@ -10,9 +10,9 @@ import numpy as np
 
 from . import _lib
 
-REP_SPARSE, REP_ARRAY, REP_REORG = 0, 1, 2
+REP_AUTO, REP_SPARSE, REP_ARRAY, REP_REORG = -1, 0, 1, 2
 OUT_F32, OUT_I8 = 0, 1
-REP_BY_NAME = {"sparse": REP_SPARSE, "gpu_sparse": REP_SPARSE, "array": REP_ARRAY,
+REP_BY_NAME = {"auto": REP_AUTO, "sparse": REP_SPARSE, "gpu_sparse": REP_SPARSE, "array": REP_ARRAY,
                "gpu_array": REP_ARRAY, "reorg": REP_REORG, "gpu_reorg": REP_REORG}
 
 
@@ -29,7 +29,8 @@ class ScheduleC(ctypes.Structure):
     _fields_ = [("representation", ctypes.c_int32), ("tile_size", ctypes.c_int32),
                 ("rows_per_block", ctypes.c_int32), ("rows_per_thread", ctypes.c_int32),
                 ("tree_threads", ctypes.c_int32), ("tree_chunks", ctypes.c_int32),
-                ("cache_trees", ctypes.c_int32), ("reserved", ctypes.c_int32 * 5)]
+                ("cache_trees", ctypes.c_int32), ("feature_bits", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 4)]
 
 
 class ForestInfoC(ctypes.Structure):
@@ -95,10 +96,10 @@ def forest_arrays_c(f):
 
 
 def make_schedule(representation="sparse", tile_size=1, rows_per_block=0, rows_per_thread=0,
-                  tree_threads=0, tree_chunks=0, cache_trees=0) -> ScheduleC:
+                  tree_threads=0, tree_chunks=0, cache_trees=0, feature_bits=0) -> ScheduleC:
     rep = REP_BY_NAME[representation] if isinstance(representation, str) else int(representation)
     return ScheduleC(rep, tile_size, rows_per_block, rows_per_thread, tree_threads, tree_chunks,
-                     cache_trees)
+                     cache_trees, feature_bits)
 
 
 def _torch():
