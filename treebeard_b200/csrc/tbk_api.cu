@@ -132,7 +132,10 @@ int ensure_orig(tbk_forest *f) {
 
 enum Mode { kPredict, kPartial, kLeafIds };
 
-int quant_smem_bytes(int num_features) { return 128 + 3 * tb::kQStage + (num_features + 1) * 64; }
+int quant_meta_bytes(int groups_per_chunk) { return (groups_per_chunk * 8 + 127) / 128 * 128; }
+int quant_smem_bytes(int num_features, int groups_per_chunk = tb::kQMaxGroupsPerChunk) {
+  return 128 + quant_meta_bytes(groups_per_chunk) + 3 * tb::kQStage + (num_features + 1) * 64;
+}
 
 // One prediction with the 16-bit-key kernel (one block per 32 rows, 32 warps).
 int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
@@ -143,6 +146,8 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   int64_t chunks = 1;
   if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
   else if (grid_x < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + grid_x - 1) / grid_x;
+  // the group table of a chunk lives in shared memory: bound the groups per chunk
+  chunks = std::max<int64_t>(chunks, (G + tb::kQMaxGroupsPerChunk - 1) / tb::kQMaxGroupsPerChunk);
   chunks = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(chunks, G), 65535));
   const int gpc = (int)((G + chunks - 1) / chunks);
   chunks = (G + gpc - 1) / gpc;
@@ -155,7 +160,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   plan.staged = 1;
   plan.cache_rows = 1;
   plan.stage_bytes = tb::kQStage;
-  plan.smem_bytes = quant_smem_bytes(q.num_features);
+  plan.smem_bytes = quant_smem_bytes(q.num_features, gpc);
   plan.threads = 1024;
   plan.grid_x = grid_x;
   f->last_plan = plan;
@@ -197,6 +202,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   p.vec4_ok = (q.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
   p.status = f->d_status;
   p.tie_count = f->d_ties;
+  p.meta_bytes = quant_meta_bytes(gpc);
   CUDA_TRY(cudaFuncSetAttribute((const void *)tb::tb_walk_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
   if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
   dim3 grid((unsigned)grid_x, (unsigned)chunks);
@@ -440,8 +446,8 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
     CUDA_TRY_F(cudaMalloc(&f->d_qscale, nf * 4));
     CUDA_TRY_F(cudaMemset(f->d_qlo, 0, nf * 4));
     CUDA_TRY_F(cudaMemset(f->d_qscale, 0, nf * 4));
-    CUDA_TRY_F(cudaMalloc(&f->d_ties, 8));
-    CUDA_TRY_F(cudaMemset(f->d_ties, 0, 8));
+    CUDA_TRY_F(cudaMalloc(&f->d_ties, 128));
+    CUDA_TRY_F(cudaMemset(f->d_ties, 0, 128));
     CUDA_TRY_F(cudaMemcpy(f->d_qnode, q.node_plane.data(), n * 4, cudaMemcpyHostToDevice));
     CUDA_TRY_F(cudaMemcpy(f->d_qleaf, q.leaf_plane.data(), n * 4, cudaMemcpyHostToDevice));
     CUDA_TRY_F(cudaMemcpy(f->d_qexact, q.exact_plane.data(), n * 4, cudaMemcpyHostToDevice));
@@ -564,6 +570,14 @@ int tbk_forest_get_info(const tbk_forest *f, tbk_forest_info *info) {
       info->reserved[0] = (int32_t)(ties & 0x7fffffff);
       info->reserved[1] = (int32_t)(ties >> 31);
     }
+#ifdef TBK_QUANT_PROF
+    unsigned long long prof[9] = {0};
+    if (cudaMemcpy(prof, f->d_ties + 1, 64, cudaMemcpyDeviceToHost) == cudaSuccess && prof[7] > 0) {
+      // average cycles per block: staging, then the six phases of the group loop
+      std::fprintf(stderr, "[quant prof] blocks %llu  stage %llu | tick0 %llu  wait_node %llu  walk %llu  release %llu  wait_leaf %llu  leaf+release %llu\n",
+                   prof[7], prof[0] / prof[7], prof[1] / prof[7], prof[2] / prof[7], prof[3] / prof[7], prof[4] / prof[7], prof[5] / prof[7], prof[6] / prof[7]);
+    }
+#endif
   }
   return TBK_OK;
 }

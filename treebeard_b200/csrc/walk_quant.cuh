@@ -10,8 +10,17 @@
 // issued by a different warp so that two copies are always in flight.  Per-row sums live
 // in registers and are combined across the 32 warps once, at the end.
 //
+// The walk is fully unrolled per depth and fetches BOTH children of the current node
+// while the key comparison is still in flight, which takes the node load off the
+// dependent chain.  Key ties are only flagged on the fast path; a flagged (row, tree)
+// pair is then re-walked on the exact fp32 values from global memory.
+//
+// Waiting on a stage is done by one lane per warp (mbarrier.try_wait); stages are freed
+// by a block-wide barrier.
+//
 // Reference counterparts: the walk of src/mlir/CodeGenStateMachine.cpp:149-243 over the
-// reorg layout (src/gpu/ReorgForestRepresentation.cpp:495-571), the row cache
+// reorg layout (src/gpu/ReorgForestRepresentation.cpp:495-571), the unrolled walk of
+// padded trees (src/mlir/WalkDecisionTreeLoweringPass.cpp:24-53), the row cache
 // (src/gpu/GPURepresentations.cpp:279-399) and the per-thread-column reduction
 // (src/reduction/LowerReduceOps.cpp:921-1003).
 #pragma once
@@ -44,12 +53,14 @@ struct QuantParams {
   int32_t num_groups, groups_per_chunk, num_features, transform;
   float initial_value;
   int32_t vec4_ok;
+  int32_t meta_bytes;            // shared-memory bytes reserved for the group table
   int32_t *status;
   unsigned long long *tie_count; // optional statistics
 };
 
 constexpr int kQStage = 32768;
-constexpr uint32_t kQWaitLimit = 1u << 20;
+constexpr int kQMaxGroupsPerChunk = 240;
+constexpr uint32_t kQWaitTries = 1u << 20;
 
 __device__ __forceinline__ uint32_t quant_key_dev(float v, float lo, float sc) {
   const float y = __fmaf_rn(__fsub_rn(v, lo), -sc, 65533.0f);
@@ -74,17 +85,89 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
   return v;
 }
 __device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
-  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory");
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v));
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait_q(uint64_t *bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kQWaitLimit; ++it) {
-    if (mbar_test(bar, parity)) return true;
-    if (it > 32) __nanosleep(40);
+// Bounded, hardware-suspended wait (one calling thread).
+__device__ __forceinline__ bool mbar_try_wait_bounded(uint64_t *bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < kQWaitTries; ++it) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+                 " selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(addr), "r"(parity), "r"(200u)
+                 : "memory");
+    if (ok) return true;
   }
   return false;
+}
+// Lane 0 waits; the result (and the ordering it implies) is shared with the warp.
+__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_try_wait_bounded(bar, parity) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// Fast walk of DEPTH levels of one column of a staged node plane.  Returns the byte
+// address of the slot reached (colbase + 128 * slot); *tie is set when any key
+// comparison on the path tied (the result is then not to be trusted).
+template <int DEPTH>
+__device__ __forceinline__ uint32_t quant_walk(uint32_t colbase, uint32_t keys_lane, bool *tie) {
+  uint32_t A = colbase;
+  bool t = false;
+  if (DEPTH > 0) {
+    uint32_t node = lds_u32(A);
+    const uint32_t cL = 128u - colbase;
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      const uint32_t kx = lds_u16(keys_lane + (node >> 16) * 64u);
+      const uint32_t AL = 2u * A + cL;
+      uint32_t nL = 0, nR = 0;
+      if (d + 1 < DEPTH) {
+        nL = lds_u32(AL);
+        nR = lds_u32(AL + 128u);
+      }
+      const uint32_t kt = node & 0xffffu;
+      const bool right = kx < kt;
+      t |= (kx == kt);
+      A = right ? AL + 128u : AL;
+      node = right ? nR : nL;
+    }
+  }
+  *tie = t;
+  return A;
+}
+
+__device__ __forceinline__ uint32_t quant_walk_any(uint32_t depth, uint32_t colbase, uint32_t keys_lane, bool *tie) {
+  switch (depth) {
+  case 0: return quant_walk<0>(colbase, keys_lane, tie);
+  case 1: return quant_walk<1>(colbase, keys_lane, tie);
+  case 2: return quant_walk<2>(colbase, keys_lane, tie);
+  case 3: return quant_walk<3>(colbase, keys_lane, tie);
+  case 4: return quant_walk<4>(colbase, keys_lane, tie);
+  case 5: return quant_walk<5>(colbase, keys_lane, tie);
+  case 6: return quant_walk<6>(colbase, keys_lane, tie);
+  case 7: return quant_walk<7>(colbase, keys_lane, tie);
+  default: return quant_walk<8>(colbase, keys_lane, tie);
+  }
+}
+
+// Re-walk of one (row, tree) pair behind a key tie: the staged keys decide wherever they
+// can, and only the tied comparisons read the exact fp32 values from global memory.
+// Returns the slot reached (level-order numbering of the planes).
+__device__ __noinline__ uint32_t quant_walk_exact(uint32_t colbase, uint32_t keys_lane, const float *exact_plane,
+                                                  size_t plane_row, uint32_t depth, uint32_t col,
+                                                  const float *rowp) {
+  uint32_t s = 0;
+  for (uint32_t d = 0; d < depth; ++d) {
+    const uint32_t node = lds_u32(colbase + s * 128u);
+    const uint32_t f = node >> 16, kt = node & 0xffffu;
+    const uint32_t kx = lds_u16(keys_lane + f * 64u);
+    bool right = kx < kt;
+    if (kx == kt) right = !(__ldg(rowp + f) < __ldg(exact_plane + (plane_row + s) * 32u + col));
+    s = 2u * s + 1u + (right ? 1u : 0u);
+  }
+  return s;
 }
 
 // Fills the key field of every split node from its exact threshold (run once at upload,
@@ -97,13 +180,20 @@ __global__ void tb_quant_fill_keys(uint32_t *node_plane, const float *exact_plan
   if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_key_dev(exact_plane[i], lo[f], scale[f]);
 }
 
+#ifdef TBK_QUANT_PROF
+#define TBK_TICK(i) do { const long long t_now = clock64(); t_acc[i] += t_now - t_prev; t_prev = t_now; } while (0)
+#else
+#define TBK_TICK(i) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int F = p.num_features;
   uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);      // [3]
-  uint64_t *empty = full + 3;                                   // [3]
-  unsigned char *ring = smem_raw + 128;
+  // group table of this chunk: {plane offset in 32-element rows, depth}
+  uint2 *gtab = reinterpret_cast<uint2 *>(smem_raw + 128);
+  unsigned char *ring = smem_raw + 128 + p.meta_bytes;
   const uint32_t ring_s = smem_u32(ring);
   const uint32_t keys_s = ring_s + 3 * kQStage;                 // u16 [F+1][32]
   const uint32_t keys_lane = keys_s + lane * 2;
@@ -113,39 +203,58 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   const float *rowp = p.rows + (live ? row : 0) * p.ld;
   const int g0 = blockIdx.y * p.groups_per_chunk;
   const int g1 = min(p.num_groups, g0 + p.groups_per_chunk);
-  const int P = 2 * (g1 - g0); // pieces: node plane, leaf plane of each group
+  const int NG = g1 - g0;
+  const int P = 2 * NG; // pieces: node plane, leaf plane of each group
 
+#ifdef TBK_QUANT_PROF
+  const long long t_block0 = clock64();
+#endif
   if (tid == 0) {
-    for (int i = 0; i < 3; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 32);
-    }
+    for (int i = 0; i < 3; ++i) mbar_init(&full[i], 1);
     fence_barrier_init();
+  }
+  for (int i = tid; i < NG; i += blockDim.x) {
+    const DevQuantGroup gm = p.groups[g0 + i];
+    gtab[i] = make_uint2((uint32_t)(gm.elem_off >> 5), gm.depth);
   }
   __syncthreads();
 
   auto issue = [&](int piece) {
-    const DevQuantGroup gm = p.groups[g0 + (piece >> 1)];
-    const uint32_t bytes = gm.slots * 128u;
-    const void *src = (piece & 1) ? static_cast<const void *>(p.leaf_plane + gm.elem_off)
-                                  : static_cast<const void *>(p.node_plane + gm.elem_off);
+    const uint2 gm = gtab[piece >> 1];
+    const uint32_t bytes = 128u << gm.y;
+    const size_t off = (size_t)gm.x * 32;
+    const void *src = (piece & 1) ? static_cast<const void *>(p.leaf_plane + off)
+                                  : static_cast<const void *>(p.node_plane + off);
     uint64_t *bar = &full[piece % 3];
     mbar_expect_tx(bar, bytes);
     bulk_g2s(ring + (size_t)(piece % 3) * kQStage, src, bytes, bar);
   };
   if (lane == 0 && warp < 3 && warp < P) issue(warp);
 
-  // ---- stage the row tile as keys: keys[f][row]
+  // ---- stage the row tile as keys: keys[f][row].  Four row loads per thread are put in
+  // flight before any of them is consumed.
   if (p.vec4_ok) {
-    for (int k = warp; k < F / 4; k += 32) {
-      const float4 v = live ? __ldg(reinterpret_cast<const float4 *>(rowp) + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4 lo = __ldg(reinterpret_cast<const float4 *>(p.lo) + k);
-      const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale) + k);
-      const uint32_t a = keys_lane + (uint32_t)k * 256u;
-      sts_u16(a, quant_key_dev(v.x, lo.x, sc.x));
-      sts_u16(a + 64, quant_key_dev(v.y, lo.y, sc.y));
-      sts_u16(a + 128, quant_key_dev(v.z, lo.z, sc.z));
-      sts_u16(a + 192, quant_key_dev(v.w, lo.w, sc.w));
+    const int nv = F / 4;
+    for (int k0 = warp; k0 < nv; k0 += 128) {
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int k = k0 + 32 * j;
+        v[j] = (live && k < nv) ? __ldg(reinterpret_cast<const float4 *>(rowp) + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int k = k0 + 32 * j;
+        if (k < nv) {
+          const float4 lo = __ldg(reinterpret_cast<const float4 *>(p.lo) + k);
+          const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale) + k);
+          const uint32_t a = keys_lane + (uint32_t)k * 256u;
+          sts_u16(a, quant_key_dev(v[j].x, lo.x, sc.x));
+          sts_u16(a + 64, quant_key_dev(v[j].y, lo.y, sc.y));
+          sts_u16(a + 128, quant_key_dev(v[j].z, lo.z, sc.z));
+          sts_u16(a + 192, quant_key_dev(v[j].w, lo.w, sc.w));
+        }
+      }
     }
   } else {
     for (int k = warp; k < F; k += 32)
@@ -153,62 +262,69 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   }
   if (warp == 0) sts_u16(keys_lane + (uint32_t)F * 64u, 65535u); // sentinel feature
   __syncthreads();
+#ifdef TBK_QUANT_PROF
+  const long long t_stage = clock64() - t_block0;
+  long long t_prev = clock64(), t_acc[6] = {0, 0, 0, 0, 0, 0};
+#endif
 
   const uint32_t col = (uint32_t)(lane + warp) & 31u;
   float acc = 0.f;
   bool ok = true;
   unsigned ties = 0;
 
-  // after a piece is consumed: release its stage and, if it is this warp's turn, refill it
+  // A block-wide barrier (which also carries any wait failure to every thread, so that
+  // the exit is uniform) frees the stage; the refill is issued by a rotating warp.
+  bool failed = false;
   auto release = [&](int piece) {
-    __syncwarp();
-    if (lane == 0) {
-      uint64_t *e = &empty[piece % 3];
-      mbar_arrive(e);
-      const int next = piece + 3;
-      if (next < P && (next & 31) == warp) {
-        if (mbar_wait_q(e, (uint32_t)(piece / 3) & 1u)) issue(next);
-        else ok = false;
-      }
-    }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    failed = __syncthreads_or(!ok) != 0;
+    const int next = piece + 3;
+    if (!failed && next < P && lane == 0 && (next & 31) == warp) issue(next);
   };
 
-  for (int gi = 0; gi < g1 - g0 && ok; ++gi) {
-    const DevQuantGroup gm = p.groups[g0 + gi];
+  for (int gi = 0; gi < NG; ++gi) {
+    const uint2 gm = gtab[gi];
+    const uint32_t depth = gm.y, slots = 1u << gm.y;
     int piece = 2 * gi;
-    if (!mbar_wait_q(&full[piece % 3], (uint32_t)(piece / 3) & 1u)) { ok = false; break; }
-    const uint32_t colbase = ring_s + (uint32_t)(piece % 3) * kQStage + col * 4u;
-    const uint32_t cL = 128u - colbase, cR = 256u - colbase;
-    uint32_t A = colbase;
-#pragma unroll 2
-    for (uint32_t d = 0; d < gm.depth; ++d) {
-      const uint32_t node = lds_u32(A);
-      const uint32_t f = node >> 16, kt = node & 0xffffu;
-      const uint32_t kx = lds_u16(keys_lane + f * 64u);
-      bool right = kx < kt;
-      if (kx == kt) {
-        // keys tie: decide on the exact fp32 values
-        const uint32_t slot = (A - colbase) >> 7;
-        const float thr = __ldg(p.exact_plane + gm.elem_off + (unsigned long long)slot * 32u + col);
-        right = !(__ldg(rowp + f) < thr);
+    TBK_TICK(0);
+    ok = warp_wait(&full[piece % 3], (uint32_t)(piece / 3) & 1u, lane);
+    TBK_TICK(1);
+    uint32_t slot = 0;
+    if (ok) {
+      const uint32_t colbase = ring_s + (uint32_t)(piece % 3) * kQStage + col * 4u;
+      bool tie;
+      slot = (quant_walk_any(depth, colbase, keys_lane, &tie) - colbase) >> 7;
+      if (tie) {
+        slot = quant_walk_exact(colbase, keys_lane, p.exact_plane, gm.x, depth, col, rowp);
         ++ties;
       }
-      A = 2u * A + (right ? cR : cL);
     }
-    const uint32_t leaf = ((A - colbase) >> 7) - (gm.slots - 1u);
+    const uint32_t leaf = slot - (slots - 1u);
+    TBK_TICK(2);
     release(piece);
-    if (!ok) break;
+    TBK_TICK(3);
+    if (failed) break;
     ++piece;
-    if (!mbar_wait_q(&full[piece % 3], (uint32_t)(piece / 3) & 1u)) { ok = false; break; }
-    acc += lds_f32(ring_s + (uint32_t)(piece % 3) * kQStage + leaf * 128u + col * 4u);
-    if (p.leaf_ids != nullptr && live) {
-      const int t = p.tree_index[(g0 + gi) * 32 + (int)col];
-      if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[gm.elem_off + (unsigned long long)leaf * 32u + col];
+    ok = warp_wait(&full[piece % 3], (uint32_t)(piece / 3) & 1u, lane);
+    TBK_TICK(4);
+    if (ok) {
+      acc += lds_f32(ring_s + (uint32_t)(piece % 3) * kQStage + leaf * 128u + col * 4u);
+      if (p.leaf_ids != nullptr && live) {
+        const int t = p.tree_index[(g0 + gi) * 32 + (int)col];
+        if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[((size_t)gm.x + leaf) * 32u + col];
+      }
     }
     release(piece);
+    TBK_TICK(5);
+    if (failed) break;
   }
-  if (__syncthreads_or(!ok)) {
+#ifdef TBK_QUANT_PROF
+  if (p.tie_count != nullptr && lane == 0 && (warp == 5)) {
+    atomicAdd(p.tie_count + 1, (unsigned long long)t_stage);
+    for (int i = 0; i < 6; ++i) atomicAdd(p.tie_count + 2 + i, (unsigned long long)t_acc[i]);
+    atomicAdd(p.tie_count + 8, 1ull);
+  }
+#endif
+  if (failed) {
     if (tid == 0) atomicExch(p.status, 4);
     return;
   }
