@@ -190,7 +190,8 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int F = p.num_features;
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);      // [3]
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);      // [3] tree pieces
+  uint64_t *sbar = full + 3;                                    // [2] row-staging rounds
   // group table of this chunk: {plane offset in 32-element rows, depth}
   uint2 *gtab = reinterpret_cast<uint2 *>(smem_raw + 128);
   unsigned char *ring = smem_raw + 128 + p.meta_bytes;
@@ -210,7 +211,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   const long long t_block0 = clock64();
 #endif
   if (tid == 0) {
-    for (int i = 0; i < 3; ++i) mbar_init(&full[i], 1);
+    for (int i = 0; i < 5; ++i) mbar_init(&full[i], 1);
     fence_barrier_init();
   }
   for (int i = tid; i < NG; i += blockDim.x) {
@@ -229,36 +230,48 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
     mbar_expect_tx(bar, bytes);
     bulk_g2s(ring + (size_t)(piece % 3) * kQStage, src, bytes, bar);
   };
+  // ---- stage the row tile as keys: keys[f][row]
   if (lane == 0 && warp < 3 && warp < P) issue(warp);
-
-  // ---- stage the row tile as keys: keys[f][row].  Four row loads per thread are put in
-  // flight before any of them is consumed.
-  if (p.vec4_ok) {
-    const int nv = F / 4;
-    for (int k0 = warp; k0 < nv; k0 += 128) {
-      float4 v[4];
+  {
+    // A warp takes a block of 32 consecutive features: every load instruction reads 128
+    // contiguous bytes of ONE row (lane = feature), so DRAM sees whole lines and adjacent
+    // warps continue the same rows.  A lane thus collects its feature for all 32 rows,
+    // packs the 32 keys into 64 bytes and writes them with four 16-byte stores.  Loads
+    // go to L2 only (the unified L1 is almost entirely shared memory here); sixteen are
+    // in flight per thread.
+    const long long row0 = (long long)blockIdx.x * 32;
+    const int live_rows = (int)min((long long)32, p.n_rows - row0);
+    const float *tile = p.rows + row0 * p.ld;
+    for (int f0 = warp * 32; f0 < F; f0 += 32 * 32) {
+      const int f = f0 + lane;
+      const bool fok = f < F;
+      const float lo = fok ? __ldg(p.lo + f) : 0.f, sc = fok ? __ldg(p.scale + f) : 0.f;
+      uint32_t packed[16];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int k = k0 + 32 * j;
-        v[j] = (live && k < nv) ? __ldg(reinterpret_cast<const float4 *>(rowp) + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      for (int half = 0; half < 2; ++half) {
+        float x[16];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int k = k0 + 32 * j;
-        if (k < nv) {
-          const float4 lo = __ldg(reinterpret_cast<const float4 *>(p.lo) + k);
-          const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale) + k);
-          const uint32_t a = keys_lane + (uint32_t)k * 256u;
-          sts_u16(a, quant_key_dev(v[j].x, lo.x, sc.x));
-          sts_u16(a + 64, quant_key_dev(v[j].y, lo.y, sc.y));
-          sts_u16(a + 128, quant_key_dev(v[j].z, lo.z, sc.z));
-          sts_u16(a + 192, quant_key_dev(v[j].w, lo.w, sc.w));
+        for (int r = 0; r < 16; ++r) {
+          const int rr = half * 16 + r;
+          x[r] = (fok && rr < live_rows) ? __ldcg(tile + (long long)rr * p.ld + f) : 0.f;
         }
+#pragma unroll
+        for (int r = 0; r < 16; r += 2)
+          packed[half * 8 + r / 2] = quant_key_dev(x[r], lo, sc) | (quant_key_dev(x[r + 1], lo, sc) << 16);
+      }
+      if (fok) {
+        const uint32_t dst = keys_s + (uint32_t)f * 64u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 16u * c), "r"(packed[4 * c]),
+                       "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3]));
       }
     }
-  } else {
-    for (int k = warp; k < F; k += 32)
-      sts_u16(keys_lane + (uint32_t)k * 64u, quant_key_dev(live ? __ldg(rowp + k) : 0.f, __ldg(p.lo + k), __ldg(p.scale + k)));
+  }
+  bool failed = false;
+  if (failed) {
+    if (tid == 0) atomicExch(p.status, 4);
+    return;
   }
   if (warp == 0) sts_u16(keys_lane + (uint32_t)F * 64u, 65535u); // sentinel feature
   __syncthreads();
@@ -274,7 +287,6 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
 
   // A block-wide barrier (which also carries any wait failure to every thread, so that
   // the exit is uniform) frees the stage; the refill is issued by a rotating warp.
-  bool failed = false;
   auto release = [&](int piece) {
     failed = __syncthreads_or(!ok) != 0;
     const int next = piece + 3;
