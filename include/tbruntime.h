@@ -167,6 +167,15 @@ TREEBEARD_RUNTIME_EXPORT void *TB_GetKernelForest(intptr_t inferenceRunner);
 TREEBEARD_RUNTIME_EXPORT intptr_t TB_CreateInferenceRunnerFromArrays(const void *forestArrays, intptr_t options,
                                                                      intptr_t gpuScheduleOptions,
                                                                      const char *representation);
+/* Host-side model loading, no device involved: parses a model file with the named front
+ * end ("xgboost_json" / "onnx_file"; numberOfFeatures as in Set_numberOfFeatures, 0 = from
+ * the file) and exposes the forest as flat arrays (tbk_forest_arrays*, include/tbk.h; the
+ * pointers stay valid until TB_FreeForest).  What the reference's ForestCreator builds in
+ * ConstructForest (src/json/xgboostparser.h:116-219, src/json/onnxmodelparser.h:220-374). */
+TREEBEARD_RUNTIME_EXPORT intptr_t TB_LoadForest(const char *modelPath, const char *creatorType,
+                                                int32_t numberOfFeatures);
+TREEBEARD_RUNTIME_EXPORT int32_t TB_ForestGetArrays(intptr_t forest, void *forestArraysOut);
+TREEBEARD_RUNTIME_EXPORT void TB_FreeForest(intptr_t forest);
 /* Width in bits of the input element / result element types of a runner
  * (GetInputTypeBitWidth / GetReturnTypeBitWidth of the generated module,
  * src/json/forestcreator.h:307-313). */

@@ -121,6 +121,21 @@ def main():
         np.savez_compressed(os.path.join(HERE, f"{stem}.npz"), rows=rows, expected=exp)
         manifest[stem] = {"rows": ROWS, "expected_from": "reference header via oracle/_ref"}
 
+    # ONNX: the reference's abalone regressor (consumed by its src/test/ONNXTests.cpp:32).
+    # The file is parsed with this repository's native ONNX front end; the CSV pins the
+    # result, and the forest is stored as flat arrays.
+    onnx_path = os.path.join(args.ref, "onnx_models", "abalone_onnx_model_save.onnx")
+    if os.path.exists(onnx_path):
+        from treebeard_b200 import treebeard
+        forest = treebeard.LoadForest(onnx_path, "onnx_file", 8)
+        rows, exp = read_csv(onnx_path + ".csv")
+        manifest["abalone_onnx"] = check(forest, rows, exp)
+        np.savez_compressed(os.path.join(HERE, "abalone_onnx.npz"), tree_off=forest.tree_off,
+                            left=forest.left, right=forest.right, feat=forest.feat, thr=forest.thr,
+                            class_id=forest.class_id, num_classes=forest.num_classes,
+                            transform=forest.transform, initial_value=forest.initial_value,
+                            num_features=forest.num_features, rows=rows[:ROWS], expected=exp[:ROWS])
+
     with open(os.path.join(HERE, "manifest.json"), "w") as fh:
         json.dump(manifest, fh, indent=1, sort_keys=True)
     bad = {k: v for k, v in manifest.items()

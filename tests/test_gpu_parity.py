@@ -247,3 +247,30 @@ def test_auto_representation_picks_keys_for_wide_rows_only():
     with pytest.raises(kernels.TbkError):
         deep, _ = small_config("c5", rows=1)
         kernels.DeviceForest(deep, representation="reorg", feature_bits=16)
+
+
+@pytest.mark.parametrize("mode", ["BRANCH_LT", "BRANCH_GEQ"])
+def test_runner_from_onnx_file(mode, tmp_path):
+    from treebeard_b200 import synth, treebeard
+    forest, X = small_config("c2", rows=512, trees=64)
+    path = str(tmp_path / "m.onnx")
+    synth.save_onnx(forest, path, mode=mode)
+    options = treebeard.CompilerOptions(512, 1)
+    options.SetNumberOfFeatures(forest.num_features)
+    runner = treebeard.TreebeardInferenceRunner.FromONNXModelFile(path, options)
+    assert runner.rowSize == forest.num_features
+    assert_predictions_close(runner.RunInference(X), oracle.predict(forest, X))
+    ctx = treebeard.TreebeardContext(path, "", options)
+    ctx.SetInputFiletype("onnx_file")
+    ctx.SetRepresentationType("gpu_sparse")
+    again = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx)
+    assert_predictions_close(again.RunInference(X), oracle.predict(forest, X))
+
+
+def test_abalone_onnx_golden_on_gpu(golden_dir):
+    from treebeard_b200 import kernels
+    z = np.load(os.path.join(golden_dir, "abalone_onnx.npz"))
+    forest = golden_forest(z)
+    for rep in ("sparse", "array", "reorg"):
+        got = kernels.DeviceForest(forest, representation=rep).predict(_dev(z["rows"])).cpu().numpy()
+        assert oracle.fp_equal(got, z["expected"]).all()

@@ -138,10 +138,10 @@ int rep_from_name(const std::string &name) {
   return -1;
 }
 
-bool load_forest(const std::string &creator, const std::string &path, tb::Forest *f) {
+bool load_forest(const std::string &creator, const std::string &path, tb::Forest *f, int32_t num_features = 0) {
   std::string err;
   if (creator == "xgboost_json") err = tb::load_xgboost_json(path, f);
-  else if (creator == "onnx_file") err = tb::load_onnx_file(path, f);
+  else if (creator == "onnx_file") err = tb::load_onnx_file(path, num_features, f);
   else err = "unknown forest creator \"" + creator + "\"";
   if (!err.empty()) {
     set_error(TBK_ERR_IO, err);
@@ -224,7 +224,7 @@ InferenceRunner *runner_from_context(TreebeardContext *ctx) {
     return nullptr;
   }
   if (!ctx->forestLoaded) {
-    if (!load_forest(ctx->creatorType, ctx->modelPath, &ctx->forest)) return nullptr;
+    if (!load_forest(ctx->creatorType, ctx->modelPath, &ctx->forest, ctx->options.numberOfFeatures)) return nullptr;
     ctx->forestLoaded = true;
   }
   return build_runner(ctx->forest, ctx->options, ctx->hasGpuOptions ? &ctx->gpuOptions : nullptr,
@@ -431,7 +431,7 @@ intptr_t CreateInferenceRunnerForONNXModel(const char *modelPath, intptr_t optio
     return 0;
   }
   tb::Forest forest;
-  if (!load_forest("onnx_file", modelPath, &forest)) return 0;
+  if (!load_forest("onnx_file", modelPath, &forest, opt->numberOfFeatures)) return 0;
   return reinterpret_cast<intptr_t>(build_runner(forest, *opt, nullptr, ""));
 }
 
@@ -460,6 +460,42 @@ intptr_t TB_CreateInferenceRunnerFromArrays(const void *forestArrays, intptr_t o
   return reinterpret_cast<intptr_t>(build_runner(f, *opt, reinterpret_cast<GPUAutoScheduleOptions *>(gpuOptions),
                                                  representation ? representation : ""));
 }
+
+// ---- host-side model loading (no device involved) ----
+
+intptr_t TB_LoadForest(const char *modelPath, const char *creatorType, int32_t numberOfFeatures) {
+  clear_error();
+  if (!modelPath || !creatorType) {
+    set_error(TBK_ERR_INVALID, "null argument");
+    return 0;
+  }
+  auto *f = new tb::Forest();
+  if (!load_forest(creatorType, modelPath, f, numberOfFeatures)) {
+    delete f;
+    return 0;
+  }
+  return reinterpret_cast<intptr_t>(f);
+}
+
+int32_t TB_ForestGetArrays(intptr_t forest, void *arraysOut) {
+  auto *f = reinterpret_cast<tb::Forest *>(forest);
+  auto *fa = static_cast<tbk_forest_arrays *>(arraysOut);
+  if (!f || !fa) return TBK_ERR_INVALID;
+  fa->num_trees = f->num_trees();
+  fa->tree_off = f->tree_off.data();
+  fa->left = f->left.data();
+  fa->right = f->right.data();
+  fa->feat = f->feat.data();
+  fa->thr = f->thr.data();
+  fa->class_id = f->class_id.data();
+  fa->num_classes = f->num_classes;
+  fa->transform = f->transform;
+  fa->initial_value = f->initial_value;
+  fa->num_features = f->num_features;
+  return TBK_OK;
+}
+
+void TB_FreeForest(intptr_t forest) { delete reinterpret_cast<tb::Forest *>(forest); }
 
 // ---- process-wide switches ----
 
@@ -545,7 +581,7 @@ void BuildHIRRepresentation(void *c) {
   auto *ctx = static_cast<TreebeardContext *>(c);
   if (!ctx) return set_error(TBK_ERR_INVALID, "null context");
   if (!ctx->forestLoaded) {
-    if (!load_forest(ctx->creatorType, ctx->modelPath, &ctx->forest)) return;
+    if (!load_forest(ctx->creatorType, ctx->modelPath, &ctx->forest, ctx->options.numberOfFeatures)) return;
     ctx->forestLoaded = true;
   }
   if (!ctx->schedule)

@@ -140,7 +140,10 @@ class DeviceForest:
 
     def close(self):
         if getattr(self, "_h", None) and not getattr(self, "_borrowed", False):
-            lib().tbk_forest_free(self._h)
+            try:
+                lib().tbk_forest_free(self._h)
+            except TypeError:      # interpreter shutdown: module globals are already gone
+                pass
         self._h = None
 
     __del__ = close

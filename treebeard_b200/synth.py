@@ -264,3 +264,115 @@ def to_xgboost_dict(f: ForestArrays) -> dict:
 def save_xgboost_json(f: ForestArrays, path: str) -> None:
     with open(path, "w") as fh:
         json.dump(to_xgboost_dict(f), fh)
+
+
+# ---------------------------------------------------------------------------
+# ONNX writer (TreeEnsembleRegressor / TreeEnsembleClassifier, protobuf wire format)
+
+
+def _varint(v: int) -> bytes:
+    v &= (1 << 64) - 1
+    out = bytearray()
+    while True:
+        b = v & 0x7F
+        v >>= 7
+        if v:
+            out.append(b | 0x80)
+        else:
+            out.append(b)
+            return bytes(out)
+
+
+def _field(num: int, wire: int, payload: bytes) -> bytes:
+    return _varint((num << 3) | wire) + payload
+
+
+def _bytes_field(num: int, data: bytes) -> bytes:
+    return _field(num, 2, _varint(len(data)) + data)
+
+
+def _attr(name: str, *, f=None, i=None, s=None, floats=None, ints=None, strings=None,
+          packed: bool = False) -> bytes:
+    import struct
+    body = _bytes_field(1, name.encode())
+    if f is not None:
+        body += _field(2, 5, struct.pack("<f", f)) + _field(20, 0, _varint(1))
+    if i is not None:
+        body += _field(3, 0, _varint(i)) + _field(20, 0, _varint(2))
+    if s is not None:
+        body += _bytes_field(4, s.encode()) + _field(20, 0, _varint(3))
+    if floats is not None:
+        arr = np.asarray(floats, np.float32)
+        if packed:
+            body += _bytes_field(7, arr.tobytes())
+        else:
+            body += b"".join(_field(7, 5, struct.pack("<f", x)) for x in arr)
+        body += _field(20, 0, _varint(6))
+    if ints is not None:
+        if packed:
+            body += _bytes_field(8, b"".join(_varint(int(x)) for x in ints))
+        else:
+            body += b"".join(_field(8, 0, _varint(int(x))) for x in ints)
+        body += _field(20, 0, _varint(7))
+    if strings is not None:
+        body += b"".join(_bytes_field(9, x.encode()) for x in strings) + _field(20, 0, _varint(8))
+    return _bytes_field(5, body)
+
+
+def to_onnx_bytes(f: ForestArrays, mode: str = "BRANCH_LT", packed: bool = False) -> bytes:
+    """Serialises the forest as a single-node ONNX graph.  ``mode`` picks the comparison the
+    file states; thresholds and branches are rewritten so that every mode describes the SAME
+    function as the forest's "x < t goes left" (x <= t' with t' the float below t, and the
+    negated modes with the branches exchanged)."""
+    classifier = f.num_classes > 0
+    tree_ids, node_ids, feats, values, modes, true_ids, false_ids = [], [], [], [], [], [], []
+    w_tree, w_node, w_ids, w_val = [], [], [], []
+    swap = mode in ("BRANCH_GEQ", "BRANCH_GT")
+    lower = mode in ("BRANCH_LEQ", "BRANCH_GT")
+    for t in range(f.num_trees):
+        a, b = int(f.tree_off[t]), int(f.tree_off[t + 1])
+        for n in range(b - a):
+            leaf = f.left[a + n] < 0
+            thr = np.float32(f.thr[a + n])
+            if not leaf and lower:
+                thr = np.nextafter(thr, np.float32(-np.inf))
+            lchild, rchild = int(f.left[a + n]), int(f.right[a + n])
+            tree_ids.append(t); node_ids.append(n)
+            feats.append(0 if leaf else int(f.feat[a + n]))
+            values.append(0.0 if leaf else float(thr))
+            modes.append("LEAF" if leaf else mode)
+            true_ids.append(0 if leaf else (rchild if swap else lchild))
+            false_ids.append(0 if leaf else (lchild if swap else rchild))
+            if leaf:
+                w_tree.append(t); w_node.append(n)
+                w_ids.append(int(f.class_id[t]) if classifier else 0)
+                w_val.append(float(f.thr[a + n]))
+    post = {IDENTITY: "NONE", SIGMOID: "LOGISTIC", SOFTMAX: "SOFTMAX"}[f.transform]
+    kw = dict(packed=packed)
+    attrs = [
+        _attr("nodes_treeids", ints=tree_ids, **kw), _attr("nodes_nodeids", ints=node_ids, **kw),
+        _attr("nodes_featureids", ints=feats, **kw), _attr("nodes_values", floats=values, **kw),
+        _attr("nodes_modes", strings=modes), _attr("nodes_truenodeids", ints=true_ids, **kw),
+        _attr("nodes_falsenodeids", ints=false_ids, **kw),
+        _attr("nodes_missing_value_tracks_true", ints=[0] * len(node_ids), **kw),
+        _attr("post_transform", s=post),
+    ]
+    pre = "class_" if classifier else "target_"
+    attrs += [_attr(pre + "treeids", ints=w_tree, **kw), _attr(pre + "nodeids", ints=w_node, **kw),
+              _attr(pre + "ids", ints=w_ids, **kw), _attr(pre + "weights", floats=w_val, **kw)]
+    if classifier:
+        attrs += [_attr("classlabels_int64s", ints=list(range(f.num_classes)), **kw),
+                  _attr("base_values", floats=[f.initial_value] * f.num_classes, **kw)]
+        op = "TreeEnsembleClassifier"
+    else:
+        attrs += [_attr("n_targets", i=1), _attr("base_values", floats=[f.initial_value], **kw)]
+        op = "TreeEnsembleRegressor"
+    node = (_bytes_field(1, b"X") + _bytes_field(2, b"Y") + _bytes_field(3, b"ensemble") +
+            _bytes_field(4, op.encode()) + b"".join(attrs) + _bytes_field(7, b"ai.onnx.ml"))
+    graph = _bytes_field(1, node) + _bytes_field(2, b"forest")
+    return _field(1, 0, _varint(7)) + _bytes_field(2, b"treebeard_b200") + _bytes_field(7, graph)
+
+
+def save_onnx(f: ForestArrays, path: str, mode: str = "BRANCH_LT", packed: bool = False) -> None:
+    with open(path, "wb") as fh:
+        fh.write(to_onnx_bytes(f, mode, packed))

@@ -368,6 +368,32 @@ class TreebeardInferenceRunner:
         return int(_rt.TB_GetKernelForest(self.inferenceRunner) or 0)
 
 
+def LoadForest(model_path: str, file_type: str = "xgboost_json", number_of_features: int = 0):
+    """Parses a model file with the native front end ("xgboost_json" / "onnx_file") and
+    returns the forest as flat numpy arrays (a ``synth.ForestArrays``).  Host only."""
+    from .kernels import ForestArraysC
+    from .synth import ForestArrays
+    h = _rt.TB_LoadForest(model_path.encode("ascii"), file_type.encode("ascii"), number_of_features)
+    if not h:
+        treebeardAPI.check()
+        raise TreebeardRuntimeError("model could not be loaded")
+    try:
+        c = ForestArraysC()
+        _rt.TB_ForestGetArrays(h, ctypes.addressof(c))
+        T = c.num_trees
+        off = numpy.ctypeslib.as_array(ctypes.cast(c.tree_off, ctypes.POINTER(ctypes.c_int64)), (T + 1,)).copy()
+        n = int(off[-1])
+
+        def arr(ptr, ctype, count):
+            return numpy.ctypeslib.as_array(ctypes.cast(ptr, ctypes.POINTER(ctype)), (count,)).copy()
+        return ForestArrays(off, arr(c.left, ctypes.c_int32, n), arr(c.right, ctypes.c_int32, n),
+                            arr(c.feat, ctypes.c_int32, n), arr(c.thr, ctypes.c_float, n),
+                            arr(c.class_id, ctypes.c_int32, T), c.num_classes, c.transform,
+                            c.initial_value, c.num_features)
+    finally:
+        _rt.TB_FreeForest(h)
+
+
 def GenerateLLVMIRForXGBoostModel(modelJSONPathStr, llvmIRPathStr, modelGlobalsJSONPathStr, options):
     _rt.GenerateLLVMIRForXGBoostModel(modelJSONPathStr.encode("ascii"), llvmIRPathStr.encode("ascii"),
                                       modelGlobalsJSONPathStr.encode("ascii"), options.optionsPtr)

@@ -82,6 +82,9 @@ _SIGNATURES = {
     "TB_SetDevice": ((_I32,), None),
     "TB_GetKernelForest": ((_I64,), _I64),
     "TB_CreateInferenceRunnerFromArrays": ((_VP, _I64, _I64, _CP), _I64),
+    "TB_LoadForest": ((_CP, _CP, _I32), _I64),
+    "TB_ForestGetArrays": ((_I64, _VP), _I32),
+    "TB_FreeForest": ((_I64,), None),
     "TB_GetInputTypeBitWidth": ((_I64,), _I32),
     "TB_GetReturnTypeBitWidth": ((_I64,), _I32),
 }
