@@ -152,6 +152,28 @@ TBK_EXPORT int tbk_predict_leaf_ids(tbk_forest *forest, const float *d_rows, int
 TBK_EXPORT int tbk_predict_host(tbk_forest *forest, const float *h_rows, int64_t n_rows,
                                 int64_t ld, void *h_out, int32_t out_kind);
 
+/* tbk_predict for callers that may not allocate device memory while predicting (a server
+ * whose memory budget is fixed at start-up, a latency-critical loop that cannot risk the
+ * synchronisation an allocation can imply, a runtime that forbids allocations outside its
+ * own pool).  It has no counterpart in the reference.  Same arguments, same results as
+ * tbk_predict, computed by the same two kernels (walk into per-tree-chunk partial sums,
+ * atomic-free second pass), but the partial sums live in a fixed 8 MiB array inside the
+ * library image instead of a buffer grown with cudaMalloc; the call performs no
+ * cudaMalloc / cudaFree and uses no allocating library.
+ *   - Limit: n_rows x tree chunks x max(1, num_classes) <= 2 Mi (2097152) floats; larger
+ *     requests fail with TBK_ERR_UNSUPPORTED and a message naming the sizes.  Split the
+ *     batch, pin tree_chunks in the schedule, or use tbk_predict.
+ *   - Every GPU that loads the library holds the array until the process exits.
+ *   - The first call on a device looks up the array's device address (once per device);
+ *     make that first call before any stream capture.
+ *   - All calls on a device share the array: calls that overlap on the GPU (different
+ *     streams, or different forests) race on it.  Serialise them.  Nothing in it needs
+ *     clearing between calls: every element read by the second pass is written by the walk
+ *     of the same call.
+ *   - Forests in the 16-bit key layout are not covered (TBK_ERR_UNSUPPORTED). */
+TBK_EXPORT int tbk_predict_noalloc(tbk_forest *forest, const float *d_rows, int64_t n_rows, int64_t ld,
+                                   void *d_out, int32_t out_kind, void *stream);
+
 /* Device time of the walk (+ second pass) of the most recent tbk_predict* call on
  * this forest, in microseconds, measured with CUDA events when enabled; the
  * reference's counterpart is a host clock around the launch

@@ -722,6 +722,120 @@ int tbk_check_status(tbk_forest *f) {
 } // extern "C"
 
 // ---------------------------------------------------------------------------
+// Prediction for callers that must not allocate.
+//
+// Some hosts of this library may not call cudaMalloc on the prediction path: a serving
+// loop whose memory is fixed at start-up (a pool carved once, with nothing left over for
+// the driver to hand out later), a latency-critical thread that cannot afford the implicit
+// device synchronisation an allocation may bring, or an embedding runtime whose policy
+// forbids device allocations outside its own allocator.  tbk_predict sizes its tree-chunk
+// partial sums at run time and grows a cudaMalloc'ed buffer when a larger batch arrives;
+// this variant runs the same two kernels (walk into per-chunk partials, then the
+// atomic-free second pass) with the partials in a fixed array that is part of the loaded
+// library image, so it never allocates or frees anything.
+//
+// The array lives on every GPU that loads the library, from load until the process exits
+// (kNoAllocScratchFloats * 4 bytes = 8 MiB per GPU).  In host code its name is only a
+// stand-in for the device object; the device address is looked up once per device with
+// cudaGetSymbolAddress while that device is current, and that address is what the kernels
+// receive.
+
+namespace {
+
+constexpr size_t kNoAllocScratchFloats = size_t(1) << 21; // 2 Mi floats = 8 MiB
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+constexpr int kMaxDevices = 64;
+float *g_noalloc_addr[kMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+// Device address of the scratch array on `device` (which must be current).
+int noalloc_scratch_address(int device, float **out) {
+  if (device < 0 || device >= kMaxDevices) return fail(TBK_ERR_INVALID, "device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_addr[device]) {
+    float *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(TBK_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", device, cudaGetErrorString(e));
+    g_noalloc_addr[device] = ptr;
+  }
+  *out = g_noalloc_addr[device];
+  return TBK_OK;
+}
+
+} // namespace
+
+extern "C" int tbk_predict_noalloc(tbk_forest *f, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
+                                   int32_t out_kind, void *stream_) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  std::lock_guard<std::mutex> lock(f->mu);
+  const auto &pk = f->packed;
+  if (f->quant) return fail(TBK_ERR_UNSUPPORTED, "tbk_predict_noalloc does not cover the 16-bit key layout");
+  if (n_rows < 0 || ld < pk.num_features) return fail(TBK_ERR_INVALID, "ld (%lld) is smaller than the row size (%d)", (long long)ld, pk.num_features);
+  if (n_rows == 0) return TBK_OK;
+  if (!d_rows || !d_out) return fail(TBK_ERR_INVALID, "null pointer");
+  if (out_kind != TBK_OUT_F32 && out_kind != TBK_OUT_I8) return fail(TBK_ERR_INVALID, "unknown output kind %d", out_kind);
+  if (out_kind == TBK_OUT_I8 && pk.num_classes == 0) return fail(TBK_ERR_INVALID, "int8 output needs a multiclass forest");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  CUDA_TRY(cudaSetDevice(f->device));
+  float *scratch = nullptr;
+  int rc = noalloc_scratch_address(f->device, &scratch);
+  if (rc != TBK_OK) return rc;
+
+  tb::ForestShape shape{pk.num_features, pk.num_classes, (int64_t)pk.groups.size(), pk.max_group_bytes,
+                        (int32_t)pk.lut.size(), pk.representation, pk.tile_size};
+  tb::LaunchPlan plan;
+  std::string why = tb::select_launch(shape, f->user, n_rows, f->max_smem_optin, f->num_sms, false, &plan);
+  if (!why.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", why.c_str());
+  const int W = std::max(1, pk.num_classes);
+  const size_t need = (size_t)plan.chunks * (size_t)n_rows * (size_t)W;
+  if (need > kNoAllocScratchFloats)
+    return fail(TBK_ERR_UNSUPPORTED,
+                "tbk_predict_noalloc: %lld rows x %d tree chunks x %d outputs need %zu partial sums, the fixed scratch "
+                "holds %zu; split the batch or use tbk_predict",
+                (long long)n_rows, plan.chunks, W, need, kNoAllocScratchFloats);
+
+  tb::WalkParams p{};
+  p.blob = f->d_blob;
+  p.groups = f->d_groups;
+  p.tree_class = f->d_tree_class;
+  p.tree_index = f->d_tree_index;
+  p.lut = f->d_lut;
+  p.lut_bytes = (int32_t)pk.lut.size();
+  p.rows = d_rows;
+  p.n_rows = n_rows;
+  p.ld = ld;
+  p.partial = scratch; // every (chunk, row, output) element is written by the walk: nothing to clear
+  p.out = d_out;
+  p.out_kind = out_kind;
+  p.write_partial = 1;
+  p.num_trees = pk.num_trees;
+  p.num_groups = (int32_t)pk.groups.size();
+  p.groups_per_chunk = plan.groups_per_chunk;
+  p.num_features = pk.num_features;
+  p.num_classes = pk.num_classes;
+  p.transform = pk.transform;
+  p.initial_value = (float)pk.initial_value;
+  p.row_warps = plan.row_warps;
+  p.tree_threads = plan.tree_threads;
+  p.stage_bytes = plan.staged ? plan.stage_bytes : 0;
+  p.vec4_ok = (pk.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
+  p.status = f->d_status;
+  KernelFn fn = pick_kernel(pk.representation, pk.tile_size, plan.rows_per_lane, plan.staged, plan.cache_rows);
+  CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
+  dim3 grid((unsigned)plan.grid_x, (unsigned)plan.chunks), block((unsigned)plan.threads);
+  fn<<<grid, block, plan.smem_bytes, stream>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  const int tpb = 256;
+  tb::tb_finalize_kernel<<<(unsigned)((n_rows + tpb - 1) / tpb), tpb, 0, stream>>>(
+      scratch, plan.chunks, n_rows, W, pk.num_classes, (float)pk.initial_value, pk.transform, d_out, out_kind);
+  CUDA_TRY(cudaGetLastError());
+  f->launches += 2;
+  return TBK_OK;
+}
+
+// ---------------------------------------------------------------------------
 // Host-only utilities (no device is touched).
 
 extern "C" {

@@ -62,6 +62,7 @@ def lib():
         L.tbk_forest_free.argtypes = [vp]
         L.tbk_forest_get_info.argtypes = [vp, vp]
         L.tbk_predict.argtypes = [vp, vp, i64, i64, vp, i32, vp]
+        L.tbk_predict_noalloc.argtypes = [vp, vp, i64, i64, vp, i32, vp]
         L.tbk_predict_partial.argtypes = [vp, vp, i64, i64, vp, vp]
         L.tbk_finalize.argtypes = [vp, vp, i64, vp, i32, vp]
         L.tbk_predict_leaf_ids.argtypes = [vp, vp, i64, i64, vp, vp]
