@@ -31,6 +31,11 @@ from treebeard_b200 import synth  # noqa: E402
 
 HBM_FALLBACK_GBS = 6650.0
 
+# DRAM bytes per row (dram__bytes_read.sum + dram__bytes_write.sum) of the walk kernel, from
+# one ncu capture per workload on a reduced batch (see profiles/); traffic grows in
+# proportion to the rows, so a launch's traffic is this figure times its rows.
+NCU_DRAM_BYTES_PER_ROW = {"c3": 8190.0, "c2": 118.2}
+
 
 def bytes_per_row(cfg):
     """Algorithmic HBM bytes per predicted row: features in + prediction out."""
@@ -288,8 +293,11 @@ def main():
     kernel_ms = statistics.mean(per_step_ms)
     bpr = bytes_per_row(cfg)
     achieved = n_rows * bpr / (kernel_ms * 1e-3) / 1e9
+    per_row = NCU_DRAM_BYTES_PER_ROW.get(args.workload) if not args.trees else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak,
+                "traffic": per_row * n_rows if per_row else None,
+                "traffic_source": "ncu dram bytes per row on a reduced batch x rows" if per_row else None,
                 "peak_source": f"hbm_gbs of {peak_src}",
                 "algorithmic_bytes_per_row": bpr, "kernel_ms": kernel_ms,
                 "node_visits_per_s": n_rows * visits_per_row(cfg) / (kernel_ms * 1e-3)}
