@@ -59,7 +59,7 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
   q.tree_index.assign(G * kQuantCols, -1);
   uint64_t elems = 0;
   for (int64_t g = 0; g < G; ++g) {
-    uint32_t d = 0;
+    uint32_t d = 1; // at least one level, so that every group has both halves of its planes
     for (int c = 0; c < kQuantCols && g * kQuantCols + c < T; ++c)
       d = std::max<uint32_t>(d, depth[order[g * kQuantCols + c]]);
     q.groups[g] = QuantGroup{elems, d, 1u << d};
@@ -93,7 +93,7 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
         }
         const int32_t ft = f.feat[a + it.node];
         const float thr = f.thr[a + it.node];
-        const uint64_t e = gm.elem_off + (uint64_t)it.slot * kQuantCols + c;
+        const uint64_t e = gm.elem_off + (uint64_t)quant_plane_slot(it.slot, it.level, gm.depth) * kQuantCols + c;
         q.node_plane[e] = ((uint32_t)ft << 16) | quant_key(thr, q.lo[ft], q.scale[ft]);
         q.exact_plane[e] = thr;
         stack.push_back({f.left[a + it.node], 2 * it.slot + 1, it.level + 1});
@@ -121,7 +121,7 @@ void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows,
         if (t < 0) continue;
         uint32_t n = 0;
         for (uint32_t d = 0; d < gm.depth; ++d) {
-          const uint64_t e = gm.elem_off + (uint64_t)n * kQuantCols + c;
+          const uint64_t e = gm.elem_off + (uint64_t)quant_plane_slot(n, d, gm.depth) * kQuantCols + c;
           const uint32_t node = q.node_plane[e];
           const uint32_t ft = node >> 16, kt = node & 0xffffu, kx = keys[ft];
           bool right = kx < kt;

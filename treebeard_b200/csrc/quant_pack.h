@@ -55,6 +55,15 @@ struct QuantForest {
   std::vector<float> lo, scale;     // per feature (+ sentinel entry)
 };
 
+// Slot of a split node in the node / exact planes.  Nodes are in level order (root 0,
+// children 2n+1, 2n+2) except that the bottom decision level is pushed back by one slot:
+// the first half of a plane (2^(depth-1) slots) then holds levels 0..depth-2 plus one unused
+// slot, the second half exactly the bottom level, and each half is one contiguous piece
+// for the kernel's staging ring.
+inline uint32_t quant_plane_slot(uint32_t heap_slot, uint32_t level, uint32_t depth) {
+  return level + 1 == depth ? heap_slot + 1 : heap_slot;
+}
+
 // host restatement of the key function (the device computes keys with the same
 // arithmetic: one subtraction, one fused multiply-add, one floor-and-saturate)
 inline uint16_t quant_key(float v, float lo, float scale) {

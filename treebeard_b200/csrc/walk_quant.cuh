@@ -10,6 +10,13 @@
 // issued by a different warp so that two copies are always in flight.  Per-row sums live
 // in registers and are combined across the 32 warps once, at the end.
 //
+// The block works as TWO independent halves of 16 warps: half h takes the groups h, h+2,
+// ... of the chunk, for all 32 rows (two columns per lane, walked in lock-step), with its
+// own three-slot ring of 16 KB pieces (upper levels / bottom level of the node plane, two
+// halves of the leaf plane) and its own named barrier.  While one half waits for a piece
+// or sits in a barrier, the other half keeps the issue slots and the shared-memory pipe
+// busy; the forest is still streamed only once per 32-row tile.
+//
 // The walk is fully unrolled per depth and fetches BOTH children of the current node
 // while the key comparison is still in flight, which takes the node load off the
 // dependent chain.  Key ties are only flagged on the fast path; a flagged (row, tree)
@@ -180,23 +187,31 @@ __global__ void tb_quant_fill_keys(uint32_t *node_plane, const float *exact_plan
   if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_key_dev(exact_plane[i], lo[f], scale[f]);
 }
 
-#ifdef TBK_QUANT_PROF
-#define TBK_TICK(i) do { const long long t_now = clock64(); t_acc[i] += t_now - t_prev; t_prev = t_now; } while (0)
-#else
-#define TBK_TICK(i) do { } while (0)
-#endif
+constexpr int kQPiece = 16384;  // one ring slot: half a plane of a group of 8 levels
+constexpr int kQHalfWarps = 16; // warps per half-block
+
+// Barrier over the 512 threads of one half-block that also ORs a predicate across them.
+__device__ __forceinline__ bool half_barrier_or(int id, bool pred) {
+  uint32_t r;
+  asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.or.pred p, %2, 512, q;\n"
+               " selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(r)
+               : "r"((uint32_t)pred), "r"(id)
+               : "memory");
+  return r != 0;
+}
 
 __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int half = warp / kQHalfWarps, hw = warp % kQHalfWarps;
   const int F = p.num_features;
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);      // [3] tree pieces
-  uint64_t *sbar = full + 3;                                    // [2] row-staging rounds
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw) + half * 3; // [2 halves][3 slots]
   // group table of this chunk: {plane offset in 32-element rows, depth}
   uint2 *gtab = reinterpret_cast<uint2 *>(smem_raw + 128);
-  unsigned char *ring = smem_raw + 128 + p.meta_bytes;
+  unsigned char *ring = smem_raw + 128 + p.meta_bytes + (size_t)half * 3 * kQPiece;
   const uint32_t ring_s = smem_u32(ring);
-  const uint32_t keys_s = ring_s + 3 * kQStage;                 // u16 [F+1][32]
+  const uint32_t keys_s = smem_u32(smem_raw + 128 + p.meta_bytes) + 6 * kQPiece; // u16 [F+1][32]
   const uint32_t keys_lane = keys_s + lane * 2;
 
   const long long row = (long long)blockIdx.x * 32 + lane;
@@ -205,13 +220,11 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   const int g0 = blockIdx.y * p.groups_per_chunk;
   const int g1 = min(p.num_groups, g0 + p.groups_per_chunk);
   const int NG = g1 - g0;
-  const int P = 2 * NG; // pieces: node plane, leaf plane of each group
+  const int NGh = (NG - half + 1) / 2; // groups half, half + 2, ... of the chunk
+  const int P = 4 * NGh;               // pieces of this half: node upper, node bottom, leaf lo, leaf hi
 
-#ifdef TBK_QUANT_PROF
-  const long long t_block0 = clock64();
-#endif
   if (tid == 0) {
-    for (int i = 0; i < 5; ++i) mbar_init(&full[i], 1);
+    for (int i = 0; i < 6; ++i) mbar_init(reinterpret_cast<uint64_t *>(smem_raw) + i, 1);
     fence_barrier_init();
   }
   for (int i = tid; i < NG; i += blockDim.x) {
@@ -221,17 +234,19 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   __syncthreads();
 
   auto issue = [&](int piece) {
-    const uint2 gm = gtab[piece >> 1];
-    const uint32_t bytes = 128u << gm.y;
-    const size_t off = (size_t)gm.x * 32;
-    const void *src = (piece & 1) ? static_cast<const void *>(p.leaf_plane + off)
-                                  : static_cast<const void *>(p.node_plane + off);
+    const uint2 gm = gtab[2 * (piece >> 2) + half];
+    const int j = piece & 3;
+    const uint32_t hs = 1u << (gm.y - 1);          // slots per piece
+    const size_t off = ((size_t)gm.x + ((j & 1) ? hs : 0u)) * 32;
+    const void *src = j < 2 ? static_cast<const void *>(p.node_plane + off)
+                            : static_cast<const void *>(p.leaf_plane + off);
     uint64_t *bar = &full[piece % 3];
-    mbar_expect_tx(bar, bytes);
-    bulk_g2s(ring + (size_t)(piece % 3) * kQStage, src, bytes, bar);
+    mbar_expect_tx(bar, hs * 128u);
+    bulk_g2s(ring + (size_t)(piece % 3) * kQPiece, src, hs * 128u, bar);
   };
+  if (lane == 0 && hw < 3 && hw < P) issue(hw);
+
   // ---- stage the row tile as keys: keys[f][row]
-  if (lane == 0 && warp < 3 && warp < P) issue(warp);
   {
     // A warp takes a block of 32 consecutive features: every load instruction reads 128
     // contiguous bytes of ONE row (lane = feature), so DRAM sees whole lines and adjacent
@@ -248,16 +263,16 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
       const float lo = fok ? __ldg(p.lo + f) : 0.f, sc = fok ? __ldg(p.scale + f) : 0.f;
       uint32_t packed[16];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int part = 0; part < 2; ++part) {
         float x[16];
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-          const int rr = half * 16 + r;
+          const int rr = part * 16 + r;
           x[r] = (fok && rr < live_rows) ? __ldcg(tile + (long long)rr * p.ld + f) : 0.f;
         }
 #pragma unroll
         for (int r = 0; r < 16; r += 2)
-          packed[half * 8 + r / 2] = quant_key_dev(x[r], lo, sc) | (quant_key_dev(x[r + 1], lo, sc) << 16);
+          packed[part * 8 + r / 2] = quant_key_dev(x[r], lo, sc) | (quant_key_dev(x[r + 1], lo, sc) << 16);
       }
       if (fok) {
         const uint32_t dst = keys_s + (uint32_t)f * 64u;
@@ -268,75 +283,90 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
       }
     }
   }
-  bool failed = false;
-  if (failed) {
-    if (tid == 0) atomicExch(p.status, 4);
-    return;
-  }
   if (warp == 0) sts_u16(keys_lane + (uint32_t)F * 64u, 65535u); // sentinel feature
   __syncthreads();
-#ifdef TBK_QUANT_PROF
-  const long long t_stage = clock64() - t_block0;
-  long long t_prev = clock64(), t_acc[6] = {0, 0, 0, 0, 0, 0};
-#endif
 
-  const uint32_t col = (uint32_t)(lane + warp) & 31u;
+  // the two columns this lane walks in every group of its half
+  const uint32_t col[2] = {(uint32_t)(lane + hw) & 31u, (uint32_t)(lane + hw + 16) & 31u};
   float acc = 0.f;
-  bool ok = true;
+  bool ok = true, failed = false;
   unsigned ties = 0;
 
-  // A block-wide barrier (which also carries any wait failure to every thread, so that
-  // the exit is uniform) frees the stage; the refill is issued by a rotating warp.
-  auto release = [&](int piece) {
-    failed = __syncthreads_or(!ok) != 0;
-    const int next = piece + 3;
-    if (!failed && next < P && lane == 0 && (next & 31) == warp) issue(next);
+  // A barrier over the half-block (which also carries any wait failure to its 512 threads,
+  // so that their exit is uniform) frees a slot; the refill is issued by a rotating warp.
+  auto release = [&](int first, int count) {
+    failed = half_barrier_or(1 + half, !ok);
+    if (!failed && lane == 0)
+      for (int i = 0; i < count; ++i) {
+        const int next = first + i + 3;
+        if (next < P && (next % kQHalfWarps) == hw) issue(next);
+      }
   };
+  auto piece_ready = [&](int piece) { return warp_wait(&full[piece % 3], (uint32_t)(piece / 3) & 1u, lane); };
+  auto slot_addr = [&](int piece) { return ring_s + (uint32_t)(piece % 3) * kQPiece; };
 
-  for (int gi = 0; gi < NG; ++gi) {
+  for (int k = 0; k < NGh; ++k) {
+    const int gi = 2 * k + half;
     const uint2 gm = gtab[gi];
-    const uint32_t depth = gm.y, slots = 1u << gm.y;
-    int piece = 2 * gi;
-    TBK_TICK(0);
-    ok = warp_wait(&full[piece % 3], (uint32_t)(piece / 3) & 1u, lane);
-    TBK_TICK(1);
-    uint32_t slot = 0;
+    const uint32_t depth = gm.y, hs = 1u << (depth - 1);
+    const int q = 4 * k;
+    uint32_t idx[2] = {0, 0}, leaf[2] = {0, 0};
+
+    // upper levels 0 .. depth-2
+    ok = piece_ready(q);
     if (ok) {
-      const uint32_t colbase = ring_s + (uint32_t)(piece % 3) * kQStage + col * 4u;
-      bool tie;
-      slot = (quant_walk_any(depth, colbase, keys_lane, &tie) - colbase) >> 7;
-      if (tie) {
-        slot = quant_walk_exact(colbase, keys_lane, p.exact_plane, gm.x, depth, col, rowp);
-        ++ties;
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const uint32_t colbase = slot_addr(q) + col[w] * 4u;
+        bool tie;
+        uint32_t s = (quant_walk_any(depth - 1, colbase, keys_lane, &tie) - colbase) >> 7;
+        if (tie) {
+          s = quant_walk_exact(colbase, keys_lane, p.exact_plane, gm.x, depth - 1, col[w], rowp);
+          ++ties;
+        }
+        idx[w] = s - (hs - 1u); // position inside the bottom decision level
       }
     }
-    const uint32_t leaf = slot - (slots - 1u);
-    TBK_TICK(2);
-    release(piece);
-    TBK_TICK(3);
+    release(q, 1);
     if (failed) break;
-    ++piece;
-    ok = warp_wait(&full[piece % 3], (uint32_t)(piece / 3) & 1u, lane);
-    TBK_TICK(4);
+
+    // bottom decision level
+    ok = piece_ready(q + 1);
     if (ok) {
-      acc += lds_f32(ring_s + (uint32_t)(piece % 3) * kQStage + leaf * 128u + col * 4u);
-      if (p.leaf_ids != nullptr && live) {
-        const int t = p.tree_index[(g0 + gi) * 32 + (int)col];
-        if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[((size_t)gm.x + leaf) * 32u + col];
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const uint32_t node = lds_u32(slot_addr(q + 1) + idx[w] * 128u + col[w] * 4u);
+        const uint32_t f = node >> 16, kt = node & 0xffffu;
+        const uint32_t kx = lds_u16(keys_lane + f * 64u);
+        bool right = kx < kt;
+        if (kx == kt) {
+          right = !(__ldg(rowp + f) < __ldg(p.exact_plane + ((size_t)gm.x + hs + idx[w]) * 32u + col[w]));
+          ++ties;
+        }
+        leaf[w] = 2u * idx[w] + (right ? 1u : 0u);
       }
     }
-    release(piece);
-    TBK_TICK(5);
+    release(q + 1, 1);
+    if (failed) break;
+
+    // leaf values: lower and upper half of the leaf plane
+    ok = piece_ready(q + 2);
+    if (ok) ok = piece_ready(q + 3);
+    if (ok) {
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const uint32_t a = leaf[w] < hs ? slot_addr(q + 2) + leaf[w] * 128u : slot_addr(q + 3) + (leaf[w] - hs) * 128u;
+        acc += lds_f32(a + col[w] * 4u);
+        if (p.leaf_ids != nullptr && live) {
+          const int t = p.tree_index[(g0 + gi) * 32 + (int)col[w]];
+          if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[((size_t)gm.x + leaf[w]) * 32u + col[w]];
+        }
+      }
+    }
+    release(q + 2, 2);
     if (failed) break;
   }
-#ifdef TBK_QUANT_PROF
-  if (p.tie_count != nullptr && lane == 0 && (warp == 5)) {
-    atomicAdd(p.tie_count + 1, (unsigned long long)t_stage);
-    for (int i = 0; i < 6; ++i) atomicAdd(p.tie_count + 2 + i, (unsigned long long)t_acc[i]);
-    atomicAdd(p.tie_count + 8, 1ull);
-  }
-#endif
-  if (failed) {
+  if (__syncthreads_or(failed)) {
     if (tid == 0) atomicExch(p.status, 4);
     return;
   }
@@ -344,7 +374,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   if (p.leaf_ids != nullptr) return;
 
   // ---- combine the 32 warps (one partial per row each)
-  float *red = reinterpret_cast<float *>(ring);
+  float *red = reinterpret_cast<float *>(smem_raw + 128 + p.meta_bytes);
   red[warp * 32 + lane] = acc;
   __syncthreads();
   if (warp != 0 || !live) return;
