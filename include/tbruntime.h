@@ -9,7 +9,8 @@
  *   - nothing aborts: a failing call returns 0 / does nothing and records a status and a
  *     message readable through TB_GetLastStatus / TB_GetLastError;
  *   - there is one back end (the B200 kernels): the CPU-runner constructors build the
- *     same GPU runner, and the entry points that emit LLVM IR report "unsupported";
+ *     same GPU runner, and the entry points that emit LLVM IR write a compiled-model
+ *     file instead (binary forest + bound options), which InitializeInferenceRunner loads;
  *   - RunInference accepts host pointers (as the reference) and CUDA device pointers.
  */
 #ifndef TBRUNTIME_H
@@ -26,9 +27,11 @@ extern "C" {
 #define TREEBEARD_RUNTIME_EXPORT __attribute__((visibility("default")))
 
 /* ---- execution (src/runtime/runtime.cpp:35-121) ---- */
-/* Loads a packed-forest file written by SavePackedForest (the counterpart of the
- * reference's ahead-of-time .so + globals JSON pair, runtime.cpp:35-54). */
-TREEBEARD_RUNTIME_EXPORT intptr_t InitializeInferenceRunner(const char *packedForestPath,
+/* Builds a runner from a compiled-model file written by GenerateLLVMIRForXGBoostModel /
+ * CreateLLVMIRForONNXModel / LowerToLLVMAndDumpIR -- the counterpart of the reference's
+ * ahead-of-time .so + globals JSON pair (runtime.cpp:35-54).  modelGlobalsJSONPath may be
+ * NULL or empty; when given, the options it names replace those stored in the file. */
+TREEBEARD_RUNTIME_EXPORT intptr_t InitializeInferenceRunner(const char *modelFilePath,
                                                             const char *modelGlobalsJSONPath);
 /* inputs: batchSize x rowSize fp32, row-major; results: batchSize elements of the
  * return type (fp32, or int8 class ids) -- runtime.cpp:58-67 */
@@ -77,6 +80,8 @@ TREEBEARD_RUNTIME_EXPORT void Set_treeWalkInterleaveFactor(intptr_t options, int
 TREEBEARD_RUNTIME_EXPORT void Set_sharedMemoryReduce(intptr_t options, int32_t val);
 
 /* ---- one-call runner construction (runtime.cpp:216-297) ---- */
+/* The two "LLVM IR" calls write the compiled-model file to their second path and the
+ * globals JSON to their third (there is no LLVM back end). */
 TREEBEARD_RUNTIME_EXPORT void GenerateLLVMIRForXGBoostModel(const char *modelJSONPath, const char *llvmIRPath,
                                                             const char *modelGlobalsJSONPath, intptr_t options);
 TREEBEARD_RUNTIME_EXPORT intptr_t CreateInferenceRunner(const char *modelJSONPath, const char *profileCSVPath,
@@ -168,7 +173,7 @@ TREEBEARD_RUNTIME_EXPORT intptr_t TB_CreateInferenceRunnerFromArrays(const void 
                                                                      intptr_t gpuScheduleOptions,
                                                                      const char *representation);
 /* Host-side model loading, no device involved: parses a model file with the named front
- * end ("xgboost_json" / "onnx_file"; numberOfFeatures as in Set_numberOfFeatures, 0 = from
+ * end ("xgboost_json" / "onnx_file", or "compiled_model" for a compiled-model file; numberOfFeatures as in Set_numberOfFeatures, 0 = from
  * the file) and exposes the forest as flat arrays (tbk_forest_arrays*, include/tbk.h; the
  * pointers stay valid until TB_FreeForest).  What the reference's ForestCreator builds in
  * ConstructForest (src/json/xgboostparser.h:116-219, src/json/onnxmodelparser.h:220-374). */

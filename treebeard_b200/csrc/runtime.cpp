@@ -8,6 +8,7 @@
 #include "../../include/tbk.h"
 #include "forest.h"
 #include "loaders.h"
+#include "model_file.h"
 
 #include <cuda_runtime_api.h>
 
@@ -142,6 +143,10 @@ bool load_forest(const std::string &creator, const std::string &path, tb::Forest
   std::string err;
   if (creator == "xgboost_json") err = tb::load_xgboost_json(path, f);
   else if (creator == "onnx_file") err = tb::load_onnx_file(path, num_features, f);
+  else if (creator == "compiled_model") { // host-side readers only (TB_LoadForest)
+    tb::ModelFileOptions ignored;
+    err = tb::load_model_file(path, f, &ignored);
+  }
   else err = "unknown forest creator \"" + creator + "\"";
   if (!err.empty()) {
     set_error(TBK_ERR_IO, err);
@@ -231,6 +236,65 @@ InferenceRunner *runner_from_context(TreebeardContext *ctx) {
                       ctx->representation);
 }
 
+// ---- compiled-model files (model_file.h) ----
+
+tb::ModelFileOptions to_file_options(const CompilerOptions &opt, const GPUAutoScheduleOptions *gpu,
+                                     const std::string &repName) {
+  tb::ModelFileOptions m;
+  m.batch_size = opt.batchSize;
+  m.tile_size = opt.tileSize <= 0 ? 1 : opt.tileSize;
+  m.threshold_width = opt.thresholdTypeWidth;
+  m.feature_index_width = opt.featureIndexTypeWidth;
+  m.input_width = opt.inputElementTypeWidth;
+  m.return_width = opt.returnTypeWidth;
+  m.return_is_float = opt.returnTypeFloatType ? 1 : 0;
+  m.number_of_features = opt.numberOfFeatures > 0 ? opt.numberOfFeatures : 0;
+  if (gpu) {
+    m.has_gpu_options = 1;
+    m.rows_per_block = gpu->numRowsPerTB;
+    m.rows_per_thread = gpu->numRowsPerThread;
+    m.tree_threads = gpu->numTreeThreads;
+    m.cache_trees = gpu->cacheTrees ? 1 : 0;
+    m.cache_rows = gpu->cacheRows ? 1 : 0;
+  }
+  // an unnamed representation is resolved now, so that the file does not depend on the
+  // loading process's default
+  m.representation = repName.empty() ? (g_use_sparse ? "gpu_sparse" : "gpu_array") : repName;
+  return m;
+}
+
+void from_file_options(const tb::ModelFileOptions &m, CompilerOptions *opt, GPUAutoScheduleOptions *gpu) {
+  opt->batchSize = m.batch_size;
+  opt->tileSize = m.tile_size;
+  opt->thresholdTypeWidth = m.threshold_width;
+  opt->featureIndexTypeWidth = m.feature_index_width;
+  opt->inputElementTypeWidth = m.input_width;
+  opt->returnTypeWidth = m.return_width;
+  opt->returnTypeFloatType = m.return_is_float != 0;
+  opt->numberOfFeatures = m.number_of_features > 0 ? m.number_of_features : -1;
+  gpu->numRowsPerTB = m.rows_per_block;
+  gpu->numRowsPerThread = m.rows_per_thread;
+  gpu->numTreeThreads = m.tree_threads;
+  gpu->cacheTrees = m.cache_trees != 0;
+  gpu->cacheRows = m.cache_rows != 0;
+}
+
+bool write_compiled_model(const tb::Forest &forest, const CompilerOptions &opt, const GPUAutoScheduleOptions *gpu,
+                          const std::string &repName, const char *modelFilePath, const char *globalsPath) {
+  if (!modelFilePath || !*modelFilePath) {
+    set_error(TBK_ERR_INVALID, "no output path for the compiled-model file");
+    return false;
+  }
+  const tb::ModelFileOptions m = to_file_options(opt, gpu, repName);
+  std::string err = tb::save_model_file(modelFilePath, forest, m);
+  if (err.empty() && globalsPath && *globalsPath) err = tb::save_globals_json(globalsPath, forest, m);
+  if (!err.empty()) {
+    set_error(TBK_ERR_IO, err);
+    return false;
+  }
+  return true;
+}
+
 void run_batch(InferenceRunner *r, void *inputs, void *results, int64_t rows) {
   const int32_t kind = (!r->returnFloat && r->returnWidth == 8) ? TBK_OUT_I8 : TBK_OUT_F32;
   cudaPointerAttributes attr{};
@@ -293,9 +357,24 @@ void TB_SetDevice(int32_t device) { g_device = device; }
 
 // ---- execution ----
 
-intptr_t InitializeInferenceRunner(const char *, const char *) {
-  set_error(TBK_ERR_UNSUPPORTED, "loading a precompiled model is not available in this build");
-  return 0;
+intptr_t InitializeInferenceRunner(const char *modelFilePath, const char *modelGlobalsJSONPath) {
+  clear_error();
+  if (!modelFilePath) {
+    set_error(TBK_ERR_INVALID, "null argument");
+    return 0;
+  }
+  tb::Forest forest;
+  tb::ModelFileOptions m;
+  std::string err = tb::load_model_file(modelFilePath, &forest, &m);
+  if (err.empty() && modelGlobalsJSONPath && *modelGlobalsJSONPath) err = tb::load_globals_json(modelGlobalsJSONPath, &m);
+  if (!err.empty()) {
+    set_error(TBK_ERR_IO, err);
+    return 0;
+  }
+  CompilerOptions opt;
+  GPUAutoScheduleOptions gpu;
+  from_file_options(m, &opt, &gpu);
+  return reinterpret_cast<intptr_t>(build_runner(forest, opt, m.has_gpu_options ? &gpu : nullptr, m.representation));
 }
 
 void RunInference(intptr_t runner, void *inputs, void *results) {
@@ -404,11 +483,28 @@ GPU_OPTION_SETTER(sharedMemoryReduce, val != 0)
 
 // ---- one-call construction ----
 
-void GenerateLLVMIRForXGBoostModel(const char *, const char *, const char *, intptr_t) {
-  set_error(TBK_ERR_UNSUPPORTED, "this library has no LLVM back end; build a runner instead");
+// The reference's ahead-of-time flow writes LLVM IR (compiled to a shared object by the
+// user) plus a globals JSON, and InitializeInferenceRunner loads the pair back.  There is
+// no LLVM back end here: the same two calls write the compiled-model file (binary forest +
+// bound options) to the second path and the globals JSON to the third, and
+// InitializeInferenceRunner loads that pair.
+void GenerateLLVMIRForXGBoostModel(const char *modelJSONPath, const char *modelFilePath, const char *globalsPath,
+                                   intptr_t options) {
+  clear_error();
+  auto *opt = reinterpret_cast<CompilerOptions *>(options);
+  if (!modelJSONPath || !opt) return set_error(TBK_ERR_INVALID, "null argument");
+  tb::Forest forest;
+  if (!load_forest("xgboost_json", modelJSONPath, &forest)) return;
+  write_compiled_model(forest, *opt, nullptr, "", modelFilePath, globalsPath);
 }
-void CreateLLVMIRForONNXModel(const char *, const char *, const char *, intptr_t) {
-  set_error(TBK_ERR_UNSUPPORTED, "this library has no LLVM back end; build a runner instead");
+void CreateLLVMIRForONNXModel(const char *modelPath, const char *modelFilePath, const char *globalsPath,
+                              intptr_t options) {
+  clear_error();
+  auto *opt = reinterpret_cast<CompilerOptions *>(options);
+  if (!modelPath || !opt) return set_error(TBK_ERR_INVALID, "null argument");
+  tb::Forest forest;
+  if (!load_forest("onnx_file", modelPath, &forest, opt->numberOfFeatures)) return;
+  write_compiled_model(forest, *opt, nullptr, "", modelFilePath, globalsPath);
 }
 
 intptr_t CreateInferenceRunner(const char *modelJSONPath, const char *, intptr_t options) {
@@ -595,9 +691,22 @@ void *GetScheduleFromTBContext(intptr_t c) {
   return ctx->schedule.get();
 }
 
-bool LowerToLLVMAndDumpIR(void *, const char *) {
-  set_error(TBK_ERR_UNSUPPORTED, "this library has no LLVM back end");
-  return false;
+// Writes the context's compiled-model file to fileName and, when the context was given a
+// globals path, the globals JSON there (the reference dumps LLVM IR and its serializer's
+// globals file at this point: src/runtime/runtime.cpp:434-440).
+bool LowerToLLVMAndDumpIR(void *c, const char *fileName) {
+  clear_error();
+  auto *ctx = static_cast<TreebeardContext *>(c);
+  if (!ctx) {
+    set_error(TBK_ERR_INVALID, "null context");
+    return false;
+  }
+  if (!ctx->forestLoaded) {
+    if (!load_forest(ctx->creatorType, ctx->modelPath, &ctx->forest, ctx->options.numberOfFeatures)) return false;
+    ctx->forestLoaded = true;
+  }
+  return write_compiled_model(ctx->forest, ctx->options, ctx->hasGpuOptions ? &ctx->gpuOptions : nullptr,
+                              ctx->representation, fileName, ctx->globalsPath.c_str());
 }
 
 void *ConstructInferenceRunnerFromHIR(void *c) {
