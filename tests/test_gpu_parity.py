@@ -245,8 +245,56 @@ def test_auto_representation_picks_keys_for_wide_rows_only():
     assert b.info().schedule.feature_bits == 32
     assert_predictions_close(a.predict(_dev(Xw)).cpu().numpy(), oracle.predict(wide, Xw))
     with pytest.raises(kernels.TbkError):
-        deep, _ = small_config("c5", rows=1)
-        kernels.DeviceForest(deep, representation="reorg", feature_bits=16)
+        multi, _ = small_config("c4", rows=1)
+        kernels.DeviceForest(multi, representation="reorg", feature_bits=16)
+
+
+@pytest.mark.parametrize("trees,rows", [(1, 70), (24, 1500), (33, 20000)])
+def test_deep_tree_kernel_is_exact(trees, rows):
+    """Deep trees (12 levels): whole trees staged through shared memory over a tile of
+    16-bit keys.  Leaves must be exactly the oracle's, ties, NaN and infinities included;
+    covers an odd tree count, ragged tiles, tree chunks and the partial-sum path."""
+    from treebeard_b200 import kernels
+    forest, X = small_config("c5", rows=rows, trees=trees)
+    X = X.copy()
+    split = np.nonzero(forest.left >= 0)[0]
+    for i in range(600):
+        g = split[(i * 101) % len(split)]
+        X[i % len(X), forest.feat[g]] = forest.thr[g]
+    for i in range(6, 60):
+        g = forest.tree_off[i % trees]
+        X[i, forest.feat[g]] = forest.thr[g]
+    X[3, :] = np.nan
+    X[4, 0] = np.inf
+    X[5, 1] = -np.inf
+    want, want_ids = oracle.predict(forest, X, leaf_ids=True)
+    df = kernels.DeviceForest(forest, representation="auto", batch_hint=len(X))
+    info = df.info()
+    assert info.schedule.feature_bits == 16 and info.num_groups == (trees + 1) // 2
+    dX = _dev(X)
+    ids = df.predict_leaf_ids(dX).cpu().numpy()
+    df.check_status()
+    assert np.array_equal(ids, want_ids), f"{(ids != want_ids).sum()} leaf ids differ"
+    got = df.predict(dX).cpu().numpy()
+    df.check_status()
+    ok = ~np.isnan(want)
+    assert_predictions_close(got[ok], want[ok])
+    assert df.info().reserved[0] > 0          # key ties were hit and resolved exactly
+    n = min(777, rows)
+    part = df.predict_partial(dX[:n])
+    again = df.finalize(part).cpu().numpy()
+    assert_predictions_close(again[ok[:n]], want[:n][ok[:n]])
+    # explicit tree chunks and a padded row stride
+    chunked = kernels.DeviceForest(forest, representation="auto", tree_chunks=3, batch_hint=len(X))
+    wide = torch.zeros((len(X), forest.num_features + 3), device="cuda")
+    wide[:, :forest.num_features] = dX
+    got2 = chunked.predict(wide[:, :forest.num_features]).cpu().numpy()
+    chunked.check_status()
+    assert_predictions_close(got2[ok], want[ok])
+    # the fp32 global-memory walk of the same forest agrees
+    plain = kernels.DeviceForest(forest, representation="sparse", batch_hint=len(X))
+    assert plain.info().schedule.feature_bits == 32
+    assert_predictions_close(plain.predict(dX).cpu().numpy()[ok], want[ok])
 
 
 @pytest.mark.parametrize("mode", ["BRANCH_LT", "BRANCH_GEQ"])

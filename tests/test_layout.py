@@ -123,10 +123,36 @@ def test_sixteen_bit_key_layout_is_exact_including_ties(name):
     assert info.num_groups == (forest.num_trees + 31) // 32
 
 
+@pytest.mark.parametrize("trees", [1, 7, 24])
+def test_deep_tree_key_layout_is_exact_including_ties(trees):
+    """Deep trees (9..12 levels): one complete tree per stage, rows as 16-bit keys, two
+    trees per pair.  Same exactness requirement as the wide-row layout."""
+    forest, X = small_config("c5", rows=300, trees=trees)
+    X = X.copy()
+    split = np.nonzero(forest.left >= 0)[0]
+    for i in range(250):
+        g = split[(i * 101) % len(split)]
+        X[i % len(X), forest.feat[g]] = forest.thr[g]
+    for i in range(6, 40):                      # ties at roots are always reached
+        g = forest.tree_off[i % trees]
+        X[i, forest.feat[g]] = forest.thr[g]
+    X[3, :] = np.nan
+    X[4, 0] = np.inf
+    X[5, 1] = -np.inf
+    want_pred, want = oracle.predict(forest, X, leaf_ids=True)
+    ids, sums, info = kernels.host_layout_check(forest, X, representation="reorg", feature_bits=16)
+    assert np.array_equal(ids, want)
+    assert info.max_depth > 8 and info.num_groups == (forest.num_trees + 1) // 2
+    assert info.schedule.feature_bits == 16
+    assert info.reserved[0] >= 5   # ties were exercised
+    np.testing.assert_allclose(sums[:, 0] + forest.initial_value, want_pred, rtol=1e-5, atol=1e-6)
+
+
 def test_sixteen_bit_keys_refuse_what_they_cannot_hold():
-    deep, _ = small_config("c5", rows=1)        # 12 levels: planes would not fit a stage
+    # 13 levels: a whole-tree stage would need 32 KB planes
+    chain = synth.generate_forest(5, 2, 13, 4, 0.3, 0.1, synth.Marginal("uniform01", 4))
     with pytest.raises(kernels.TbkError, match="deeper"):
-        kernels.host_layout_check(deep, None, representation="reorg", feature_bits=16)
+        kernels.host_layout_check(chain, None, representation="reorg", feature_bits=16)
     multi, _ = small_config("c4", rows=1)
     with pytest.raises(kernels.TbkError, match="single-output"):
         kernels.host_layout_check(multi, None, representation="reorg", feature_bits=16)

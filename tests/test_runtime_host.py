@@ -48,8 +48,10 @@ def test_bad_inputs_report_errors_instead_of_aborting(tmp_path):
     ctx2 = treebeard.TreebeardContext(str(bad), "", options)
     with pytest.raises(treebeard.TreebeardRuntimeError, match="JSON"):
         ctx2.BuildHIRRepresentation()
-    with pytest.raises(treebeard.TreebeardRuntimeError, match="no LLVM"):
-        ctx.DumpLLVMIR(str(tmp_path / "x.ll"))
+    # dumping a model that cannot be read fails on the model, and writes nothing
+    with pytest.raises(treebeard.TreebeardRuntimeError, match="cannot open"):
+        ctx.DumpLLVMIR(str(tmp_path / "x.tbmodel"))
+    assert not (tmp_path / "x.tbmodel").exists()
 
 
 def test_unknown_objective_is_an_error(tmp_path):

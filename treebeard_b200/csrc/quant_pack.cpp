@@ -6,6 +6,31 @@
 
 namespace tb {
 
+std::string quant_feature_ranges(const Forest &f, std::vector<float> *lo_out, std::vector<float> *scale_out) {
+  const int F = f.num_features;
+  std::vector<float> lo(F + 1, std::numeric_limits<float>::infinity());
+  std::vector<float> hi(F + 1, -std::numeric_limits<float>::infinity());
+  for (int64_t g = 0; g < f.num_nodes(); ++g) {
+    if (!std::isfinite(f.thr[g])) return "non-finite threshold or leaf value";
+    if (f.is_leaf(g)) continue;
+    lo[f.feat[g]] = std::min(lo[f.feat[g]], f.thr[g]);
+    hi[f.feat[g]] = std::max(hi[f.feat[g]], f.thr[g]);
+  }
+  lo_out->assign(F + 1, 0.f);
+  scale_out->assign(F + 1, 0.f);
+  for (int i = 0; i < F; ++i) {
+    if (!(hi[i] >= lo[i])) continue; // feature not used by any split
+    (*lo_out)[i] = lo[i];
+    // a single threshold needs no range: any huge slope separates everything but x == t
+    // 65531 (not 65532) keeps the key of the largest threshold at >= 1 under rounding, so
+    // that it never ties with the saturated key 0 of everything above it
+    float s = hi[i] > lo[i] ? 65531.0f / (hi[i] - lo[i]) : 0x1p40f;
+    if (!std::isfinite(s) || s <= 0.f) s = 0x1p40f;
+    (*scale_out)[i] = s;
+  }
+  return "";
+}
+
 std::string pack_quant(const Forest &f, QuantForest *out) {
   std::string err = validate(f);
   if (!err.empty()) return err;
@@ -22,26 +47,8 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
   q.num_trees = T;
   q.num_nodes = f.num_nodes();
 
-  std::vector<float> lo(F + 1, std::numeric_limits<float>::infinity());
-  std::vector<float> hi(F + 1, -std::numeric_limits<float>::infinity());
-  for (int64_t g = 0; g < f.num_nodes(); ++g) {
-    if (!std::isfinite(f.thr[g])) return "non-finite threshold or leaf value";
-    if (f.is_leaf(g)) continue;
-    lo[f.feat[g]] = std::min(lo[f.feat[g]], f.thr[g]);
-    hi[f.feat[g]] = std::max(hi[f.feat[g]], f.thr[g]);
-  }
-  q.lo.assign(F + 1, 0.f);
-  q.scale.assign(F + 1, 0.f);
-  for (int i = 0; i < F; ++i) {
-    if (!(hi[i] >= lo[i])) continue; // feature not used by any split
-    q.lo[i] = lo[i];
-    // a single threshold needs no range: any huge slope separates everything but x == t
-    // 65531 (not 65532) keeps the key of the largest threshold at >= 1 under rounding, so
-    // that it never ties with the saturated key 0 of everything above it
-    float s = hi[i] > lo[i] ? 65531.0f / (hi[i] - lo[i]) : 0x1p40f;
-    if (!std::isfinite(s) || s <= 0.f) s = 0x1p40f;
-    q.scale[i] = s;
-  }
+  err = quant_feature_ranges(f, &q.lo, &q.scale);
+  if (!err.empty()) return err;
 
   std::vector<int32_t> depth(T);
   for (int64_t t = 0; t < T; ++t) {

@@ -75,6 +75,11 @@ inline uint16_t quant_key(float v, float lo, float scale) {
   return (uint16_t)fl;
 }
 
+// Per-feature key parameters (entries 0..num_features; the last belongs to the sentinel
+// feature): lo = smallest threshold of the feature, scale = a_f above.  Fails on a
+// non-finite threshold or leaf value.
+std::string quant_feature_ranges(const Forest &f, std::vector<float> *lo, std::vector<float> *scale);
+
 // Empty string on success.  Fails (so that the caller can fall back to another layout)
 // for multiclass forests, trees deeper than kQuantMaxDepth, or non-finite thresholds.
 std::string pack_quant(const Forest &f, QuantForest *out);

@@ -3,9 +3,11 @@
 #include "../../include/tbk.h"
 #include "pack.h"
 #include "quant_pack.h"
+#include "deep_pack.h"
 #include "schedule.h"
 #include "walk_kernels.cuh"
 #include "walk_quant.cuh"
+#include "walk_deep.cuh"
 
 #include <algorithm>
 #include <cstdarg>
@@ -66,6 +68,10 @@ struct tbk_forest {
   tb::DevQuantGroup *d_qgroups = nullptr;
   int32_t *d_qtree_index = nullptr, *d_qorig = nullptr;
   unsigned long long *d_ties = nullptr;
+  // one-tree-per-stage layout (deep trees); shares the device buffers of the key layout
+  bool deep = false;
+  tb::DeepForest df;
+  int deep_row_warps = 0, deep_slots = 0;
   // host pipeline
   float *d_in[2] = {nullptr, nullptr};
   unsigned char *d_res[2] = {nullptr, nullptr};
@@ -227,6 +233,121 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   return TBK_OK;
 }
 
+// Shared-memory plan of the deep-tree kernel: the most row warps (even, at most 16 -- one
+// block per SM either way, and more rows per tile mean fewer passes over the forest) whose
+// key tile leaves room for a ring of at least 4 whole-tree pieces.
+bool deep_plan(int num_features, int max_depth, int smem_limit, int *row_warps, int *slots) {
+  const int64_t slot = 4ll << std::max(max_depth, tb::kDeepMinDepth);
+  for (int rw = 16; rw >= 4; rw -= 2) {
+    const int64_t keys = (int64_t)(num_features + 1) * 64 * rw;
+    const int64_t room = (int64_t)smem_limit - 128 - keys;
+    const int64_t s = std::min<int64_t>(tb::kDeepMaxSlots, room / slot);
+    if (s >= 4) {
+      *row_warps = rw;
+      *slots = (int)s;
+      return true;
+    }
+  }
+  return false;
+}
+int deep_smem_bytes(const tbk_forest *f) {
+  return 128 + f->deep_slots * (4 << std::max(f->df.max_depth, tb::kDeepMinDepth)) +
+         (f->df.num_features + 1) * 64 * f->deep_row_warps;
+}
+
+// One prediction with the deep-tree kernel (one block per 32 x row_warps rows).
+int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
+             float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot) {
+  const auto &q = f->df;
+  const int64_t G = (int64_t)q.pairs.size();
+  // small batches: fewer row warps per block, so that the tiles still cover the SMs
+  int rw = f->deep_row_warps;
+  while (rw > 4 && (n_rows + 32 * rw - 1) / (32 * rw) < f->num_sms) rw -= 2;
+  const int64_t rows_per_block = 32 * rw;
+  const int64_t grid_x = (n_rows + rows_per_block - 1) / rows_per_block;
+  int64_t chunks = 1;
+  if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
+  else if (grid_x < (int64_t)f->num_sms) chunks = ((int64_t)f->num_sms + grid_x - 1) / grid_x;
+  chunks = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(chunks, G), 65535));
+  const int gpc = (int)((G + chunks - 1) / chunks);
+  chunks = (G + gpc - 1) / gpc;
+  tb::LaunchPlan plan;
+  plan.row_warps = rw;
+  plan.tree_threads = 1;
+  plan.rows_per_lane = 1;
+  plan.chunks = (int32_t)chunks;
+  plan.groups_per_chunk = gpc;
+  plan.staged = 1;
+  plan.cache_rows = 1;
+  plan.stage_bytes = 4u << std::max(q.max_depth, tb::kDeepMinDepth);
+  plan.smem_bytes = deep_smem_bytes(f);
+  plan.threads = 32 * rw;
+  plan.grid_x = grid_x;
+  f->last_plan = plan;
+
+  const bool need_partials = mode == kPartial || (mode == kPredict && chunks > 1);
+  float *partial_dst = nullptr;
+  if (need_partials) {
+    if (mode == kPartial && chunks == 1) {
+      partial_dst = d_partial;
+    } else {
+      const size_t need = ((size_t)chunks * n_rows * sizeof(float) + 255) & ~(size_t)255;
+      int rc = ensure_scratch(f, 2 * need);
+      if (rc) return rc;
+      partial_dst = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(f->d_scratch) + (size_t)slot * (f->scratch_bytes / 2));
+    }
+  }
+  tb::DeepParams p{};
+  p.node_plane = f->d_qnode;
+  p.leaf_plane = f->d_qleaf;
+  p.exact_plane = f->d_qexact;
+  p.pairs = f->d_qgroups;
+  p.tree_index = f->d_qtree_index;
+  p.orig_leaf = f->d_qorig;
+  p.lo = f->d_qlo;
+  p.scale = f->d_qscale;
+  p.rows = d_rows;
+  p.n_rows = n_rows;
+  p.ld = ld;
+  p.partial = partial_dst;
+  p.out = d_out;
+  p.write_partial = need_partials ? 1 : 0;
+  p.leaf_ids = mode == kLeafIds ? d_leaf_ids : nullptr;
+  p.num_trees = q.num_trees;
+  p.num_pairs = (int32_t)G;
+  p.pairs_per_chunk = gpc;
+  p.num_features = q.num_features;
+  p.transform = q.transform;
+  p.initial_value = (float)q.initial_value;
+  p.ring_slots = f->deep_slots;
+  p.slot_bytes = plan.stage_bytes;
+  p.key_stride = 64u * (uint32_t)f->deep_row_warps; // the tile keeps its full width whatever rw is
+  p.status = f->d_status;
+  p.tie_count = f->d_ties;
+  CUDA_TRY(cudaFuncSetAttribute((const void *)tb::tb_walk_deep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
+  if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
+  dim3 grid((unsigned)grid_x, (unsigned)chunks);
+  tb::tb_walk_deep_kernel<<<grid, plan.threads, plan.smem_bytes, stream>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  ++f->launches;
+  const int tpb = 256;
+  if (mode == kPredict && chunks > 1) {
+    tb::tb_finalize_kernel<<<(unsigned)((n_rows + tpb - 1) / tpb), tpb, 0, stream>>>(
+        partial_dst, (int)chunks, n_rows, 1, 0, (float)q.initial_value, q.transform, d_out, TBK_OUT_F32);
+    CUDA_TRY(cudaGetLastError());
+    ++f->launches;
+  } else if (mode == kPartial && chunks > 1) {
+    tb::tb_sum_partials_kernel<<<(unsigned)((n_rows + tpb - 1) / tpb), tpb, 0, stream>>>(partial_dst, (int)chunks, n_rows, d_partial);
+    CUDA_TRY(cudaGetLastError());
+    ++f->launches;
+  }
+  if (f->timing) {
+    CUDA_TRY(cudaEventRecord(f->ev1, stream));
+    f->ev_pending = true;
+  }
+  return TBK_OK;
+}
+
 // One prediction over device-resident rows.
 int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
         int32_t out_kind, float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot = 0) {
@@ -241,6 +362,7 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
   }
   CUDA_TRY(cudaSetDevice(f->device));
   if (f->quant) return run_quant(f, mode, d_rows, n_rows, ld, d_out, d_partial, d_leaf_ids, stream, slot);
+  if (f->deep) return run_deep(f, mode, d_rows, n_rows, ld, d_out, d_partial, d_leaf_ids, stream, slot);
 
   tb::ForestShape shape{pk.num_features, pk.num_classes, (int64_t)pk.groups.size(), pk.max_group_bytes,
                         (int32_t)pk.lut.size(), pk.representation, pk.tile_size};
@@ -335,6 +457,45 @@ int check_status(tbk_forest *f) {
   return TBK_OK;
 }
 
+// Uploads the planes of a 16-bit-key layout (quant_pack.h / deep_pack.h) and fills the
+// threshold keys on the device, so that thresholds and row values are quantised by the
+// very same arithmetic.
+int upload_key_planes(tbk_forest *f, const std::vector<uint32_t> &node, const std::vector<float> &leaf,
+                      const std::vector<float> &exact, const std::vector<int32_t> &orig,
+                      const std::vector<tb::QuantGroup> &groups, const std::vector<int32_t> &tree_index,
+                      const std::vector<float> &lo, const std::vector<float> &scale, int num_features) {
+  const size_t n = node.size();
+  static_assert(sizeof(tb::QuantGroup) == sizeof(tb::DevQuantGroup), "group metadata layout");
+  CUDA_TRY(cudaMalloc(&f->d_qnode, n * 4));
+  CUDA_TRY(cudaMalloc(&f->d_qleaf, n * 4));
+  CUDA_TRY(cudaMalloc(&f->d_qexact, n * 4));
+  CUDA_TRY(cudaMalloc(&f->d_qorig, n * 4));
+  CUDA_TRY(cudaMalloc(&f->d_qgroups, groups.size() * sizeof(tb::QuantGroup)));
+  CUDA_TRY(cudaMalloc(&f->d_qtree_index, tree_index.size() * 4));
+  // lo / scale are read with 16-byte loads: pad to a multiple of 4 entries
+  const size_t nf = ((size_t)num_features + 1 + 3) / 4 * 4;
+  CUDA_TRY(cudaMalloc(&f->d_qlo, nf * 4));
+  CUDA_TRY(cudaMalloc(&f->d_qscale, nf * 4));
+  CUDA_TRY(cudaMemset(f->d_qlo, 0, nf * 4));
+  CUDA_TRY(cudaMemset(f->d_qscale, 0, nf * 4));
+  CUDA_TRY(cudaMalloc(&f->d_ties, 128));
+  CUDA_TRY(cudaMemset(f->d_ties, 0, 128));
+  CUDA_TRY(cudaMemcpy(f->d_qnode, node.data(), n * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(f->d_qleaf, leaf.data(), n * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(f->d_qexact, exact.data(), n * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(f->d_qorig, orig.data(), n * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(f->d_qgroups, groups.data(), groups.size() * sizeof(tb::QuantGroup), cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(f->d_qtree_index, tree_index.data(), tree_index.size() * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(f->d_qlo, lo.data(), lo.size() * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(f->d_qscale, scale.data(), scale.size() * 4, cudaMemcpyHostToDevice));
+  tb::tb_quant_fill_keys<<<(unsigned)((n + 255) / 256), 256>>>(f->d_qnode, f->d_qexact, f->d_qlo, f->d_qscale,
+                                                             (unsigned long long)n, num_features);
+  CUDA_TRY(cudaGetLastError());
+  CUDA_TRY(cudaDeviceSynchronize());
+  ++f->launches;
+  return TBK_OK;
+}
+
 void free_pipeline(tbk_forest *f) {
   for (int i = 0; i < 2; ++i) {
     if (f->d_in[i]) cudaFree(f->d_in[i]);
@@ -406,7 +567,14 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
   const int ts = f->user.tile_size <= 0 ? 1 : f->user.tile_size;
   // an fp32 tile of 32 rows (plus the sentinel column) must fit beside a little metadata
   const bool fp32_tile_fits = (int64_t)(host.num_features + 1) * 128 + 1024 <= f->max_smem_optin;
-  bool want_quant = bits == 16 ||
+  {
+    const std::string verr = tb::validate(host);
+    if (!verr.empty()) return bail(fail(TBK_ERR_INVALID, "%s", verr.c_str()));
+  }
+  int max_depth = 0;
+#pragma omp parallel for reduction(max : max_depth) schedule(dynamic, 64)
+  for (int64_t t = 0; t < T; ++t) max_depth = std::max(max_depth, (int)tb::tree_depth(host, t));
+  bool want_quant = (bits == 16 && max_depth <= tb::kQuantMaxDepth) ||
                     (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits);
   if (want_quant) {
     std::string qerr = tb::pack_quant(host, &f->qf);
@@ -416,6 +584,48 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
       if (bits == 16) return bail(fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str()));
       want_quant = false;
       f->qf = tb::QuantForest();
+    }
+  }
+  // ---- deep trees: whole-tree stages over a key tile (deep_pack.h)
+  if (!want_quant && host.num_classes == 0 && ts == 1 && bits != 32 &&
+      (bits == 16 || f->user.representation == TBK_REP_AUTO)) {
+    int rw = 0, slots = 0;
+    const bool fits = max_depth > tb::kQuantMaxDepth && max_depth <= tb::kDeepMaxDepth &&
+                      deep_plan(host.num_features, max_depth, f->max_smem_optin, &rw, &slots);
+    if (fits) {
+      std::string derr = tb::pack_deep(host, &f->df);
+      if (derr.empty()) {
+        auto &q = f->df;
+        f->deep = true;
+        f->deep_row_warps = rw;
+        f->deep_slots = slots;
+        f->user.representation = TBK_REP_REORG;
+        f->packed.representation = tb::kReorg;
+        f->packed.tile_size = 1;
+        f->packed.num_features = q.num_features;
+        f->packed.transform = q.transform;
+        f->packed.initial_value = q.initial_value;
+        f->packed.num_trees = q.num_trees;
+        f->packed.num_nodes = q.num_nodes;
+        f->packed.max_depth = q.max_depth;
+        int urc = upload_key_planes(f, q.node_plane, q.leaf_plane, q.exact_plane, q.orig_leaf, q.pairs, q.tree_index,
+                                    q.lo, q.scale, q.num_features);
+        if (urc != TBK_OK) return bail(urc);
+        std::vector<uint32_t>().swap(q.node_plane);
+        std::vector<float>().swap(q.leaf_plane);
+        std::vector<float>().swap(q.exact_plane);
+        std::vector<int32_t>().swap(q.orig_leaf);
+        tb::LaunchPlan &pl = f->last_plan;
+        pl.row_warps = rw; pl.tree_threads = 1; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
+        pl.stage_bytes = 4u << std::max(q.max_depth, tb::kDeepMinDepth); pl.smem_bytes = deep_smem_bytes(f); pl.threads = 32 * rw;
+        *out = f;
+        return TBK_OK;
+      }
+      if (bits == 16) return bail(fail(TBK_ERR_UNSUPPORTED, "%s", derr.c_str()));
+      f->df = tb::DeepForest();
+    } else if (bits == 16) {
+      return bail(fail(TBK_ERR_UNSUPPORTED, "16-bit feature keys: neither key layout fits this forest (depth %d, %d features)",
+                       max_depth, host.num_features));
     }
   }
   if (rep == TBK_REP_AUTO) rep = TBK_REP_SPARSE;
@@ -432,36 +642,9 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
     f->packed.num_trees = q.num_trees;
     f->packed.num_nodes = q.num_nodes;
     f->packed.max_depth = q.max_depth;
-    const size_t n = q.node_plane.size();
-    static_assert(sizeof(tb::QuantGroup) == sizeof(tb::DevQuantGroup), "group metadata layout");
-    CUDA_TRY_F(cudaMalloc(&f->d_qnode, n * 4));
-    CUDA_TRY_F(cudaMalloc(&f->d_qleaf, n * 4));
-    CUDA_TRY_F(cudaMalloc(&f->d_qexact, n * 4));
-    CUDA_TRY_F(cudaMalloc(&f->d_qorig, n * 4));
-    CUDA_TRY_F(cudaMalloc(&f->d_qgroups, q.groups.size() * sizeof(tb::QuantGroup)));
-    CUDA_TRY_F(cudaMalloc(&f->d_qtree_index, q.tree_index.size() * 4));
-    // lo / scale are read with 16-byte loads: pad to a multiple of 4 entries
-    const size_t nf = ((size_t)q.num_features + 1 + 3) / 4 * 4;
-    CUDA_TRY_F(cudaMalloc(&f->d_qlo, nf * 4));
-    CUDA_TRY_F(cudaMalloc(&f->d_qscale, nf * 4));
-    CUDA_TRY_F(cudaMemset(f->d_qlo, 0, nf * 4));
-    CUDA_TRY_F(cudaMemset(f->d_qscale, 0, nf * 4));
-    CUDA_TRY_F(cudaMalloc(&f->d_ties, 128));
-    CUDA_TRY_F(cudaMemset(f->d_ties, 0, 128));
-    CUDA_TRY_F(cudaMemcpy(f->d_qnode, q.node_plane.data(), n * 4, cudaMemcpyHostToDevice));
-    CUDA_TRY_F(cudaMemcpy(f->d_qleaf, q.leaf_plane.data(), n * 4, cudaMemcpyHostToDevice));
-    CUDA_TRY_F(cudaMemcpy(f->d_qexact, q.exact_plane.data(), n * 4, cudaMemcpyHostToDevice));
-    CUDA_TRY_F(cudaMemcpy(f->d_qorig, q.orig_leaf.data(), n * 4, cudaMemcpyHostToDevice));
-    CUDA_TRY_F(cudaMemcpy(f->d_qgroups, q.groups.data(), q.groups.size() * sizeof(tb::QuantGroup), cudaMemcpyHostToDevice));
-    CUDA_TRY_F(cudaMemcpy(f->d_qtree_index, q.tree_index.data(), q.tree_index.size() * 4, cudaMemcpyHostToDevice));
-    CUDA_TRY_F(cudaMemcpy(f->d_qlo, q.lo.data(), q.lo.size() * 4, cudaMemcpyHostToDevice));
-    CUDA_TRY_F(cudaMemcpy(f->d_qscale, q.scale.data(), q.scale.size() * 4, cudaMemcpyHostToDevice));
-    // threshold keys come from the same device arithmetic that will quantise the rows
-    tb::tb_quant_fill_keys<<<(unsigned)((n + 255) / 256), 256>>>(f->d_qnode, f->d_qexact, f->d_qlo, f->d_qscale,
-                                                               (unsigned long long)n, q.num_features);
-    CUDA_TRY_F(cudaGetLastError());
-    CUDA_TRY_F(cudaDeviceSynchronize());
-    ++f->launches;
+    int urc = upload_key_planes(f, q.node_plane, q.leaf_plane, q.exact_plane, q.orig_leaf, q.groups, q.tree_index,
+                                q.lo, q.scale, q.num_features);
+    if (urc != TBK_OK) return bail(urc);
     // host copies of the big planes are no longer needed
     std::vector<uint32_t>().swap(f->qf.node_plane);
     std::vector<float>().swap(f->qf.leaf_plane);
@@ -542,8 +725,9 @@ int tbk_forest_get_info(const tbk_forest *f, tbk_forest_info *info) {
   const auto &p = f->packed;
   info->num_trees = p.num_trees;
   info->num_nodes = p.num_nodes;
-  info->num_groups = f->quant ? (int64_t)f->qf.groups.size() : (int64_t)p.groups.size();
-  info->packed_bytes = f->quant ? (int64_t)(f->qf.groups.empty() ? 0 : 8 * (f->qf.groups.back().elem_off + (uint64_t)f->qf.groups.back().slots * tb::kQuantCols)) :
+  info->num_groups = f->quant ? (int64_t)f->qf.groups.size() : f->deep ? (int64_t)f->df.pairs.size() : (int64_t)p.groups.size();
+  info->packed_bytes = f->deep ? (int64_t)(f->df.pairs.empty() ? 0 : 8 * (f->df.pairs.back().elem_off + 2ull * f->df.pairs.back().slots)) :
+                       f->quant ? (int64_t)(f->qf.groups.empty() ? 0 : 8 * (f->qf.groups.back().elem_off + (uint64_t)f->qf.groups.back().slots * tb::kQuantCols)) :
                        p.groups.empty() ? 0 : (int64_t)(p.groups.back().byte_off +
       (((uint64_t)p.groups.back().slots * tb::kGroupTrees * p.tile_bytes + 15) & ~15ull));
   info->max_depth = p.max_depth;
@@ -559,25 +743,17 @@ int tbk_forest_get_info(const tbk_forest *f, tbk_forest_info *info) {
   info->schedule.tree_threads = pl.tree_threads;
   info->schedule.tree_chunks = pl.chunks;
   info->schedule.cache_trees = pl.staged ? 1 : 2;
-  info->schedule.feature_bits = f->quant ? 16 : 32;
+  info->schedule.feature_bits = (f->quant || f->deep) ? 16 : 32;
   info->staged = pl.staged;
   info->smem_bytes = pl.smem_bytes;
   info->threads_per_block = pl.threads;
-  if (f->quant && f->d_ties) {
+  if ((f->quant || f->deep) && f->d_ties) {
     // key ties resolved on exact values so far (statistics; synchronises with the device)
     unsigned long long ties = 0;
     if (cudaMemcpy(&ties, f->d_ties, 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
       info->reserved[0] = (int32_t)(ties & 0x7fffffff);
       info->reserved[1] = (int32_t)(ties >> 31);
     }
-#ifdef TBK_QUANT_PROF
-    unsigned long long prof[9] = {0};
-    if (cudaMemcpy(prof, f->d_ties + 1, 64, cudaMemcpyDeviceToHost) == cudaSuccess && prof[7] > 0) {
-      // average cycles per block: staging, then the six phases of the group loop
-      std::fprintf(stderr, "[quant prof] blocks %llu  stage %llu | tick0 %llu  wait_node %llu  walk %llu  release %llu  wait_leaf %llu  leaf+release %llu\n",
-                   prof[7], prof[0] / prof[7], prof[1] / prof[7], prof[2] / prof[7], prof[3] / prof[7], prof[4] / prof[7], prof[5] / prof[7], prof[6] / prof[7]);
-    }
-#endif
   }
   return TBK_OK;
 }
@@ -771,7 +947,7 @@ extern "C" int tbk_predict_noalloc(tbk_forest *f, const float *d_rows, int64_t n
   if (!f) return fail(TBK_ERR_INVALID, "null forest");
   std::lock_guard<std::mutex> lock(f->mu);
   const auto &pk = f->packed;
-  if (f->quant) return fail(TBK_ERR_UNSUPPORTED, "tbk_predict_noalloc does not cover the 16-bit key layout");
+  if (f->quant || f->deep) return fail(TBK_ERR_UNSUPPORTED, "tbk_predict_noalloc does not cover the 16-bit key layouts");
   if (n_rows < 0 || ld < pk.num_features) return fail(TBK_ERR_INVALID, "ld (%lld) is smaller than the row size (%d)", (long long)ld, pk.num_features);
   if (n_rows == 0) return TBK_OK;
   if (!d_rows || !d_out) return fail(TBK_ERR_INVALID, "null pointer");
@@ -857,20 +1033,38 @@ int tbk_host_layout_check(const tbk_forest_arrays *fa, const tbk_schedule *sched
   host.initial_value = fa->initial_value;
   host.num_features = fa->num_features;
   if (schedule && schedule->feature_bits == 16) {
-    tb::QuantForest q;
-    std::string qerr = tb::pack_quant(host, &q);
-    if (!qerr.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str());
-    int64_t ties = 0;
-    if (rows && n_rows > 0) tb::walk_quant_on_host(q, rows, n_rows, ld, leaf_ids, sums, &ties);
+    // the key layouts: groups of 32 trees up to 8 levels, whole-tree stages beyond
+    int max_depth = 0;
+    {
+      const std::string verr = tb::validate(host);
+      if (!verr.empty()) return fail(TBK_ERR_INVALID, "%s", verr.c_str());
+      for (int64_t t = 0; t < T; ++t) max_depth = std::max(max_depth, (int)tb::tree_depth(host, t));
+    }
+    int64_t ties = 0, groups = 0, elems = 0;
+    if (max_depth <= tb::kQuantMaxDepth) {
+      tb::QuantForest q;
+      std::string qerr = tb::pack_quant(host, &q);
+      if (!qerr.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str());
+      if (rows && n_rows > 0) tb::walk_quant_on_host(q, rows, n_rows, ld, leaf_ids, sums, &ties);
+      groups = (int64_t)q.groups.size();
+      elems = (int64_t)q.node_plane.size();
+    } else {
+      tb::DeepForest q;
+      std::string qerr = tb::pack_deep(host, &q);
+      if (!qerr.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str());
+      if (rows && n_rows > 0) tb::walk_deep_on_host(q, rows, n_rows, ld, leaf_ids, sums, &ties);
+      groups = (int64_t)q.pairs.size();
+      elems = (int64_t)q.node_plane.size();
+    }
     if (info) {
       std::memset(info, 0, sizeof *info);
-      info->num_trees = q.num_trees;
-      info->num_nodes = q.num_nodes;
-      info->num_groups = (int64_t)q.groups.size();
-      info->packed_bytes = (int64_t)q.node_plane.size() * 8;
-      info->max_depth = q.max_depth;
-      info->num_features = q.num_features;
-      info->transform = q.transform;
+      info->num_trees = T;
+      info->num_nodes = N;
+      info->num_groups = groups;
+      info->packed_bytes = elems * 8;
+      info->max_depth = max_depth;
+      info->num_features = host.num_features;
+      info->transform = host.transform;
       info->schedule.representation = TBK_REP_REORG;
       info->schedule.tile_size = 1;
       info->schedule.feature_bits = 16;

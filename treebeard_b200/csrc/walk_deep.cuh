@@ -1,0 +1,269 @@
+// Walk kernel for the one-tree-per-stage layout (deep_pack.h): forests of deep trees.
+//
+// One block = RW warps = one tile of 32*RW rows, staged ONCE as 16-bit keys and kept for
+// the whole forest.  Lane = row: every thread walks its own row through BOTH trees of a
+// pair in lock-step (two independent dependence chains per thread), so all threads of the
+// block read the same two node planes.  The planes stream through a ring of whole-tree
+// pieces (node plane of tree 0, of tree 1, leaf plane of tree 0, of tree 1; 16 KB each at
+// 12 levels) filled by cp.async.bulk copies that different warps issue, so that several
+// are in flight while a pair is walked; a block-wide barrier after each phase frees two
+// slots.  Sums stay in the owning thread's register: there is no cross-thread reduction.
+//
+// Keys of two row warps are interleaved (feature-major, 128 bytes per warp pair: word j =
+// row j of the even warp | row j of the odd warp << 16), so a warp's key load touches 32
+// distinct banks.  The children of a node are one aligned 8-byte pair, fetched while the
+// key comparison is in flight.  A key tie is only flagged on the fast path; the flagged
+// (row, tree) is re-walked with exact fp32 comparisons at the tied steps.
+//
+// Reference counterparts: src/mlir/CodeGenStateMachine.cpp:149-243 (scalar walk),
+// src/mlir/WalkDecisionTreeLoweringPass.cpp:24-53 (fixed-depth walk of padded trees),
+// src/gpu/GPURepresentations.cpp:279-399 (row cache) and :630-715 (tree cache).
+#pragma once
+#include "walk_quant.cuh"
+
+namespace tb {
+
+struct DeepParams {
+  const uint32_t *node_plane;
+  const float *leaf_plane;
+  const float *exact_plane;
+  const DevQuantGroup *pairs;
+  const int32_t *tree_index;
+  const int32_t *orig_leaf;
+  const float *lo;
+  const float *scale;
+  const float *rows;
+  long long n_rows, ld;
+  float *partial;
+  void *out;
+  int32_t write_partial;
+  int32_t *leaf_ids;
+  long long num_trees;
+  int32_t num_pairs, pairs_per_chunk, num_features, transform;
+  float initial_value;
+  int32_t ring_slots;  // 4 .. 8
+  uint32_t slot_bytes; // 4 << max depth of the forest
+  uint32_t key_stride; // bytes per feature in the key tile: 64 * (row warps rounded up to even)
+  int32_t *status;
+  unsigned long long *tie_count;
+};
+
+constexpr int kDeepMaxSlots = 8;
+
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+
+// Fast walk of DEPTH levels of two trees.  base0 / base1: shared-memory addresses of the
+// node planes; returns the heap indices reached (in [2^DEPTH, 2^(DEPTH+1))) and whether
+// any key comparison on either path tied.
+template <int DEPTH>
+__device__ __forceinline__ void deep_walk(uint32_t base0, uint32_t base1, uint32_t key_lane, uint32_t ks,
+                                          uint32_t *i0_out, uint32_t *i1_out, bool *tie0, bool *tie1) {
+  uint32_t i0 = 1, i1 = 1;
+  uint32_t n0 = lds_u32(base0 + 4), n1 = lds_u32(base1 + 4);
+  bool t0 = false, t1 = false;
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {
+    const uint32_t kx0 = lds_u16(key_lane + (n0 >> 16) * ks);
+    const uint32_t kx1 = lds_u16(key_lane + (n1 >> 16) * ks);
+    uint2 c0 = make_uint2(0, 0), c1 = make_uint2(0, 0);
+    if (d + 1 < DEPTH) {
+      c0 = lds_u64(base0 + i0 * 8u);
+      c1 = lds_u64(base1 + i1 * 8u);
+    }
+    const uint32_t kt0 = n0 & 0xffffu, kt1 = n1 & 0xffffu;
+    const bool r0 = kx0 < kt0, r1 = kx1 < kt1;
+    t0 |= kx0 == kt0;
+    t1 |= kx1 == kt1;
+    i0 = 2u * i0 + (r0 ? 1u : 0u);
+    i1 = 2u * i1 + (r1 ? 1u : 0u);
+    n0 = r0 ? c0.y : c0.x;
+    n1 = r1 ? c1.y : c1.x;
+  }
+  *i0_out = i0;
+  *i1_out = i1;
+  *tie0 = t0;
+  *tie1 = t1;
+}
+
+__device__ __forceinline__ void deep_walk_any(uint32_t depth, uint32_t base0, uint32_t base1, uint32_t key_lane,
+                                              uint32_t ks, uint32_t *i0, uint32_t *i1, bool *t0, bool *t1) {
+  switch (depth) {
+  case 2: return deep_walk<2>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 3: return deep_walk<3>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 4: return deep_walk<4>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 5: return deep_walk<5>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 6: return deep_walk<6>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 7: return deep_walk<7>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 8: return deep_walk<8>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 9: return deep_walk<9>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 10: return deep_walk<10>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  case 11: return deep_walk<11>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  default: return deep_walk<12>(base0, base1, key_lane, ks, i0, i1, t0, t1);
+  }
+}
+
+// Re-walk of one (row, tree) behind a key tie: the staged keys decide wherever they can,
+// the tied comparisons read the exact fp32 values from global memory.
+__device__ __noinline__ uint32_t deep_walk_exact(uint32_t base, uint32_t key_lane, uint32_t ks, uint32_t depth,
+                                                 const float *exact_tree, const float *rowp) {
+  uint32_t i = 1;
+  for (uint32_t d = 0; d < depth; ++d) {
+    const uint32_t node = lds_u32(base + i * 4u);
+    const uint32_t f = node >> 16, kt = node & 0xffffu;
+    const uint32_t kx = lds_u16(key_lane + f * ks);
+    bool right = kx < kt;
+    if (kx == kt) right = !(__ldg(rowp + f) < __ldg(exact_tree + i));
+    i = 2u * i + (right ? 1u : 0u);
+  }
+  return i;
+}
+
+__global__ void __launch_bounds__(1024, 1) tb_walk_deep_kernel(const DeepParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int RW = blockDim.x >> 5;
+  const int F = p.num_features;
+  const int S = p.ring_slots;
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw); // [S]
+  unsigned char *ring = smem_raw + 128;
+  const uint32_t ring_s = smem_u32(ring);
+  const uint32_t keys_s = ring_s + (uint32_t)S * p.slot_bytes;
+  const uint32_t ks = p.key_stride;
+  const uint32_t key_lane = keys_s + (uint32_t)(warp >> 1) * 128u + (uint32_t)lane * 4u + (uint32_t)(warp & 1) * 2u;
+
+  const long long row = ((long long)blockIdx.x * RW + warp) * 32 + lane;
+  const bool live = row < p.n_rows;
+  const float *rowp = p.rows + (live ? row : 0) * p.ld;
+  const int g0 = blockIdx.y * p.pairs_per_chunk;
+  const int g1 = min(p.num_pairs, g0 + p.pairs_per_chunk);
+  const int P = 4 * (g1 - g0); // pieces of this block
+
+  if (tid == 0) {
+    for (int i = 0; i < S; ++i) mbar_init(&full[i], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  // piece 4k + j of the block: j = 0, 1 node planes of the pair's trees, j = 2, 3 leaf planes.
+  // Pieces are consumed in order, so slots and barrier phases advance by counters (S and RW
+  // are run-time values: no division on the hot path).
+  auto issue = [&](int piece, int slot) {
+    const DevQuantGroup gm = p.pairs[g0 + (piece >> 2)];
+    const int j = piece & 3;
+    const size_t off = (size_t)gm.elem_off + ((j & 1) ? gm.slots : 0u);
+    const void *src = j < 2 ? static_cast<const void *>(p.node_plane + off)
+                            : static_cast<const void *>(p.leaf_plane + off);
+    uint64_t *bar = &full[slot];
+    mbar_expect_tx(bar, gm.slots * 4u);
+    bulk_g2s(ring + (size_t)slot * p.slot_bytes, src, gm.slots * 4u, bar);
+  };
+  if (lane == 0 && warp < S && warp < P) issue(warp, warp);
+  if (RW < S && tid == 0)
+    for (int i = RW; i < S && i < P; ++i) issue(i, i);
+
+  // ---- stage this thread's row as keys
+  {
+    const bool vec = (F % 4 == 0) && (p.ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.rows) & 15) == 0);
+    if (vec) {
+      for (int f = 0; f < F; f += 4) {
+        const float4 x = live ? __ldg(reinterpret_cast<const float4 *>(rowp + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 lo = __ldg(reinterpret_cast<const float4 *>(p.lo + f));
+        const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + f));
+        sts_u16(key_lane + (uint32_t)f * ks, quant_key_dev(x.x, lo.x, sc.x));
+        sts_u16(key_lane + (uint32_t)(f + 1) * ks, quant_key_dev(x.y, lo.y, sc.y));
+        sts_u16(key_lane + (uint32_t)(f + 2) * ks, quant_key_dev(x.z, lo.z, sc.z));
+        sts_u16(key_lane + (uint32_t)(f + 3) * ks, quant_key_dev(x.w, lo.w, sc.w));
+      }
+    } else {
+      for (int f = 0; f < F; ++f)
+        sts_u16(key_lane + (uint32_t)f * ks, quant_key_dev(live ? __ldg(rowp + f) : 0.f, __ldg(p.lo + f), __ldg(p.scale + f)));
+    }
+    sts_u16(key_lane + (uint32_t)F * ks, 65535u); // sentinel feature
+  }
+  // (each thread reads back only the keys it wrote: no barrier is needed for the tile)
+
+  float acc = 0.f;
+  bool ok = true, failed = false;
+  unsigned ties = 0;
+  int slot = 0;          // ring slot of the next piece to consume
+  uint32_t parity = 0;   // phase of that slot's barrier
+  int issuer = 0;        // warp that issues the next refill
+  int next_piece = S;    // next piece to issue
+
+  // Takes the next piece: waits for it and returns its shared-memory address.
+  auto take = [&](int *slot_out) -> uint32_t {
+    const int s = slot;
+    if (ok) ok = warp_wait(&full[s], parity, lane);
+    *slot_out = s;
+    if (++slot == S) {
+      slot = 0;
+      parity ^= 1u;
+    }
+    return ring_s + (uint32_t)s * p.slot_bytes;
+  };
+  // A block-wide barrier (which also carries a wait failure to every thread, so that the
+  // exit is uniform) frees the two slots just consumed; two rotating warps refill them.
+  auto release = [&](int sa, int sb) {
+    failed = __syncthreads_or(!ok) != 0;
+    const int slots[2] = {sa, sb};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (!failed && next_piece < P && lane == 0 && warp == issuer) issue(next_piece, slots[i]);
+      ++next_piece;
+      if (++issuer == RW) issuer = 0;
+    }
+  };
+
+  for (int k = 0; k < g1 - g0; ++k) {
+    const DevQuantGroup gm = p.pairs[g0 + k];
+    const uint32_t depth = gm.depth;
+    uint32_t i0 = 0, i1 = 0;
+    int sa, sb;
+
+    const uint32_t n0 = take(&sa), n1 = take(&sb);
+    if (ok) {
+      bool t0, t1;
+      deep_walk_any(depth, n0, n1, key_lane, ks, &i0, &i1, &t0, &t1);
+      if (t0) {
+        i0 = deep_walk_exact(n0, key_lane, ks, depth, p.exact_plane + gm.elem_off, rowp);
+        ++ties;
+      }
+      if (t1) {
+        i1 = deep_walk_exact(n1, key_lane, ks, depth, p.exact_plane + gm.elem_off + gm.slots, rowp);
+        ++ties;
+      }
+    }
+    release(sa, sb);
+    if (failed) break;
+
+    const uint32_t l0 = take(&sa), l1 = take(&sb);
+    if (ok) {
+      const uint32_t j0 = i0 - gm.slots, j1 = i1 - gm.slots;
+      acc += lds_f32(l0 + j0 * 4u);
+      acc += lds_f32(l1 + j1 * 4u);
+      if (p.leaf_ids != nullptr && live) {
+        const int t0 = p.tree_index[(g0 + k) * 2], t1 = p.tree_index[(g0 + k) * 2 + 1];
+        if (t0 >= 0) p.leaf_ids[row * p.num_trees + t0] = p.orig_leaf[gm.elem_off + j0];
+        if (t1 >= 0) p.leaf_ids[row * p.num_trees + t1] = p.orig_leaf[gm.elem_off + gm.slots + j1];
+      }
+    }
+    release(sa, sb);
+    if (failed) break;
+  }
+  if (failed) {
+    if (tid == 0) atomicExch(p.status, 4);
+    return;
+  }
+  if (p.tie_count != nullptr && ties) atomicAdd(p.tie_count, (unsigned long long)ties);
+  if (p.leaf_ids != nullptr || !live) return;
+  if (p.write_partial)
+    p.partial[(long long)blockIdx.y * p.n_rows + row] = acc;
+  else
+    reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + acc, p.transform);
+}
+
+} // namespace tb
