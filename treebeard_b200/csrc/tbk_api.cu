@@ -238,16 +238,19 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
 // key tile leaves room for a ring of at least 4 whole-tree pieces.
 bool deep_plan(int num_features, int max_depth, int smem_limit, int *row_warps, int *slots) {
   const int64_t slot = 4ll << std::max(max_depth, tb::kDeepMinDepth);
-  for (int rw = 16; rw >= 4; rw -= 2) {
-    const int64_t keys = (int64_t)(num_features + 1) * 64 * rw;
-    const int64_t room = (int64_t)smem_limit - 128 - keys;
-    const int64_t s = std::min<int64_t>(tb::kDeepMaxSlots, room / slot);
-    if (s >= 4) {
-      *row_warps = rw;
-      *slots = (int)s;
-      return true;
+  // six slots hold a pair (four pieces) plus the node planes of the next one; with fewer
+  // the kernel still runs, without that prefetch
+  for (int want = 6; want >= 4; want -= 2)
+    for (int rw = 16; rw >= 4; rw -= 2) {
+      const int64_t keys = (int64_t)(num_features + 1) * 64 * rw;
+      const int64_t room = (int64_t)smem_limit - 128 - keys;
+      const int64_t s = std::min<int64_t>(tb::kDeepMaxSlots, room / slot);
+      if (s >= want) {
+        *row_warps = rw;
+        *slots = (int)s;
+        return true;
+      }
     }
-  }
   return false;
 }
 int deep_smem_bytes(const tbk_forest *f) {

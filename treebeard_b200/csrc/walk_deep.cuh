@@ -6,7 +6,7 @@
 // block read the same two node planes.  The planes stream through a ring of whole-tree
 // pieces (node plane of tree 0, of tree 1, leaf plane of tree 0, of tree 1; 16 KB each at
 // 12 levels) filled by cp.async.bulk copies that different warps issue, so that several
-// are in flight while a pair is walked; a block-wide barrier after each phase frees two
+// are in flight while a pair is walked; one block-wide barrier per pair frees its four
 // slots.  Sums stay in the owning thread's register: there is no cross-thread reduction.
 //
 // Keys of two row warps are interleaved (feature-major, 128 bytes per warp pair: word j =
@@ -59,6 +59,12 @@ __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
 // Fast walk of DEPTH levels of two trees.  base0 / base1: shared-memory addresses of the
 // node planes; returns the heap indices reached (in [2^DEPTH, 2^(DEPTH+1))) and whether
 // any key comparison on either path tied.
+// Upper levels (few distinct nodes per level: loads of a warp mostly coincide) fetch both
+// children while the key comparison is in flight; from level kDeepSpecLevels on, where the
+// lanes' nodes are scattered over the banks, only the chosen child is fetched (half the
+// shared-memory wavefronts of a pair load, at the price of a longer dependence chain).
+constexpr int kDeepSpecLevels = 5;
+
 template <int DEPTH>
 __device__ __forceinline__ void deep_walk(uint32_t base0, uint32_t base1, uint32_t key_lane, uint32_t ks,
                                           uint32_t *i0_out, uint32_t *i1_out, bool *tie0, bool *tie1) {
@@ -69,8 +75,9 @@ __device__ __forceinline__ void deep_walk(uint32_t base0, uint32_t base1, uint32
   for (int d = 0; d < DEPTH; ++d) {
     const uint32_t kx0 = lds_u16(key_lane + (n0 >> 16) * ks);
     const uint32_t kx1 = lds_u16(key_lane + (n1 >> 16) * ks);
+    const bool spec = d + 1 < DEPTH && d < kDeepSpecLevels;
     uint2 c0 = make_uint2(0, 0), c1 = make_uint2(0, 0);
-    if (d + 1 < DEPTH) {
+    if (spec) {
       c0 = lds_u64(base0 + i0 * 8u);
       c1 = lds_u64(base1 + i1 * 8u);
     }
@@ -80,8 +87,13 @@ __device__ __forceinline__ void deep_walk(uint32_t base0, uint32_t base1, uint32
     t1 |= kx1 == kt1;
     i0 = 2u * i0 + (r0 ? 1u : 0u);
     i1 = 2u * i1 + (r1 ? 1u : 0u);
-    n0 = r0 ? c0.y : c0.x;
-    n1 = r1 ? c1.y : c1.x;
+    if (spec) {
+      n0 = r0 ? c0.y : c0.x;
+      n1 = r1 ? c1.y : c1.x;
+    } else if (d + 1 < DEPTH) {
+      n0 = lds_u32(base0 + i0 * 4u);
+      n1 = lds_u32(base1 + i1 * 4u);
+    }
   }
   *i0_out = i0;
   *i1_out = i1;
@@ -122,7 +134,21 @@ __device__ __noinline__ uint32_t deep_walk_exact(uint32_t base, uint32_t key_lan
   return i;
 }
 
-__global__ void __launch_bounds__(1024, 1) tb_walk_deep_kernel(const DeepParams p) {
+// Bounded wait executed by every lane of the calling warp (no election, no shuffle).
+__device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t parity) {
+  for (uint32_t it = 0; it < kQWaitTries; ++it) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+                 " selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(bar_addr), "r"(parity), "r"(200u)
+                 : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int RW = blockDim.x >> 5;
@@ -195,9 +221,10 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_deep_kernel(const DeepParams 
   int next_piece = S;    // next piece to issue
 
   // Takes the next piece: waits for it and returns its shared-memory address.
+  const uint32_t full_s = smem_u32(full);
   auto take = [&](int *slot_out) -> uint32_t {
     const int s = slot;
-    if (ok) ok = warp_wait(&full[s], parity, lane);
+    if (ok) ok = mbar_wait_all_lanes(full_s + 8u * (uint32_t)s, parity);
     *slot_out = s;
     if (++slot == S) {
       slot = 0;
@@ -205,26 +232,14 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_deep_kernel(const DeepParams 
     }
     return ring_s + (uint32_t)s * p.slot_bytes;
   };
-  // A block-wide barrier (which also carries a wait failure to every thread, so that the
-  // exit is uniform) frees the two slots just consumed; two rotating warps refill them.
-  auto release = [&](int sa, int sb) {
-    failed = __syncthreads_or(!ok) != 0;
-    const int slots[2] = {sa, sb};
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (!failed && next_piece < P && lane == 0 && warp == issuer) issue(next_piece, slots[i]);
-      ++next_piece;
-      if (++issuer == RW) issuer = 0;
-    }
-  };
 
   for (int k = 0; k < g1 - g0; ++k) {
     const DevQuantGroup gm = p.pairs[g0 + k];
     const uint32_t depth = gm.depth;
-    uint32_t i0 = 0, i1 = 0;
-    int sa, sb;
+    uint32_t i0 = gm.slots, i1 = gm.slots;
+    int sl[4];
 
-    const uint32_t n0 = take(&sa), n1 = take(&sb);
+    const uint32_t n0 = take(&sl[0]), n1 = take(&sl[1]);
     if (ok) {
       bool t0, t1;
       deep_walk_any(depth, n0, n1, key_lane, ks, &i0, &i1, &t0, &t1);
@@ -237,10 +252,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_deep_kernel(const DeepParams 
         ++ties;
       }
     }
-    release(sa, sb);
-    if (failed) break;
-
-    const uint32_t l0 = take(&sa), l1 = take(&sb);
+    const uint32_t l0 = take(&sl[2]), l1 = take(&sl[3]);
     if (ok) {
       const uint32_t j0 = i0 - gm.slots, j1 = i1 - gm.slots;
       acc += lds_f32(l0 + j0 * 4u);
@@ -251,8 +263,18 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_deep_kernel(const DeepParams 
         if (t1 >= 0) p.leaf_ids[row * p.num_trees + t1] = p.orig_leaf[gm.elem_off + gm.slots + j1];
       }
     }
-    release(sa, sb);
+    // One block-wide barrier per pair (it also carries a wait failure to every thread, so
+    // that the exit is uniform) frees the pair's four slots; four rotating warps refill
+    // them with the next pieces in order: the leaf planes of the next pair, whose node
+    // planes are already there, and the node planes of the pair after it.
+    failed = __syncthreads_or(!ok) != 0;
     if (failed) break;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (next_piece < P && lane == 0 && warp == issuer) issue(next_piece, sl[i]);
+      ++next_piece;
+      if (++issuer == RW) issuer = 0;
+    }
   }
   if (failed) {
     if (tid == 0) atomicExch(p.status, 4);
