@@ -322,3 +322,27 @@ def test_abalone_onnx_golden_on_gpu(golden_dir):
     for rep in ("sparse", "array", "reorg"):
         got = kernels.DeviceForest(forest, representation=rep).predict(_dev(z["rows"])).cpu().numpy()
         assert oracle.fp_equal(got, z["expected"]).all()
+
+
+def test_multiclass_register_class_sums_match_the_class_table_path():
+    """Large multiclass batches keep the class sums in registers (class-major groups,
+    arg-max decided on the fly); smaller ones and chunked launches use the shared-memory
+    class table.  Both must give the oracle's class ids."""
+    from treebeard_b200 import kernels, synth
+    forest, marg, _ = synth.make_config("c4", trees=78)
+    rows = 2 * 148 * 32 * 32 + 77                     # enough row tiles for the register path
+    X = synth.config_rows("c4", marg, rows)
+    dX = _dev(X)
+    fast = kernels.DeviceForest(forest, representation="sparse", batch_hint=rows)
+    table = kernels.DeviceForest(forest, representation="sparse", tree_chunks=2, batch_hint=rows)
+    a = fast.predict(dX, int8=True).cpu().numpy()
+    b = table.predict(dX, int8=True).cpu().numpy()
+    fast.check_status()
+    assert fast.info().schedule.tree_chunks == 1 and fast.info().threads_per_block == 1024
+    pick = np.arange(0, rows, 37)
+    want, sums = oracle.predict(forest, X[pick], class_sums=True)
+    assert_predictions_close(a[pick], want, forest, sums)
+    assert (a != b).mean() < 1e-4                     # only exact class-sum ties may differ
+    ids = fast.predict_leaf_ids(dX[:4096]).cpu().numpy()
+    _, want_ids = oracle.predict(forest, X[:4096], leaf_ids=True)
+    assert np.array_equal(ids, want_ids)

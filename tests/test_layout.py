@@ -27,7 +27,11 @@ def test_packed_layout_selects_oracle_leaves(name, rep, ts):
         assert np.allclose(sums[:, 0], want, rtol=1e-5, atol=1e-5)
     else:
         assert np.allclose(sums, class_sums - forest.initial_value, rtol=1e-5, atol=1e-5)
-    assert info.num_groups == (forest.num_trees + 15) // 16
+    if forest.num_classes == 0:
+        assert info.num_groups == (forest.num_trees + 15) // 16
+    else:   # every class is padded to whole groups of its own
+        per_class = np.bincount(forest.class_id, minlength=forest.num_classes)
+        assert info.num_groups == sum(max(1, (n + 15) // 16) for n in per_class)
 
 
 @pytest.mark.parametrize("ts,shapes", [(1, 1), (2, 3), (3, 8), (4, 22)])

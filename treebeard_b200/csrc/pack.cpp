@@ -332,9 +332,30 @@ std::string pack_forest(const Forest &f, const PackOptions &opt, PackedForest *o
     return tcount[x] < tcount[y];
   });
 
-  const int64_t G = (T + kGroupTrees - 1) / kGroupTrees;
+  // columns of the groups: tree index or -1 (filler).  A multiclass forest is laid out
+  // class by class, every class padded to whole groups, so that a group belongs to ONE
+  // class and the classes appear in increasing order: the kernel can then keep a class
+  // sum in a register and decide the arg-max on the fly.
+  std::vector<int64_t> cols;
+  std::vector<int16_t> col_class; // class of every column, fillers included
+  if (f.num_classes > 0) {
+    std::vector<std::vector<int64_t>> by_class(f.num_classes);
+    for (int64_t k = 0; k < T; ++k) by_class[f.class_id[order[k]]].push_back(order[k]);
+    for (int32_t cls = 0; cls < f.num_classes; ++cls) {
+      const auto &list = by_class[cls];
+      cols.insert(cols.end(), list.begin(), list.end());
+      if (list.empty()) cols.push_back(-1); // a class without trees still gets a (filler) group
+      while (cols.size() % kGroupTrees) cols.push_back(-1);
+      col_class.resize(cols.size(), (int16_t)cls);
+    }
+  } else {
+    cols.assign(order.begin(), order.end());
+    while (cols.size() % kGroupTrees) cols.push_back(-1);
+  }
+  const int64_t G = (int64_t)cols.size() / kGroupTrees;
   p.groups.resize(G);
   p.tree_class.assign(G * kGroupTrees, 0);
+  if (f.num_classes > 0) p.tree_class = col_class;
   p.tree_index.assign(G * kGroupTrees, -1);
   p.orig_off.resize(G);
   const bool implicit = opt.representation != kSparse;
@@ -345,10 +366,10 @@ std::string pack_forest(const Forest &f, const PackOptions &opt, PackedForest *o
     uint32_t gdepth = 0;
     uint64_t slots = 1;
     for (int c = 0; c < kGroupTrees; ++c) {
-      const int64_t k = g * kGroupTrees + c;
-      if (k >= T) break;
-      gdepth = std::max<uint32_t>(gdepth, tdepth[order[k]]);
-      if (!implicit) slots = std::max<uint64_t>(slots, tcount[order[k]]);
+      const int64_t t = cols[g * kGroupTrees + c];
+      if (t < 0) continue;
+      gdepth = std::max<uint32_t>(gdepth, tdepth[t]);
+      if (!implicit) slots = std::max<uint64_t>(slots, tcount[t]);
     }
     if (implicit) {
       // complete (ts+1)-ary array down to level gdepth
@@ -397,12 +418,11 @@ std::string pack_forest(const Forest &f, const PackOptions &opt, PackedForest *o
     const Tile filler; // leaf tile with value 0
     for (int c = 0; c < kGroupTrees; ++c) {
       const int64_t k = g * kGroupTrees + c;
-      const bool real = k < T;
-      const int64_t t = real ? order[k] : -1;
+      const int64_t t = cols[k];
+      const bool real = t >= 0;
       const int64_t a = real ? f.tree_off[t] : 0;
       if (real) {
         p.tree_index[k] = (int32_t)t;
-        p.tree_class[k] = f.num_classes > 0 ? (int16_t)f.class_id[t] : 0;
       }
       if (!implicit) {
         // level-order numbering of tiles, children of a tile adjacent

@@ -12,7 +12,7 @@ int64_t smem_needed(const ForestShape &fs, const LaunchPlan &p) {
   if (p.staged) bytes += 2 * (int64_t)p.stage_bytes;
   if (p.cache_rows) bytes += (int64_t)p.row_warps * (fs.num_features + 1) * rt * 4;
   const int64_t warps = (int64_t)p.row_warps * p.tree_threads;
-  if (fs.num_classes > 0)
+  if (fs.num_classes > 0 && !p.class_regs)
     bytes += warps * fs.num_classes * rt * 4;
   else if (p.tree_threads > 1)
     bytes += warps * rt * 4;
@@ -26,7 +26,7 @@ static int floor_pow2(int v) {
 }
 
 std::string select_launch(const ForestShape &fs, const tbk_schedule &user, int64_t n_rows,
-                          int32_t smem_limit, int32_t num_sms, bool leaf_ids, LaunchPlan *out) {
+                          int32_t smem_limit, int32_t num_sms, bool leaf_ids, LaunchPlan *out, bool partial) {
   (void)leaf_ids;
   if (n_rows <= 0) n_rows = 1;
   if (num_sms <= 0) num_sms = 148;
@@ -66,6 +66,10 @@ std::string select_launch(const ForestShape &fs, const tbk_schedule &user, int64
         p.staged = want_stage;
         p.stage_bytes = want_stage ? stage_bytes : 0;
         p.cache_rows = cached;
+        // class sums can stay in registers when one warp walks all trees of its rows and
+        // the launch needs no tree chunks (a batch that fills the GPU twice over anyway)
+        p.class_regs = fs.num_classes > 0 && tt == 1 && !partial && user.tree_chunks <= 1 &&
+                       row_tiles >= 2 * (int64_t)num_sms * max_warps;
         int rw_hi = max_warps / tt;
         if (user.rows_per_block > 0) rw_hi = std::max(1, std::min<int>(rw_hi, user.rows_per_block / (int)rt));
         rw_hi = (int)std::min<int64_t>(rw_hi, row_tiles);

@@ -31,6 +31,7 @@ struct LaunchPlan {
   int32_t groups_per_chunk = 1;
   int32_t staged = 0;        // tree groups staged through shared memory
   int32_t cache_rows = 1;    // row tile transposed into shared memory
+  int32_t class_regs = 0;    // multiclass: class sums in registers (no shared-memory class table)
   uint32_t stage_bytes = 0;
   int32_t smem_bytes = 0;
   int32_t threads = 32;
@@ -41,7 +42,9 @@ struct LaunchPlan {
 int64_t smem_needed(const ForestShape &fs, const LaunchPlan &p);
 
 // Fills `plan`; returns an empty string on success or the reason no launch shape fits.
+// partial: the launch writes per-class partial sums (tree-sharded use) instead of predictions.
 std::string select_launch(const ForestShape &fs, const tbk_schedule &user, int64_t n_rows,
-                          int32_t smem_limit, int32_t num_sms, bool leaf_ids, LaunchPlan *plan);
+                          int32_t smem_limit, int32_t num_sms, bool leaf_ids, LaunchPlan *plan,
+                          bool partial = false);
 
 } // namespace tb

@@ -370,7 +370,8 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
   tb::ForestShape shape{pk.num_features, pk.num_classes, (int64_t)pk.groups.size(), pk.max_group_bytes,
                         (int32_t)pk.lut.size(), pk.representation, pk.tile_size};
   tb::LaunchPlan plan;
-  std::string why = tb::select_launch(shape, f->user, n_rows, f->max_smem_optin, f->num_sms, mode == kLeafIds, &plan);
+  std::string why = tb::select_launch(shape, f->user, n_rows, f->max_smem_optin, f->num_sms, mode == kLeafIds, &plan,
+                                      mode == kPartial);
   if (!why.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", why.c_str());
   f->last_plan = plan;
 
@@ -421,6 +422,10 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
   p.stage_bytes = plan.staged ? plan.stage_bytes : 0;
   p.vec4_ok = (pk.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
   p.status = f->d_status;
+  // the plan's shared-memory size has no class table when class sums live in registers
+  if (plan.class_regs && (plan.chunks != 1 || mode == kPartial))
+    return fail(TBK_ERR_UNSUPPORTED, "launch plan with register class sums needs a single tree chunk");
+  p.class_regs = plan.class_regs;
 
   KernelFn fn = pick_kernel(pk.representation, pk.tile_size, plan.rows_per_lane, plan.staged, plan.cache_rows);
   CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));

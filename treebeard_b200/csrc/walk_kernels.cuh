@@ -64,6 +64,7 @@ struct WalkParams {
   int32_t tree_threads;
   uint32_t stage_bytes; // capacity of one stage (0 when not staged)
   int32_t vec4_ok;      // rows can be read with 16-byte loads
+  int32_t class_regs;   // multiclass: class sums in registers, arg-max decided on the fly
   int32_t *status;      // device status word, 0 = ok
 };
 
@@ -291,12 +292,44 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_kernel(const WalkParams p) {
 #pragma unroll
   for (int q = 0; q < RPL; ++q) acc[q] = 0.f;
   float *cacc = acc_s + (size_t)warp * W * RT; // multiclass: [class][row in tile]
-  if (p.num_classes > 0)
+  if (p.num_classes > 0 && !p.class_regs)
     for (int i = lane; i < W * RT; i += 32) cacc[i] = 0.f;
   __syncwarp();
+  // Multiclass with class sums in registers: the packer lays a multiclass forest out class
+  // by class (every group belongs to one class, classes in increasing order, every class
+  // present), so one register per row holds the running sum of the current class and the
+  // arg-max is updated whenever the class changes -- no shared-memory class table, which
+  // leaves room for a full block of row warps.
+  int cur_cls = -1;
+  float best[RPL];
+  int arg[RPL];
+#pragma unroll
+  for (int q = 0; q < RPL; ++q) {
+    best[q] = __int_as_float(0xff800000);
+    arg[q] = 0;
+  }
+  auto close_class = [&]() {
+    if (cur_cls < 0) return;
+#pragma unroll
+    for (int q = 0; q < RPL; ++q) {
+      const float v = p.initial_value + acc[q];
+      if (!(best[q] > v)) { // the reference's tie rule: the later class wins
+        best[q] = v;
+        arg[q] = cur_cls;
+      }
+      acc[q] = 0.f;
+    }
+  };
 
   for (int g = g0; g < g1; ++g) {
     const DevGroupMeta gm = p.groups[g];
+    if (p.class_regs) {
+      const int cls = p.tree_class[g * kCols];
+      if (cls != cur_cls) {
+        close_class();
+        cur_cls = cls;
+      }
+    }
     const uint8_t *gbase;
     if (STAGED) {
       const int s = (g - g0) & 1;
@@ -328,7 +361,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_kernel(const WalkParams p) {
               p.leaf_ids[row * p.num_trees + t] = p.orig_node[p.orig_off[g] + (size_t)slot[q] * kCols + col];
           }
         }
-      } else if (p.num_classes > 0) {
+      } else if (p.num_classes > 0 && !p.class_regs) {
         const int cls = p.tree_class[k];
 #pragma unroll
         for (int q = 0; q < RPL; ++q) cacc[cls * RT + q * 32 + lane] += v[q];
@@ -372,6 +405,15 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_kernel(const WalkParams p) {
         p.partial[(long long)blockIdx.y * p.n_rows + row] = acc[q];
       else
         reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + acc[q], p.transform);
+    }
+  } else if (p.class_regs) {
+    close_class();
+#pragma unroll
+    for (int q = 0; q < RPL; ++q) {
+      const long long row = row_base + q * 32 + lane;
+      if (row >= p.n_rows) continue;
+      if (p.out_kind == 1) reinterpret_cast<int8_t *>(p.out)[row] = (int8_t)arg[q];
+      else reinterpret_cast<float *>(p.out)[row] = (float)arg[q];
     }
   } else {
     __syncthreads();
