@@ -70,3 +70,26 @@ def test_full_size_tree_shards_add_up():
     assert_predictions_close(got[pick], want)
     ids = whole.predict_leaf_ids(torch.from_numpy(X[pick[:256]]).cuda()).cpu().numpy()
     assert np.array_equal(ids, want_ids[:256])
+
+
+def test_full_size_large_forest_c5():
+    """C5 with all 16 000 trees (deep-tree kernel): the oracle on a subsample of a 65 536-row
+    batch -- leaf ids bit-exact for every tree, predictions within tolerance -- and the
+    batch split at an odd row."""
+    from treebeard_b200 import kernels
+    forest, marg, _ = synth.make_config("c5")
+    rows = 65536
+    X = synth.config_rows("c5", marg, rows)
+    dX = torch.from_numpy(X).cuda()
+    df = kernels.DeviceForest(forest, representation="auto", batch_hint=rows)
+    assert df.info().schedule.feature_bits == 16
+    got = df.predict(dX).cpu().numpy()
+    df.check_status()
+    pick = np.sort(np.random.Generator(np.random.PCG64(11)).choice(rows, size=1024, replace=False))
+    want, want_ids = oracle.predict(forest, X[pick], leaf_ids=True)
+    assert_predictions_close(got[pick], want)
+    ids = df.predict_leaf_ids(torch.from_numpy(X[pick[:128]]).cuda()).cpu().numpy()
+    assert np.array_equal(ids, want_ids[:128])
+    k = rows // 3 + 1
+    parts = torch.cat([df.predict(dX[:k]), df.predict(dX[k:])]).cpu().numpy()
+    assert_predictions_close(parts, got)

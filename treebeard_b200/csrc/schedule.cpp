@@ -92,8 +92,32 @@ std::string select_launch(const ForestShape &fs, const tbk_schedule &user, int64
   const int64_t rows_per_block = (int64_t)p.row_warps * 32 * p.rows_per_lane;
   p.grid_x = (n_rows + rows_per_block - 1) / rows_per_block;
   int64_t chunks = 1;
-  if (user.tree_chunks > 0) chunks = user.tree_chunks;
-  else if (p.grid_x < 2 * (int64_t)num_sms) chunks = (2 * (int64_t)num_sms + p.grid_x - 1) / p.grid_x;
+  if (user.tree_chunks > 0) {
+    chunks = user.tree_chunks;
+  } else if (p.grid_x < 2 * (int64_t)num_sms) {
+    // A batch too small to fill the GPU with row tiles: split the forest into tree chunks
+    // (grid.y) where that shortens the launch.  Cost model in microseconds, fitted to
+    // measurements on B200 with a cold L2: a group costs about 2.5 (its bulk copy, one in
+    // flight ahead of the walk) or, when a warp walks several columns of it, 0.75 per
+    // column per full block of warps; a block pays about three to stage its rows; the
+    // second pass (a launch and a small kernel) about six as soon as there is more than
+    // one chunk.
+    p.smem_bytes = (int32_t)smem_needed(fs, p);
+    const int64_t threads = (int64_t)p.row_warps * p.tree_threads * 32;
+    const int64_t resident = std::max<int64_t>(1, std::min<int64_t>((233472 - 1024) / (p.smem_bytes + 1024), 2048 / threads));
+    const int64_t slots = resident * num_sms;
+    const double group_cost = std::max(2.5, 0.75 * (16.0 / p.tree_threads) * (double)threads / 1024.0);
+    double best_cost = -1.0;
+    for (int64_t c = 1; c <= std::min<int64_t>(fs.num_groups, 64); ++c) {
+      const int64_t per_block = (fs.num_groups + c - 1) / c;
+      const int64_t waves = (p.grid_x * c + slots - 1) / slots;
+      const double cost = (double)waves * ((double)per_block * group_cost + 3.0) + (c > 1 ? 6.0 : 0.0);
+      if (best_cost < 0 || cost < best_cost - 1e-9) {
+        best_cost = cost;
+        chunks = c;
+      }
+    }
+  }
   chunks = std::max<int64_t>(1, std::min<int64_t>(chunks, fs.num_groups));
   chunks = std::min<int64_t>(chunks, 65535);
   p.groups_per_chunk = (int32_t)((fs.num_groups + chunks - 1) / chunks);
