@@ -212,7 +212,9 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
   }
   // (each thread reads back only the keys it wrote: no barrier is needed for the tile)
 
-  float acc = 0.f;
+  // thousands of leaf values per row: a double accumulator keeps the sum within the
+  // fp32 rounding of the exact result (one conversion and one add per tree)
+  double acc = 0.0;
   bool ok = true, failed = false;
   unsigned ties = 0;
   int slot = 0;          // ring slot of the next piece to consume
@@ -255,8 +257,8 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
     const uint32_t l0 = take(&sl[2]), l1 = take(&sl[3]);
     if (ok) {
       const uint32_t j0 = i0 - gm.slots, j1 = i1 - gm.slots;
-      acc += lds_f32(l0 + j0 * 4u);
-      acc += lds_f32(l1 + j1 * 4u);
+      acc += (double)lds_f32(l0 + j0 * 4u);
+      acc += (double)lds_f32(l1 + j1 * 4u);
       if (p.leaf_ids != nullptr && live) {
         const int t0 = p.tree_index[(g0 + k) * 2], t1 = p.tree_index[(g0 + k) * 2 + 1];
         if (t0 >= 0) p.leaf_ids[row * p.num_trees + t0] = p.orig_leaf[gm.elem_off + j0];
@@ -283,9 +285,9 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
   if (p.tie_count != nullptr && ties) atomicAdd(p.tie_count, (unsigned long long)ties);
   if (p.leaf_ids != nullptr || !live) return;
   if (p.write_partial)
-    p.partial[(long long)blockIdx.y * p.n_rows + row] = acc;
+    p.partial[(long long)blockIdx.y * p.n_rows + row] = (float)acc;
   else
-    reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + acc, p.transform);
+    reinterpret_cast<float *>(p.out)[row] = apply_transform((float)((double)p.initial_value + acc), p.transform);
 }
 
 } // namespace tb
