@@ -134,20 +134,6 @@ __device__ __noinline__ uint32_t deep_walk_exact(uint32_t base, uint32_t key_lan
   return i;
 }
 
-// Bounded wait executed by every lane of the calling warp (no election, no shuffle).
-__device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t parity) {
-  for (uint32_t it = 0; it < kQWaitTries; ++it) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-                 " selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok)
-                 : "r"(bar_addr), "r"(parity), "r"(200u)
-                 : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-
 __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

@@ -115,6 +115,20 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, int la
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// Bounded wait executed by every lane of the calling warp (no election, no shuffle).
+__device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t parity) {
+  for (uint32_t it = 0; it < kQWaitTries; ++it) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+                 " selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(bar_addr), "r"(parity), "r"(200u)
+                 : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
 // Fast walk of DEPTH levels of one column of a staged node plane.  Returns the byte
 // address of the slot reached (colbase + 128 * slot); *tie is set when any key
 // comparison on the path tied (the result is then not to be trusted).
@@ -221,7 +235,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   const int g1 = min(p.num_groups, g0 + p.groups_per_chunk);
   const int NG = g1 - g0;
   const int NGh = (NG - half + 1) / 2; // groups half, half + 2, ... of the chunk
-  const int P = 4 * NGh;               // pieces of this half: node upper, node bottom, leaf lo, leaf hi
+  const int P = 2 * NGh;               // pieces of this half: upper levels and bottom level of the node planes
 
   if (tid == 0) {
     for (int i = 0; i < 6; ++i) mbar_init(reinterpret_cast<uint64_t *>(smem_raw) + i, 1);
@@ -234,15 +248,12 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   __syncthreads();
 
   auto issue = [&](int piece) {
-    const uint2 gm = gtab[2 * (piece >> 2) + half];
-    const int j = piece & 3;
+    const uint2 gm = gtab[2 * (piece >> 1) + half];
     const uint32_t hs = 1u << (gm.y - 1);          // slots per piece
-    const size_t off = ((size_t)gm.x + ((j & 1) ? hs : 0u)) * 32;
-    const void *src = j < 2 ? static_cast<const void *>(p.node_plane + off)
-                            : static_cast<const void *>(p.leaf_plane + off);
+    const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
     uint64_t *bar = &full[piece % 3];
     mbar_expect_tx(bar, hs * 128u);
-    bulk_g2s(ring + (size_t)(piece % 3) * kQPiece, src, hs * 128u, bar);
+    bulk_g2s(ring + (size_t)(piece % 3) * kQPiece, p.node_plane + off, hs * 128u, bar);
   };
   if (lane == 0 && hw < 3 && hw < P) issue(hw);
 
@@ -289,28 +300,35 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   // the two columns this lane walks in every group of its half
   const uint32_t col[2] = {(uint32_t)(lane + hw) & 31u, (uint32_t)(lane + hw + 16) & 31u};
   float acc = 0.f;
+  float pend[2] = {0.f, 0.f}; // leaf values of the previous group, still on their way from L2
   bool ok = true, failed = false;
   unsigned ties = 0;
 
-  // A barrier over the half-block (which also carries any wait failure to its 512 threads,
-  // so that their exit is uniform) frees a slot; the refill is issued by a rotating warp.
-  auto release = [&](int first, int count) {
+  // One barrier per group over the half-block (it also carries any wait failure to its 512
+  // threads, so that their exit is uniform) frees the group's two slots; the refills are
+  // issued by two rotating warps.
+  auto release = [&](int first) {
     failed = half_barrier_or(1 + half, !ok);
-    if (!failed && lane == 0)
-      for (int i = 0; i < count; ++i) {
+    if (!failed && lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
         const int next = first + i + 3;
         if (next < P && (next % kQHalfWarps) == hw) issue(next);
       }
+    }
   };
-  auto piece_ready = [&](int piece) { return warp_wait(&full[piece % 3], (uint32_t)(piece / 3) & 1u, lane); };
+  const uint32_t full_s = smem_u32(full);
+  auto piece_ready = [&](int piece) {
+    return mbar_wait_all_lanes(full_s + 8u * (uint32_t)(piece % 3), (uint32_t)(piece / 3) & 1u);
+  };
   auto slot_addr = [&](int piece) { return ring_s + (uint32_t)(piece % 3) * kQPiece; };
 
   for (int k = 0; k < NGh; ++k) {
     const int gi = 2 * k + half;
     const uint2 gm = gtab[gi];
     const uint32_t depth = gm.y, hs = 1u << (depth - 1);
-    const int q = 4 * k;
-    uint32_t idx[2] = {0, 0}, leaf[2] = {0, 0};
+    const int q = 2 * k;
+    uint32_t idx[2] = {0, 0};
 
     // upper levels 0 .. depth-2
     ok = piece_ready(q);
@@ -327,12 +345,14 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
         idx[w] = s - (hs - 1u); // position inside the bottom decision level
       }
     }
-    release(q, 1);
-    if (failed) break;
 
-    // bottom decision level
-    ok = piece_ready(q + 1);
+    // bottom decision level, then the two leaf values straight from global memory: a warp's
+    // 32 leaves are scattered over the leaf plane whatever its layout (one sector each), so
+    // staging the plane would move the same bytes through the ring; the loads are consumed
+    // one group later
+    if (ok) ok = piece_ready(q + 1);
     if (ok) {
+      acc += pend[0] + pend[1];
 #pragma unroll
       for (int w = 0; w < 2; ++w) {
         const uint32_t node = lds_u32(slot_addr(q + 1) + idx[w] * 128u + col[w] * 4u);
@@ -343,29 +363,19 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
           right = !(__ldg(rowp + f) < __ldg(p.exact_plane + ((size_t)gm.x + hs + idx[w]) * 32u + col[w]));
           ++ties;
         }
-        leaf[w] = 2u * idx[w] + (right ? 1u : 0u);
-      }
-    }
-    release(q + 1, 1);
-    if (failed) break;
-
-    // leaf values: lower and upper half of the leaf plane
-    ok = piece_ready(q + 2);
-    if (ok) ok = piece_ready(q + 3);
-    if (ok) {
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const uint32_t a = leaf[w] < hs ? slot_addr(q + 2) + leaf[w] * 128u : slot_addr(q + 3) + (leaf[w] - hs) * 128u;
-        acc += lds_f32(a + col[w] * 4u);
+        const uint32_t leaf = 2u * idx[w] + (right ? 1u : 0u);
+        const size_t e = ((size_t)gm.x + leaf) * 32u + col[w];
+        pend[w] = __ldg(p.leaf_plane + e);
         if (p.leaf_ids != nullptr && live) {
           const int t = p.tree_index[(g0 + gi) * 32 + (int)col[w]];
-          if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[((size_t)gm.x + leaf[w]) * 32u + col[w]];
+          if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
         }
       }
     }
-    release(q + 2, 2);
+    release(q);
     if (failed) break;
   }
+  acc += pend[0] + pend[1];
   if (__syncthreads_or(failed)) {
     if (tid == 0) atomicExch(p.status, 4);
     return;
