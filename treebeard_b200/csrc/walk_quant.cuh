@@ -1,29 +1,29 @@
 // Walk kernel for the 16-bit-key layout (quant_pack.h): forests over rows too wide for
 // an fp32 row tile.
 //
-// One block = 32 warps = one tile of 32 rows.  Lane = row; warp w walks, in every group
-// of 32 trees, column (lane + w) mod 32, so the 32 lanes of a warp read 32 distinct
-// columns of the node plane (one shared-memory wavefront) and the block covers every
-// (row, tree) pair of the group exactly once.  The row tile is staged ONCE per block as
-// 16-bit keys, transposed (keys[feature][row]); the node and leaf planes of every group
-// stream through a three-slot ring of 32 KB stages filled by cp.async.bulk copies, each
-// issued by a different warp so that two copies are always in flight.  Per-row sums live
-// in registers and are combined across the 32 warps once, at the end.
+// One block = 32 warps = one tile of 32 rows, staged ONCE per block as 16-bit keys,
+// transposed (keys[feature][row]).  Lane = row.  The block works as TWO independent halves
+// of 16 warps: half h takes the groups h, h+2, ... of the chunk for all 32 rows; warp w of
+// a half walks, in every group of 32 trees, the columns (lane + w) mod 32 and
+// (lane + w + 16) mod 32 in lock-step, so the 32 lanes of a warp read 32 distinct columns
+// of the node plane (one shared-memory wavefront per load) and the half covers every
+// (row, tree) pair of the group exactly once.  While one half waits for a piece or sits in
+// its barrier, the other keeps the issue slots and the shared-memory pipe busy; the forest
+// is still streamed only once per 32-row tile.
 //
-// The block works as TWO independent halves of 16 warps: half h takes the groups h, h+2,
-// ... of the chunk, for all 32 rows (two columns per lane, walked in lock-step), with its
-// own three-slot ring of 16 KB pieces (upper levels / bottom level of the node plane, two
-// halves of the leaf plane) and its own named barrier.  While one half waits for a piece
-// or sits in a barrier, the other half keeps the issue slots and the shared-memory pipe
-// busy; the forest is still streamed only once per 32-row tile.
+// Only the NODE planes stream through shared memory: two 16 KB pieces per group (upper
+// levels, bottom level) through a three-slot ring per half, filled by cp.async.bulk copies
+// that rotating warps issue; one named barrier per group frees the group's two slots.  The
+// leaf values are read straight from L2: a warp's 32 leaves are scattered over the leaf
+// plane (one sector each whatever its layout), so staging the plane would move the same
+// bytes, and the loads are consumed one group later.  Per-row sums live in registers and
+// are combined across the 32 warps once, at the end.
 //
 // The walk is fully unrolled per depth and fetches BOTH children of the current node
 // while the key comparison is still in flight, which takes the node load off the
 // dependent chain.  Key ties are only flagged on the fast path; a flagged (row, tree)
-// pair is then re-walked on the exact fp32 values from global memory.
-//
-// Waiting on a stage is done by one lane per warp (mbarrier.try_wait); stages are freed
-// by a block-wide barrier.
+// pair is then re-walked on the exact fp32 values from global memory.  Every lane polls
+// the stage barrier itself (mbarrier.try_wait, bounded).
 //
 // Reference counterparts: the walk of src/mlir/CodeGenStateMachine.cpp:149-243 over the
 // reorg layout (src/gpu/ReorgForestRepresentation.cpp:495-571), the unrolled walk of
@@ -61,6 +61,7 @@ struct QuantParams {
   float initial_value;
   int32_t vec4_ok;
   int32_t meta_bytes;            // shared-memory bytes reserved for the group table
+  int32_t prefetch_distance;     // tiles ahead whose rows this block pulls into L2 (0 = none)
   int32_t *status;
   unsigned long long *tie_count; // optional statistics
 };
@@ -256,6 +257,22 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
     bulk_g2s(ring + (size_t)(piece % 3) * kQPiece, p.node_plane + off, hs * 128u, bar);
   };
   if (lane == 0 && hw < 3 && hw < P) issue(hw);
+
+  // Blocks start in index order, one per SM: the tile that takes over an SM when this block
+  // ends is about gridDim-resident blocks ahead.  Pulling its rows into L2 now (a tile time
+  // ahead) lets that block stage its keys from L2 instead of HBM.
+  {
+    const long long ahead = (long long)blockIdx.x + p.prefetch_distance;
+    if (p.prefetch_distance > 0 && ahead * 32 < p.n_rows) {
+      const long long rows_there = min((long long)32, p.n_rows - ahead * 32);
+      const char *base = reinterpret_cast<const char *>(p.rows + ahead * 32 * p.ld);
+      const long long lines_per_row = ((long long)F * 4 + 127) / 128;
+      for (long long i = tid; i < rows_there * lines_per_row; i += blockDim.x) {
+        const long long r = i / lines_per_row, l = i - r * lines_per_row;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + r * p.ld * 4 + l * 128));
+      }
+    }
+  }
 
   // ---- stage the row tile as keys: keys[f][row]
   {
