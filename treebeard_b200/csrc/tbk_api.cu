@@ -209,7 +209,6 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   p.status = f->d_status;
   p.tie_count = f->d_ties;
   p.meta_bytes = quant_meta_bytes(gpc);
-  p.prefetch_distance = chunks == 1 ? f->num_sms : 0; // one resident block per SM
   CUDA_TRY(cudaFuncSetAttribute((const void *)tb::tb_walk_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
   if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
   dim3 grid((unsigned)grid_x, (unsigned)chunks);

@@ -61,7 +61,6 @@ struct QuantParams {
   float initial_value;
   int32_t vec4_ok;
   int32_t meta_bytes;            // shared-memory bytes reserved for the group table
-  int32_t prefetch_distance;     // tiles ahead whose rows this block pulls into L2 (0 = none)
   int32_t *status;
   unsigned long long *tie_count; // optional statistics
 };
@@ -257,22 +256,6 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
     bulk_g2s(ring + (size_t)(piece % 3) * kQPiece, p.node_plane + off, hs * 128u, bar);
   };
   if (lane == 0 && hw < 3 && hw < P) issue(hw);
-
-  // Blocks start in index order, one per SM: the tile that takes over an SM when this block
-  // ends is about gridDim-resident blocks ahead.  Pulling its rows into L2 now (a tile time
-  // ahead) lets that block stage its keys from L2 instead of HBM.
-  {
-    const long long ahead = (long long)blockIdx.x + p.prefetch_distance;
-    if (p.prefetch_distance > 0 && ahead * 32 < p.n_rows) {
-      const long long rows_there = min((long long)32, p.n_rows - ahead * 32);
-      const char *base = reinterpret_cast<const char *>(p.rows + ahead * 32 * p.ld);
-      const long long lines_per_row = ((long long)F * 4 + 127) / 128;
-      for (long long i = tid; i < rows_there * lines_per_row; i += blockDim.x) {
-        const long long r = i / lines_per_row, l = i - r * lines_per_row;
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + r * p.ld * 4 + l * 128));
-      }
-    }
-  }
 
   // ---- stage the row tile as keys: keys[f][row]
   {
