@@ -140,7 +140,7 @@ enum Mode { kPredict, kPartial, kLeafIds };
 
 int quant_meta_bytes(int groups_per_chunk) { return (groups_per_chunk * 8 + 127) / 128 * 128; }
 int quant_smem_bytes(int num_features, int groups_per_chunk = tb::kQMaxGroupsPerChunk) {
-  return 128 + quant_meta_bytes(groups_per_chunk) + 3 * tb::kQStage + (num_features + 1) * 64;
+  return 128 + quant_meta_bytes(groups_per_chunk) + tb::kQRingBytes + (num_features + 1) * 64;
 }
 
 // One prediction with the 16-bit-key kernel (one block per 32 rows, 32 warps).
@@ -165,7 +165,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   plan.groups_per_chunk = gpc;
   plan.staged = 1;
   plan.cache_rows = 1;
-  plan.stage_bytes = tb::kQStage;
+  plan.stage_bytes = tb::kQPiece;
   plan.smem_bytes = quant_smem_bytes(q.num_features, gpc);
   plan.threads = 1024;
   plan.grid_x = grid_x;
@@ -660,7 +660,7 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
     std::vector<int32_t>().swap(f->qf.orig_leaf);
     tb::LaunchPlan &pl = f->last_plan;
     pl.row_warps = 1; pl.tree_threads = 32; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
-    pl.stage_bytes = tb::kQStage; pl.smem_bytes = quant_smem_bytes(q.num_features); pl.threads = 1024;
+    pl.stage_bytes = tb::kQPiece; pl.smem_bytes = quant_smem_bytes(q.num_features); pl.threads = 1024;
     *out = f;
     return TBK_OK;
   }

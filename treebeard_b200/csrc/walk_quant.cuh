@@ -65,7 +65,7 @@ struct QuantParams {
   unsigned long long *tie_count; // optional statistics
 };
 
-constexpr int kQStage = 32768;
+constexpr int kQRingBytes = 6 * 16384; // two half-blocks x three 16 KB pieces
 constexpr int kQMaxGroupsPerChunk = 240;
 constexpr uint32_t kQWaitTries = 1u << 20;
 
@@ -94,27 +94,6 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
 __device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v));
 }
-// Bounded, hardware-suspended wait (one calling thread).
-__device__ __forceinline__ bool mbar_try_wait_bounded(uint64_t *bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < kQWaitTries; ++it) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-                 " selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok)
-                 : "r"(addr), "r"(parity), "r"(200u)
-                 : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-// Lane 0 waits; the result (and the ordering it implies) is shared with the warp.
-__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, int lane) {
-  int ok = 1;
-  if (lane == 0) ok = mbar_try_wait_bounded(bar, parity) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
 // Bounded wait executed by every lane of the calling warp (no election, no shuffle).
 __device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t parity) {
   for (uint32_t it = 0; it < kQWaitTries; ++it) {
