@@ -110,7 +110,8 @@ TREEBEARD_RUNTIME_EXPORT intptr_t ConstructTreebeardContextFromGPUAutoscheduleOp
 TREEBEARD_RUNTIME_EXPORT void DestroyTreebeardContext(intptr_t tbContext);
 /* "xgboost_json" or "onnx_file" (src/json/ForestCreatorFactory.cpp:7-11) */
 TREEBEARD_RUNTIME_EXPORT void SetForestCreatorType(intptr_t tbContext, const char *creatorType);
-/* "gpu_array", "gpu_sparse", "gpu_reorg", "array", "sparse" */
+/* "gpu_array", "gpu_sparse", "gpu_reorg", "array", "sparse"; addition: "gpu_auto" lets the
+ * library choose the layout for the forest (what findBestGPUScheduleAndCompileModel uses) */
 TREEBEARD_RUNTIME_EXPORT void SetRepresentationAndSerializer(intptr_t tbContext, const char *repType);
 TREEBEARD_RUNTIME_EXPORT void *GetScheduleFromTBContext(intptr_t tbContext);
 

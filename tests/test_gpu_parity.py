@@ -346,3 +346,29 @@ def test_multiclass_register_class_sums_match_the_class_table_path():
     ids = fast.predict_leaf_ids(dX[:4096]).cpu().numpy()
     _, want_ids = oracle.predict(forest, X[:4096], leaf_ids=True)
     assert np.array_equal(ids, want_ids)
+
+
+def test_auto_schedule_runner_chooses_the_layout(tmp_path):
+    """findBestGPUScheduleAndCompileModel (the reference's timed search over schedules and
+    representations) is the layout selector here: deep trees get the deep-tree layout."""
+    from treebeard_b200 import kernels, synth, treebeard
+    forest, X = small_config("c5", rows=256, trees=6)
+    path = str(tmp_path / "deep.json")
+    synth.save_xgboost_json(forest, path)
+    ctx = treebeard.TreebeardContext(path, "", treebeard.CompilerOptions(256, 1))
+    runner = treebeard.TreebeardInferenceRunner.AutoScheduleGPUInferenceRunnerFromTBContext(ctx)
+    got = runner.RunInference(X)
+    assert_predictions_close(got, oracle.predict(forest, X))
+    df = kernels.DeviceForest.from_handle(runner.kernel_forest(), 0, forest.num_trees, 0, forest.num_features)
+    assert df.info().schedule.feature_bits == 16
+    # an explicit representation keeps its plain meaning
+    ctx2 = treebeard.TreebeardContext(path, "", treebeard.CompilerOptions(256, 1))
+    ctx2.SetRepresentationType("gpu_sparse")
+    plain = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx2)
+    df2 = kernels.DeviceForest.from_handle(plain.kernel_forest(), 0, forest.num_trees, 0, forest.num_features)
+    assert df2.info().schedule.feature_bits == 32
+    assert_predictions_close(plain.RunInference(X), got)
+    # host-resident rows through the chunked pipeline of the kernel library
+    out = np.empty(len(X), np.float32)
+    df.predict_host(X, out)
+    assert_predictions_close(out, got)

@@ -136,7 +136,8 @@ int rep_from_name(const std::string &name) {
   if (name == "gpu_array" || name == "array") return TBK_REP_ARRAY;
   if (name == "gpu_sparse" || name == "sparse") return TBK_REP_SPARSE;
   if (name == "gpu_reorg") return TBK_REP_REORG;
-  return -1;
+  if (name == "gpu_auto") return TBK_REP_AUTO; // addition: the library picks the layout
+  return -2;
 }
 
 bool load_forest(const std::string &creator, const std::string &path, tb::Forest *f, int32_t num_features = 0) {
@@ -179,7 +180,7 @@ InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &o
     return nullptr;
   }
   int rep = repName.empty() ? (g_use_sparse ? TBK_REP_SPARSE : TBK_REP_ARRAY) : rep_from_name(repName);
-  if (rep < 0) {
+  if (rep < TBK_REP_AUTO) {
     set_error(TBK_ERR_INVALID, "unknown representation \"" + repName + "\"");
     return nullptr;
   }
@@ -606,7 +607,7 @@ void SetNumberOfKernelRuns(int32_t val) { g_kernel_runs = val; }
 
 void *ConstructRepresentation(const char *repName) {
   clear_error();
-  if (!repName || rep_from_name(repName) < 0) {
+  if (!repName || rep_from_name(repName) < TBK_REP_AUTO) {
     set_error(TBK_ERR_INVALID, "unknown representation");
     return nullptr;
   }
@@ -668,7 +669,7 @@ void SetRepresentationAndSerializer(intptr_t c, const char *repType) {
   clear_error();
   auto *ctx = reinterpret_cast<TreebeardContext *>(c);
   if (!ctx || !repType) return set_error(TBK_ERR_INVALID, "null argument");
-  if (rep_from_name(repType) < 0) return set_error(TBK_ERR_INVALID, std::string("unknown representation \"") + repType + "\"");
+  if (rep_from_name(repType) < TBK_REP_AUTO) return set_error(TBK_ERR_INVALID, std::string("unknown representation \"") + repType + "\"");
   ctx->representation = repType;
 }
 
@@ -728,9 +729,10 @@ void *findBestGPUScheduleAndCompileModel(void *c) {
     set_error(TBK_ERR_INVALID, "null context");
     return nullptr;
   }
-  // the selector replaces the timed search: drop any pinned launch shape and let it choose
+  // the selector replaces the timed search over schedules and representations: drop any
+  // pinned launch shape and let the library choose the layout for this forest as well
   ctx->hasGpuOptions = false;
-  if (ctx->representation.empty()) ctx->representation = "gpu_sparse";
+  ctx->representation = "gpu_auto";
   return runner_from_context(ctx);
 }
 
