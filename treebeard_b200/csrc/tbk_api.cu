@@ -233,24 +233,22 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   return TBK_OK;
 }
 
-// Shared-memory plan of the deep-tree kernel: the most row warps (even, at most 16 -- one
-// block per SM either way, and more rows per tile mean fewer passes over the forest) whose
-// key tile leaves room for a ring of at least 4 whole-tree pieces.
+// Shared-memory plan of the deep-tree kernel: the most row warps (even -- one block per SM
+// either way, and more rows per tile mean fewer passes over the forest and more walks in
+// flight) whose key tile leaves room for a ring of at least 4 whole-tree pieces.
 bool deep_plan(int num_features, int max_depth, int smem_limit, int *row_warps, int *slots) {
   const int64_t slot = 4ll << std::max(max_depth, tb::kDeepMinDepth);
-  // six slots hold a pair (four pieces) plus the node planes of the next one; with fewer
-  // the kernel still runs, without that prefetch
-  for (int want = 6; want >= 4; want -= 2)
-    for (int rw = 16; rw >= 4; rw -= 2) {
-      const int64_t keys = (int64_t)(num_features + 1) * 64 * rw;
-      const int64_t room = (int64_t)smem_limit - 128 - keys;
-      const int64_t s = std::min<int64_t>(tb::kDeepMaxSlots, room / slot);
-      if (s >= want) {
-        *row_warps = rw;
-        *slots = (int)s;
-        return true;
-      }
+  // four slots hold the node planes of the pair being walked and of the next one
+  for (int rw = 32; rw >= 4; rw -= 2) {
+    const int64_t keys = (int64_t)(num_features + 1) * 64 * rw;
+    const int64_t room = (int64_t)smem_limit - 128 - keys;
+    const int64_t s = std::min<int64_t>(tb::kDeepMaxSlots, room / slot);
+    if (s >= 4) {
+      *row_warps = rw;
+      *slots = (int)s;
+      return true;
     }
+  }
   return false;
 }
 int deep_smem_bytes(const tbk_forest *f) {
@@ -327,10 +325,12 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
   p.key_stride = 64u * (uint32_t)f->deep_row_warps; // the tile keeps its full width whatever rw is
   p.status = f->d_status;
   p.tie_count = f->d_ties;
-  CUDA_TRY(cudaFuncSetAttribute((const void *)tb::tb_walk_deep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
+  // up to 20 warps the compiler may use 96 registers per thread, beyond that 64
+  auto kernel = plan.threads <= 640 ? tb::tb_walk_deep_kernel<640> : tb::tb_walk_deep_kernel<1024>;
+  CUDA_TRY(cudaFuncSetAttribute((const void *)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
   if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
   dim3 grid((unsigned)grid_x, (unsigned)chunks);
-  tb::tb_walk_deep_kernel<<<grid, plan.threads, plan.smem_bytes, stream>>>(p);
+  kernel<<<grid, plan.threads, plan.smem_bytes, stream>>>(p);
   CUDA_TRY(cudaGetLastError());
   ++f->launches;
   const int tpb = 256;

@@ -3,11 +3,12 @@
 // One block = RW warps = one tile of 32*RW rows, staged ONCE as 16-bit keys and kept for
 // the whole forest.  Lane = row: every thread walks its own row through BOTH trees of a
 // pair in lock-step (two independent dependence chains per thread), so all threads of the
-// block read the same two node planes.  The planes stream through a ring of whole-tree
-// pieces (node plane of tree 0, of tree 1, leaf plane of tree 0, of tree 1; 16 KB each at
-// 12 levels) filled by cp.async.bulk copies that different warps issue, so that several
-// are in flight while a pair is walked; one block-wide barrier per pair frees its four
-// slots.  Sums stay in the owning thread's register: there is no cross-thread reduction.
+// block read the same two node planes.  The node planes stream through a ring of whole-tree
+// pieces (16 KB each at 12 levels) filled by cp.async.bulk copies that different warps
+// issue, the next pair's always in flight while a pair is walked; one block-wide barrier
+// per pair frees its two slots.  Leaf values are read straight from L2 (32 scattered
+// sectors per warp whatever the layout) and consumed one pair later.  Sums stay in the
+// owning thread's register: there is no cross-thread reduction.
 //
 // Keys of two row warps are interleaved (feature-major, 128 bytes per warp pair: word j =
 // row j of the even warp | row j of the odd warp << 16), so a warp's key load touches 32
@@ -134,7 +135,8 @@ __device__ __noinline__ uint32_t deep_walk_exact(uint32_t base, uint32_t key_lan
   return i;
 }
 
-__global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p) {
+template <int MAX_THREADS>
+__global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const DeepParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int RW = blockDim.x >> 5;
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
   const float *rowp = p.rows + (live ? row : 0) * p.ld;
   const int g0 = blockIdx.y * p.pairs_per_chunk;
   const int g1 = min(p.num_pairs, g0 + p.pairs_per_chunk);
-  const int P = 4 * (g1 - g0); // pieces of this block
+  const int P = 2 * (g1 - g0); // pieces of this block: the node planes of every tree
 
   if (tid == 0) {
     for (int i = 0; i < S; ++i) mbar_init(&full[i], 1);
@@ -160,18 +162,15 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
   }
   __syncthreads();
 
-  // piece 4k + j of the block: j = 0, 1 node planes of the pair's trees, j = 2, 3 leaf planes.
-  // Pieces are consumed in order, so slots and barrier phases advance by counters (S and RW
-  // are run-time values: no division on the hot path).
+  // piece 2k + j of the block: node plane of tree j of pair k.  Pieces are consumed in order,
+  // so slots and barrier phases advance by counters (S and RW are run-time values: no
+  // division on the hot path).
   auto issue = [&](int piece, int slot) {
-    const DevQuantGroup gm = p.pairs[g0 + (piece >> 2)];
-    const int j = piece & 3;
-    const size_t off = (size_t)gm.elem_off + ((j & 1) ? gm.slots : 0u);
-    const void *src = j < 2 ? static_cast<const void *>(p.node_plane + off)
-                            : static_cast<const void *>(p.leaf_plane + off);
+    const DevQuantGroup gm = p.pairs[g0 + (piece >> 1)];
+    const size_t off = (size_t)gm.elem_off + ((piece & 1) ? gm.slots : 0u);
     uint64_t *bar = &full[slot];
     mbar_expect_tx(bar, gm.slots * 4u);
-    bulk_g2s(ring + (size_t)slot * p.slot_bytes, src, gm.slots * 4u, bar);
+    bulk_g2s(ring + (size_t)slot * p.slot_bytes, p.node_plane + off, gm.slots * 4u, bar);
   };
   if (lane == 0 && warp < S && warp < P) issue(warp, warp);
   if (RW < S && tid == 0)
@@ -201,6 +200,7 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
   // thousands of leaf values per row: a double accumulator keeps the sum within the
   // fp32 rounding of the exact result (one conversion and one add per tree)
   double acc = 0.0;
+  float pend0 = 0.f, pend1 = 0.f; // leaf values of the previous pair, on their way from L2
   bool ok = true, failed = false;
   unsigned ties = 0;
   int slot = 0;          // ring slot of the next piece to consume
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
     const DevQuantGroup gm = p.pairs[g0 + k];
     const uint32_t depth = gm.depth;
     uint32_t i0 = gm.slots, i1 = gm.slots;
-    int sl[4];
+    int sl[2];
 
     const uint32_t n0 = take(&sl[0]), n1 = take(&sl[1]);
     if (ok) {
@@ -240,11 +240,14 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
         ++ties;
       }
     }
-    const uint32_t l0 = take(&sl[2]), l1 = take(&sl[3]);
+    // The two leaf values come straight from L2 and are consumed one pair later: a warp's
+    // 32 leaves are scattered over the leaf plane (one sector each), which moves the same
+    // bytes as staging the plane would, without taking ring slots.
     if (ok) {
       const uint32_t j0 = i0 - gm.slots, j1 = i1 - gm.slots;
-      acc += (double)lds_f32(l0 + j0 * 4u);
-      acc += (double)lds_f32(l1 + j1 * 4u);
+      acc += (double)pend0 + (double)pend1;
+      pend0 = __ldg(p.leaf_plane + gm.elem_off + j0);
+      pend1 = __ldg(p.leaf_plane + gm.elem_off + gm.slots + j1);
       if (p.leaf_ids != nullptr && live) {
         const int t0 = p.tree_index[(g0 + k) * 2], t1 = p.tree_index[(g0 + k) * 2 + 1];
         if (t0 >= 0) p.leaf_ids[row * p.num_trees + t0] = p.orig_leaf[gm.elem_off + j0];
@@ -252,13 +255,12 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
       }
     }
     // One block-wide barrier per pair (it also carries a wait failure to every thread, so
-    // that the exit is uniform) frees the pair's four slots; four rotating warps refill
-    // them with the next pieces in order: the leaf planes of the next pair, whose node
-    // planes are already there, and the node planes of the pair after it.
+    // that the exit is uniform) frees the pair's two slots; two rotating warps refill them
+    // with the next pieces in order.
     failed = __syncthreads_or(!ok) != 0;
     if (failed) break;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       if (next_piece < P && lane == 0 && warp == issuer) issue(next_piece, sl[i]);
       ++next_piece;
       if (++issuer == RW) issuer = 0;
@@ -268,6 +270,7 @@ __global__ void __launch_bounds__(512, 1) tb_walk_deep_kernel(const DeepParams p
     if (tid == 0) atomicExch(p.status, 4);
     return;
   }
+  acc += (double)pend0 + (double)pend1;
   if (p.tie_count != nullptr && ties) atomicAdd(p.tie_count, (unsigned long long)ties);
   if (p.leaf_ids != nullptr || !live) return;
   if (p.write_partial)
