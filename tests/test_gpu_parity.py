@@ -372,3 +372,27 @@ def test_auto_schedule_runner_chooses_the_layout(tmp_path):
     out = np.empty(len(X), np.float32)
     df.predict_host(X, out)
     assert_predictions_close(out, got)
+
+
+@pytest.mark.parametrize("rows", [500, 2 * 148 * 32 * 32])
+def test_multiclass_with_an_empty_class(rows):
+    """Both multiclass paths (shared-memory class table; class sums in registers) with a
+    class that has no trees and strongly negative leaves elsewhere, so that the empty class
+    wins on some rows."""
+    from treebeard_b200 import kernels, synth
+    forest, marg, _ = synth.make_config("c4", trees=52)
+    forest.class_id[forest.class_id == 7] = 8
+    leaves = forest.left < 0
+    forest.thr[leaves] -= np.float32(0.1)              # push every voted class down
+    X = synth.config_rows("c4", marg, rows)
+    df = kernels.DeviceForest(forest, representation="sparse", batch_hint=rows)
+    got = df.predict(_dev(X), int8=True).cpu().numpy()
+    df.check_status()
+    pick = np.arange(0, rows, max(1, rows // 2000))
+    _, sums = oracle.predict(forest, X[pick], class_sums=True)
+    # a class without trees holds the initial value alone, as in the reference's generated
+    # reduction (its header walker would leave it at 0)
+    sums[:, 7] = forest.initial_value
+    want = (sums.shape[1] - 1 - np.argmax(sums[:, ::-1], axis=1)).astype(np.float32)  # last maximum
+    assert_predictions_close(got[pick], want, forest, sums)
+    assert (want == 7).any() and (want != 7).any()     # the empty class wins on some rows only

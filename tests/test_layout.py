@@ -160,3 +160,20 @@ def test_sixteen_bit_keys_refuse_what_they_cannot_hold():
     multi, _ = small_config("c4", rows=1)
     with pytest.raises(kernels.TbkError, match="single-output"):
         kernels.host_layout_check(multi, None, representation="reorg", feature_bits=16)
+
+
+def test_multiclass_class_without_trees_keeps_its_place():
+    """Class-major groups: a class that no tree votes for still gets a (filler) group, so that
+    its sum -- the initial value alone, as in the reference's generated reduction
+    (src/reduction/LowerReduceOps.cpp:921-1003); the reference's header walker leaves such a
+    class at 0 instead -- takes part in the arg-max."""
+    forest, X = small_config("c4", rows=300, trees=52)
+    forest.class_id[forest.class_id == 7] = 8          # nobody votes for class 7 any more
+    want, want_ids, class_sums = oracle.predict(forest, X, leaf_ids=True, class_sums=True)
+    class_sums[:, 7] = forest.initial_value
+    ids, sums, info = kernels.host_layout_check(forest, X, representation="sparse")
+    assert np.array_equal(ids, want_ids)
+    assert np.allclose(sums, class_sums - forest.initial_value, rtol=1e-5, atol=1e-5)
+    assert np.all(sums[:, 7] == 0.0)
+    per_class = np.bincount(forest.class_id, minlength=forest.num_classes)
+    assert info.num_groups == sum(max(1, (n + 15) // 16) for n in per_class)
