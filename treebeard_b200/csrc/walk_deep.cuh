@@ -12,9 +12,8 @@
 //
 // Keys of two row warps are interleaved (feature-major, 128 bytes per warp pair: word j =
 // row j of the even warp | row j of the odd warp << 16), so a warp's key load touches 32
-// distinct banks.  The children of a node are one aligned 8-byte pair, fetched while the
-// key comparison is in flight.  A key tie is only flagged on the fast path; the flagged
-// (row, tree) is re-walked with exact fp32 comparisons at the tied steps.
+// distinct banks.  A key tie is only flagged on the fast path; the flagged (row, tree) is
+// re-walked with exact fp32 comparisons at the tied steps.
 //
 // Reference counterparts: src/mlir/CodeGenStateMachine.cpp:149-243 (scalar walk),
 // src/mlir/WalkDecisionTreeLoweringPass.cpp:24-53 (fixed-depth walk of padded trees),
@@ -51,21 +50,9 @@ struct DeepParams {
 
 constexpr int kDeepMaxSlots = 8;
 
-__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-
 // Fast walk of DEPTH levels of two trees.  base0 / base1: shared-memory addresses of the
 // node planes; returns the heap indices reached (in [2^DEPTH, 2^(DEPTH+1))) and whether
 // any key comparison on either path tied.
-// Upper levels (few distinct nodes per level: loads of a warp mostly coincide) fetch both
-// children while the key comparison is in flight; from level kDeepSpecLevels on, where the
-// lanes' nodes are scattered over the banks, only the chosen child is fetched (half the
-// shared-memory wavefronts of a pair load, at the price of a longer dependence chain).
-constexpr int kDeepSpecLevels = 5;
-
 template <int DEPTH>
 __device__ __forceinline__ void deep_walk(uint32_t base0, uint32_t base1, uint32_t key_lane, uint32_t ks,
                                           uint32_t *i0_out, uint32_t *i1_out, bool *tie0, bool *tie1) {
@@ -74,24 +61,16 @@ __device__ __forceinline__ void deep_walk(uint32_t base0, uint32_t base1, uint32
   bool t0 = false, t1 = false;
 #pragma unroll
   for (int d = 0; d < DEPTH; ++d) {
+    // one key load and one node load per tree and level (fetching both children ahead of
+    // the comparison measured slower: the load/store path is the scarcer resource)
     const uint32_t kx0 = lds_u16(key_lane + (n0 >> 16) * ks);
     const uint32_t kx1 = lds_u16(key_lane + (n1 >> 16) * ks);
-    const bool spec = d + 1 < DEPTH && d < kDeepSpecLevels;
-    uint2 c0 = make_uint2(0, 0), c1 = make_uint2(0, 0);
-    if (spec) {
-      c0 = lds_u64(base0 + i0 * 8u);
-      c1 = lds_u64(base1 + i1 * 8u);
-    }
     const uint32_t kt0 = n0 & 0xffffu, kt1 = n1 & 0xffffu;
-    const bool r0 = kx0 < kt0, r1 = kx1 < kt1;
     t0 |= kx0 == kt0;
     t1 |= kx1 == kt1;
-    i0 = 2u * i0 + (r0 ? 1u : 0u);
-    i1 = 2u * i1 + (r1 ? 1u : 0u);
-    if (spec) {
-      n0 = r0 ? c0.y : c0.x;
-      n1 = r1 ? c1.y : c1.x;
-    } else if (d + 1 < DEPTH) {
+    i0 = 2u * i0 + (kx0 < kt0 ? 1u : 0u);
+    i1 = 2u * i1 + (kx1 < kt1 ? 1u : 0u);
+    if (d + 1 < DEPTH) {
       n0 = lds_u32(base0 + i0 * 4u);
       n1 = lds_u32(base1 + i1 * 4u);
     }

@@ -19,9 +19,8 @@
 // bytes, and the loads are consumed one group later.  Per-row sums live in registers and
 // are combined across the 32 warps once, at the end.
 //
-// The walk is fully unrolled per depth and fetches BOTH children of the current node
-// while the key comparison is still in flight, which takes the node load off the
-// dependent chain.  Key ties are only flagged on the fast path; a flagged (row, tree)
+// The walk is fully unrolled per depth: one key load, one compare, one node load per level.
+// Key ties are only flagged on the fast path; a flagged (row, tree)
 // pair is then re-walked on the exact fp32 values from global memory.  Every lane polls
 // the stage barrier itself (mbarrier.try_wait, bounded).
 //
@@ -120,18 +119,13 @@ __device__ __forceinline__ uint32_t quant_walk(uint32_t colbase, uint32_t keys_l
     const uint32_t cL = 128u - colbase;
 #pragma unroll
     for (int d = 0; d < DEPTH; ++d) {
+      // one key load and one node load per level: the kernel is bound by the SM's load/store
+      // path, so fetching both children ahead of the comparison costs more than it hides
       const uint32_t kx = lds_u16(keys_lane + (node >> 16) * 64u);
-      const uint32_t AL = 2u * A + cL;
-      uint32_t nL = 0, nR = 0;
-      if (d + 1 < DEPTH) {
-        nL = lds_u32(AL);
-        nR = lds_u32(AL + 128u);
-      }
       const uint32_t kt = node & 0xffffu;
-      const bool right = kx < kt;
       t |= (kx == kt);
-      A = right ? AL + 128u : AL;
-      node = right ? nR : nL;
+      A = 2u * A + cL + (kx < kt ? 128u : 0u);
+      if (d + 1 < DEPTH) node = lds_u32(A);
     }
   }
   *tie = t;
