@@ -94,8 +94,8 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
           // leftmost descendant on the bottom level holds the value
           const uint64_t bottom = ((uint64_t)it.slot + 1) * (1ull << (gm.depth - it.level)) - 1;
           const uint64_t leaf = bottom - (gm.slots - 1);
-          q.leaf_plane[gm.elem_off + leaf * kQuantCols + c] = f.thr[a + it.node];
-          q.orig_leaf[gm.elem_off + leaf * kQuantCols + c] = it.node;
+          q.leaf_plane[quant_leaf_elem(gm, leaf, c)] = f.thr[a + it.node];
+          q.orig_leaf[quant_leaf_elem(gm, leaf, c)] = it.node;
           continue;
         }
         const int32_t ft = f.feat[a + it.node];
@@ -138,7 +138,7 @@ void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows,
           }
           n = 2 * n + 1 + (right ? 1 : 0);
         }
-        const uint64_t e = gm.elem_off + (uint64_t)(n - (gm.slots - 1)) * kQuantCols + c;
+        const uint64_t e = quant_leaf_elem(gm, n - (gm.slots - 1), c);
         acc += q.leaf_plane[e];
         if (leaf_ids) leaf_ids[r * q.num_trees + t] = q.orig_leaf[e];
       }

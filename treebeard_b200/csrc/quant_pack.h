@@ -9,7 +9,8 @@
 // per group of 32 trees:
 //
 //   node plane   u32 [2^D slots][32 columns]   (feature index << 16) | threshold key
-//   leaf plane   f32 [2^D slots][32 columns]   leaf values
+//   leaf plane   f32 [32 columns][2^D leaves]  leaf values, column-major: the leaves that a
+//                                              warp needs for ONE tree lie within 1 KB
 //   exact plane  f32 [2^D slots][32 columns]   fp32 thresholds (global memory only)
 //
 // Keys.  For feature f with thresholds in [lo_f, hi_f]:
@@ -62,6 +63,11 @@ struct QuantForest {
 // for the kernel's staging ring.
 inline uint32_t quant_plane_slot(uint32_t heap_slot, uint32_t level, uint32_t depth) {
   return level + 1 == depth ? heap_slot + 1 : heap_slot;
+}
+
+// Element of the leaf plane (and of orig_leaf) that holds leaf `leaf` of tree column `col`.
+inline uint64_t quant_leaf_elem(const QuantGroup &g, uint64_t leaf, uint32_t col) {
+  return g.elem_off + (uint64_t)col * g.slots + leaf;
 }
 
 // host restatement of the key function (the device computes keys with the same

@@ -140,7 +140,7 @@ enum Mode { kPredict, kPartial, kLeafIds };
 
 int quant_meta_bytes(int groups_per_chunk) { return (groups_per_chunk * 8 + 127) / 128 * 128; }
 int quant_smem_bytes(int num_features, int groups_per_chunk = tb::kQMaxGroupsPerChunk) {
-  return 128 + quant_meta_bytes(groups_per_chunk) + tb::kQRingBytes + (num_features + 1) * 64;
+  return 128 + quant_meta_bytes(groups_per_chunk) + tb::kQRingBytes + tb::kQLeafTableBytes + (num_features + 1) * 64;
 }
 
 // One prediction with the 16-bit-key kernel (one block per 32 rows, 32 warps).

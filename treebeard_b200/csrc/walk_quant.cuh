@@ -65,7 +65,8 @@ struct QuantParams {
 };
 
 constexpr int kQRingBytes = 6 * 16384; // two half-blocks x three 16 KB pieces
-constexpr int kQMaxGroupsPerChunk = 240;
+constexpr int kQMaxGroupsPerChunk = 160;
+constexpr int kQLeafTableBytes = 4096; // [2 halves][2 buffers][32 columns][32 rows] leaf numbers
 constexpr uint32_t kQWaitTries = 1u << 20;
 
 __device__ __forceinline__ uint32_t quant_key_dev(float v, float lo, float sc) {
@@ -198,7 +199,9 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   uint2 *gtab = reinterpret_cast<uint2 *>(smem_raw + 128);
   unsigned char *ring = smem_raw + 128 + p.meta_bytes + (size_t)half * 3 * kQPiece;
   const uint32_t ring_s = smem_u32(ring);
-  const uint32_t keys_s = smem_u32(smem_raw + 128 + p.meta_bytes) + 6 * kQPiece; // u16 [F+1][32]
+  // leaf numbers of a group, exchanged between the warps of a half (see below)
+  const uint32_t ltab_s = smem_u32(smem_raw + 128 + p.meta_bytes) + 6 * kQPiece + (uint32_t)half * 2048u;
+  const uint32_t keys_s = smem_u32(smem_raw + 128 + p.meta_bytes) + 6 * kQPiece + kQLeafTableBytes; // u16 [F+1][32]
   const uint32_t keys_lane = keys_s + lane * 2;
 
   const long long row = (long long)blockIdx.x * 32 + lane;
@@ -273,7 +276,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   // the two columns this lane walks in every group of its half
   const uint32_t col[2] = {(uint32_t)(lane + hw) & 31u, (uint32_t)(lane + hw + 16) & 31u};
   float acc = 0.f;
-  float pend[2] = {0.f, 0.f}; // leaf values of the previous group, still on their way from L2
+  float pend[2] = {0.f, 0.f}; // leaf values of the previous group, on their way from L2
   bool ok = true, failed = false;
   unsigned ties = 0;
 
@@ -296,12 +299,41 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   };
   auto slot_addr = [&](int piece) { return ring_s + (uint32_t)(piece % 3) * kQPiece; };
 
+  // Leaf values come straight from L2, but not in the walk's lane assignment: there the 32
+  // lanes of a warp sit in 32 different trees, i.e. 32 different lines of the leaf plane
+  // whatever its layout.  The walkers therefore drop their leaf NUMBERS (one byte each) into
+  // a [column][row] table in shared memory; after the group's barrier warp w of the half
+  // picks up columns 2w and 2w+1 for all 32 rows and loads those leaves from the
+  // column-major leaf plane, where one tree's 256 leaves span 1 KB: at most 8 lines per
+  // warp load instead of 32.  Lane = row on both sides, so the sum stays in the lane's
+  // register; the loads are consumed one group later.
+  auto fetch_leaves = [&](int gi_prev, uint2 gprev, uint32_t buf) {
+    const uint32_t slots = 2u << (gprev.y - 1);
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      const uint32_t c = 2u * (uint32_t)hw + (uint32_t)w;
+      unsigned short leaf;
+      asm volatile("ld.shared.u8 %0, [%1];" : "=h"(leaf) : "r"(ltab_s + buf * 1024u + c * 32u + (uint32_t)lane));
+      const size_t e = (size_t)gprev.x * 32u + (size_t)c * slots + leaf;
+      pend[w] = __ldg(p.leaf_plane + e);
+      if (p.leaf_ids != nullptr && live) {
+        const int t = p.tree_index[(g0 + gi_prev) * 32 + (int)c];
+        if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
+      }
+    }
+  };
+  uint2 gprev = make_uint2(0, 0);
+  int gi_prev = -1;
+
   for (int k = 0; k < NGh; ++k) {
     const int gi = 2 * k + half;
     const uint2 gm = gtab[gi];
     const uint32_t depth = gm.y, hs = 1u << (depth - 1);
     const int q = 2 * k;
     uint32_t idx[2] = {0, 0};
+
+    // leaves of the previous group (its table is complete: the barrier has been passed)
+    if (gi_prev >= 0) fetch_leaves(gi_prev, gprev, (uint32_t)(k - 1) & 1u);
 
     // upper levels 0 .. depth-2
     ok = piece_ready(q);
@@ -319,13 +351,9 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
       }
     }
 
-    // bottom decision level, then the two leaf values straight from global memory: a warp's
-    // 32 leaves are scattered over the leaf plane whatever its layout (one sector each), so
-    // staging the plane would move the same bytes through the ring; the loads are consumed
-    // one group later
+    // bottom decision level; the leaf number goes into the table
     if (ok) ok = piece_ready(q + 1);
     if (ok) {
-      acc += pend[0] + pend[1];
 #pragma unroll
       for (int w = 0; w < 2; ++w) {
         const uint32_t node = lds_u32(slot_addr(q + 1) + idx[w] * 128u + col[w] * 4u);
@@ -337,18 +365,21 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
           ++ties;
         }
         const uint32_t leaf = 2u * idx[w] + (right ? 1u : 0u);
-        const size_t e = ((size_t)gm.x + leaf) * 32u + col[w];
-        pend[w] = __ldg(p.leaf_plane + e);
-        if (p.leaf_ids != nullptr && live) {
-          const int t = p.tree_index[(g0 + gi) * 32 + (int)col[w]];
-          if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
-        }
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(ltab_s + ((uint32_t)k & 1u) * 1024u + col[w] * 32u + (uint32_t)lane),
+                     "h"((unsigned short)leaf));
       }
+      acc += pend[0] + pend[1]; // previous group's leaves have had a whole walk to arrive
+      pend[0] = pend[1] = 0.f;
     }
     release(q);
     if (failed) break;
+    gprev = gm;
+    gi_prev = gi;
   }
-  acc += pend[0] + pend[1];
+  if (!failed && gi_prev >= 0) {
+    fetch_leaves(gi_prev, gprev, (uint32_t)(NGh - 1) & 1u);
+    acc += pend[0] + pend[1];
+  }
   if (__syncthreads_or(failed)) {
     if (tid == 0) atomicExch(p.status, 4);
     return;
