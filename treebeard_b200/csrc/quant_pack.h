@@ -34,7 +34,7 @@
 namespace tb {
 
 constexpr int kQuantCols = 32;
-constexpr int kQuantMaxDepth = 8; // pieces of at most 2^8 * 128 B = 32 KB
+constexpr int kQuantMaxDepth = 8; // node planes of at most 2^8 * 128 B = 32 KB: two 16 KB stages
 
 struct QuantGroup {
   uint64_t elem_off; // offset of the group's planes, in elements (same for all planes)

@@ -14,10 +14,11 @@
 // Only the NODE planes stream through shared memory: two 16 KB pieces per group (upper
 // levels, bottom level) through a three-slot ring per half, filled by cp.async.bulk copies
 // that rotating warps issue; one named barrier per group frees the group's two slots.  The
-// leaf values are read straight from L2: a warp's 32 leaves are scattered over the leaf
-// plane (one sector each whatever its layout), so staging the plane would move the same
-// bytes, and the loads are consumed one group later.  Per-row sums live in registers and
-// are combined across the 32 warps once, at the end.
+// leaf values are read straight from L2 (staging the leaf plane would move as many bytes
+// and take ring slots) and consumed one group later; the walkers first exchange their leaf
+// numbers through a small shared-memory table, so that a warp loads ONE tree's leaves for
+// all 32 rows (see fetch_leaves).  Per-row sums live in registers and are combined across
+// the 32 warps once, at the end.
 //
 // The walk is fully unrolled per depth: one key load, one compare, one node load per level.
 // Key ties are only flagged on the fast path; a flagged (row, tree)
