@@ -83,8 +83,8 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
   return v;
 }
 __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
-  unsigned short v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  uint32_t v; // a 16-bit load into a 32-bit register zero-extends: no conversion afterwards
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
