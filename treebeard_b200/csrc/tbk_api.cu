@@ -209,10 +209,23 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   p.status = f->d_status;
   p.tie_count = f->d_ties;
   p.meta_bytes = quant_meta_bytes(gpc);
-  CUDA_TRY(cudaFuncSetAttribute((const void *)tb::tb_walk_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
+  // kernels specialised for forests whose groups all have 8 (or 6) levels; generic otherwise
+  using QuantKernel = void (*)(const tb::QuantParams);
+  const bool ids = mode == kLeafIds;
+  uint32_t dmin = 0xffffffffu, dmax = 0;
+  for (const auto &g : q.groups) {
+    dmin = std::min(dmin, g.depth);
+    dmax = std::max(dmax, g.depth);
+  }
+  const int ud = (dmin == dmax && (dmin == 8 || dmin == 6)) ? (int)dmin : 0;
+  const QuantKernel qkernel =
+      ud == 8 ? (ids ? tb::tb_walk_quant_kernel<8, true> : tb::tb_walk_quant_kernel<8, false>)
+      : ud == 6 ? (ids ? tb::tb_walk_quant_kernel<6, true> : tb::tb_walk_quant_kernel<6, false>)
+                : (ids ? tb::tb_walk_quant_kernel<0, true> : tb::tb_walk_quant_kernel<0, false>);
+  CUDA_TRY(cudaFuncSetAttribute((const void *)qkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
   if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
   dim3 grid((unsigned)grid_x, (unsigned)chunks);
-  tb::tb_walk_quant_kernel<<<grid, 1024, plan.smem_bytes, stream>>>(p);
+  qkernel<<<grid, 1024, plan.smem_bytes, stream>>>(p);
   CUDA_TRY(cudaGetLastError());
   ++f->launches;
   const int tpb = 256;
@@ -326,7 +339,19 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
   p.status = f->d_status;
   p.tie_count = f->d_ties;
   // up to 20 warps the compiler may use 96 registers per thread, beyond that 64
-  auto kernel = plan.threads <= 640 ? tb::tb_walk_deep_kernel<640> : tb::tb_walk_deep_kernel<1024>;
+  // specialised for forests whose pairs all have 12 levels; generic otherwise
+  using DeepKernel = void (*)(const tb::DeepParams);
+  uint32_t dmin = 0xffffffffu, dmax = 0;
+  for (const auto &g : q.pairs) {
+    dmin = std::min(dmin, g.depth);
+    dmax = std::max(dmax, g.depth);
+  }
+  const bool d12 = dmin == 12 && dmax == 12, ids = mode == kLeafIds, small = plan.threads <= 640;
+  const DeepKernel kernel =
+      small ? (d12 ? (ids ? tb::tb_walk_deep_kernel<640, 12, true> : tb::tb_walk_deep_kernel<640, 12, false>)
+                   : (ids ? tb::tb_walk_deep_kernel<640, 0, true> : tb::tb_walk_deep_kernel<640, 0, false>))
+            : (d12 ? (ids ? tb::tb_walk_deep_kernel<1024, 12, true> : tb::tb_walk_deep_kernel<1024, 12, false>)
+                   : (ids ? tb::tb_walk_deep_kernel<1024, 0, true> : tb::tb_walk_deep_kernel<1024, 0, false>));
   CUDA_TRY(cudaFuncSetAttribute((const void *)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
   if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
   dim3 grid((unsigned)grid_x, (unsigned)chunks);
@@ -588,6 +613,8 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
     std::string qerr = tb::pack_quant(host, &f->qf);
     if (qerr.empty() && quant_smem_bytes(host.num_features) > f->max_smem_optin)
       qerr = "rows are too wide for the 16-bit key tile";
+    if (qerr.empty() && f->qf.node_plane.size() >= (1ull << 32))
+      qerr = "forest too large for the 16-bit key layout (2^32 plane elements)";
     if (!qerr.empty()) {
       if (bits == 16) return bail(fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str()));
       want_quant = false;

@@ -114,7 +114,9 @@ __device__ __noinline__ uint32_t deep_walk_exact(uint32_t base, uint32_t key_lan
   return i;
 }
 
-template <int MAX_THREADS>
+// UD: depth shared by every pair of the forest (0 = mixed, decided per pair at run time).
+// LEAF_IDS: the launch records leaf ids instead of predictions.
+template <int MAX_THREADS, int UD, bool LEAF_IDS>
 __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const DeepParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -202,14 +204,17 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
 
   for (int k = 0; k < g1 - g0; ++k) {
     const DevQuantGroup gm = p.pairs[g0 + k];
-    const uint32_t depth = gm.depth;
+    const uint32_t depth = UD ? (uint32_t)UD : gm.depth;
     uint32_t i0 = gm.slots, i1 = gm.slots;
     int sl[2];
 
     const uint32_t n0 = take(&sl[0]), n1 = take(&sl[1]);
     if (ok) {
       bool t0, t1;
-      deep_walk_any(depth, n0, n1, key_lane, ks, &i0, &i1, &t0, &t1);
+      if constexpr (UD > 0)
+        deep_walk<UD>(n0, n1, key_lane, ks, &i0, &i1, &t0, &t1);
+      else
+        deep_walk_any(depth, n0, n1, key_lane, ks, &i0, &i1, &t0, &t1);
       if (t0) {
         i0 = deep_walk_exact(n0, key_lane, ks, depth, p.exact_plane + gm.elem_off, rowp);
         ++ties;
@@ -224,10 +229,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
     // bytes as staging the plane would, without taking ring slots.
     if (ok) {
       const uint32_t j0 = i0 - gm.slots, j1 = i1 - gm.slots;
-      acc += (double)pend0 + (double)pend1;
-      pend0 = __ldg(p.leaf_plane + gm.elem_off + j0);
-      pend1 = __ldg(p.leaf_plane + gm.elem_off + gm.slots + j1);
-      if (p.leaf_ids != nullptr && live) {
+      if (!LEAF_IDS) {
+        acc += (double)pend0 + (double)pend1;
+        pend0 = __ldg(p.leaf_plane + gm.elem_off + j0);
+        pend1 = __ldg(p.leaf_plane + gm.elem_off + gm.slots + j1);
+      }
+      if (LEAF_IDS && live) {
         const int t0 = p.tree_index[(g0 + k) * 2], t1 = p.tree_index[(g0 + k) * 2 + 1];
         if (t0 >= 0) p.leaf_ids[row * p.num_trees + t0] = p.orig_leaf[gm.elem_off + j0];
         if (t1 >= 0) p.leaf_ids[row * p.num_trees + t1] = p.orig_leaf[gm.elem_off + gm.slots + j1];
@@ -251,7 +258,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
   }
   acc += (double)pend0 + (double)pend1;
   if (p.tie_count != nullptr && ties) atomicAdd(p.tie_count, (unsigned long long)ties);
-  if (p.leaf_ids != nullptr || !live) return;
+  if (LEAF_IDS || !live) return;
   if (p.write_partial)
     p.partial[(long long)blockIdx.y * p.n_rows + row] = (float)acc;
   else

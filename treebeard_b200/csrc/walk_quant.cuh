@@ -190,6 +190,10 @@ __device__ __forceinline__ bool half_barrier_or(int id, bool pred) {
   return r != 0;
 }
 
+// UD: depth shared by every group of the forest (0 = mixed depths, decided per group at run
+// time; with a constant depth the walk is called directly and piece sizes fold).
+// LEAF_IDS: the launch records leaf ids instead of predictions.
+template <int UD, bool LEAF_IDS>
 __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -226,7 +230,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
 
   auto issue = [&](int piece) {
     const uint2 gm = gtab[2 * (piece >> 1) + half];
-    const uint32_t hs = 1u << (gm.y - 1);          // slots per piece
+    const uint32_t hs = UD ? (1u << (UD ? UD - 1 : 0)) : 1u << (gm.y - 1); // slots per piece
     const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
     uint64_t *bar = &full[piece % 3];
     mbar_expect_tx(bar, hs * 128u);
@@ -308,28 +312,35 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   // column-major leaf plane, where one tree's 256 leaves span 1 KB: at most 8 lines per
   // warp load instead of 32.  Lane = row on both sides, so the sum stays in the lane's
   // register; the loads are consumed one group later.
+  // (element offsets fit 32 bits: the host refuses planes of 2^32 elements or more)
+  const uint32_t my_cols_s = ltab_s + (2u * (uint32_t)hw) * 32u + (uint32_t)lane;
   auto fetch_leaves = [&](int gi_prev, uint2 gprev, uint32_t buf) {
-    const uint32_t slots = 2u << (gprev.y - 1);
+    const uint32_t slots = UD ? (1u << UD) : 2u << (gprev.y - 1);
 #pragma unroll
     for (int w = 0; w < 2; ++w) {
       const uint32_t c = 2u * (uint32_t)hw + (uint32_t)w;
-      unsigned short leaf;
-      asm volatile("ld.shared.u8 %0, [%1];" : "=h"(leaf) : "r"(ltab_s + buf * 1024u + c * 32u + (uint32_t)lane));
-      const size_t e = (size_t)gprev.x * 32u + (size_t)c * slots + leaf;
-      pend[w] = __ldg(p.leaf_plane + e);
-      if (p.leaf_ids != nullptr && live) {
-        const int t = p.tree_index[(g0 + gi_prev) * 32 + (int)c];
-        if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
+      uint32_t leaf;
+      asm volatile("ld.shared.u8 %0, [%1];" : "=r"(leaf) : "r"(my_cols_s + buf * 1024u + (uint32_t)w * 32u));
+      const uint32_t e = gprev.x * 32u + c * slots + leaf;
+      if (LEAF_IDS) {
+        if (live) {
+          const int t = p.tree_index[(g0 + gi_prev) * 32 + (int)c];
+          if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
+        }
+      } else {
+        pend[w] = __ldg(p.leaf_plane + e);
       }
     }
   };
   uint2 gprev = make_uint2(0, 0);
   int gi_prev = -1;
+  // where this lane drops the leaf numbers of its two walks (buffer 0)
+  const uint32_t drop_s[2] = {ltab_s + col[0] * 32u + (uint32_t)lane, ltab_s + col[1] * 32u + (uint32_t)lane};
 
   for (int k = 0; k < NGh; ++k) {
     const int gi = 2 * k + half;
     const uint2 gm = gtab[gi];
-    const uint32_t depth = gm.y, hs = 1u << (depth - 1);
+    const uint32_t depth = UD ? (uint32_t)UD : gm.y, hs = 1u << (depth - 1);
     const int q = 2 * k;
     uint32_t idx[2] = {0, 0};
 
@@ -343,7 +354,11 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
       for (int w = 0; w < 2; ++w) {
         const uint32_t colbase = slot_addr(q) + col[w] * 4u;
         bool tie;
-        uint32_t s = (quant_walk_any(depth - 1, colbase, keys_lane, &tie) - colbase) >> 7;
+        uint32_t s;
+        if constexpr (UD > 0)
+          s = (quant_walk<UD - 1>(colbase, keys_lane, &tie) - colbase) >> 7;
+        else
+          s = (quant_walk_any(depth - 1, colbase, keys_lane, &tie) - colbase) >> 7;
         if (tie) {
           s = quant_walk_exact(colbase, keys_lane, p.exact_plane, gm.x, depth - 1, col[w], rowp);
           ++ties;
@@ -366,8 +381,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
           ++ties;
         }
         const uint32_t leaf = 2u * idx[w] + (right ? 1u : 0u);
-        asm volatile("st.shared.u8 [%0], %1;" ::"r"(ltab_s + ((uint32_t)k & 1u) * 1024u + col[w] * 32u + (uint32_t)lane),
-                     "h"((unsigned short)leaf));
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop_s[w] + ((uint32_t)k & 1u) * 1024u), "r"(leaf));
       }
       acc += pend[0] + pend[1]; // previous group's leaves have had a whole walk to arrive
       pend[0] = pend[1] = 0.f;
@@ -386,7 +400,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
     return;
   }
   if (p.tie_count != nullptr && ties) atomicAdd(p.tie_count, (unsigned long long)ties);
-  if (p.leaf_ids != nullptr) return;
+  if (LEAF_IDS) return;
 
   // ---- combine the 32 warps (one partial per row each)
   float *red = reinterpret_cast<float *>(smem_raw + 128 + p.meta_bytes);
