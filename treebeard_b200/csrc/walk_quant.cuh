@@ -228,15 +228,15 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   }
   __syncthreads();
 
-  auto issue = [&](int piece) {
+  auto issue = [&](int piece, int slot) { // slot = piece % 3
     const uint2 gm = gtab[2 * (piece >> 1) + half];
     const uint32_t hs = UD ? (1u << (UD ? UD - 1 : 0)) : 1u << (gm.y - 1); // slots per piece
     const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
-    uint64_t *bar = &full[piece % 3];
+    uint64_t *bar = &full[slot];
     mbar_expect_tx(bar, hs * 128u);
-    bulk_g2s(ring + (size_t)(piece % 3) * kQPiece, p.node_plane + off, hs * 128u, bar);
+    bulk_g2s(ring + (size_t)slot * kQPiece, p.node_plane + off, hs * 128u, bar);
   };
-  if (lane == 0 && hw < 3 && hw < P) issue(hw);
+  if (lane == 0 && hw < 3 && hw < P) issue(hw, hw);
 
   // ---- stage the row tile as keys: keys[f][row]
   {
@@ -288,21 +288,23 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   // One barrier per group over the half-block (it also carries any wait failure to its 512
   // threads, so that their exit is uniform) frees the group's two slots; the refills are
   // issued by two rotating warps.
+  // Two pieces per group through three slots: the slots of a group's pieces rotate with period
+  // three -- (0,1), (2,0), (1,2) -- and so do the phases of their barriers -- (0,0), (0,1),
+  // (1,1) -- whatever the group number; both follow from two counters, without divisions.
+  int su = 0, sb = 1; // ring slots of the current group's upper-level and bottom-level pieces
   auto release = [&](int first) {
     failed = half_barrier_or(1 + half, !ok);
     if (!failed && lane == 0) {
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int next = first + i + 3;
-        if (next < P && (next % kQHalfWarps) == hw) issue(next);
-      }
+      // pieces first+3 and first+4 land in the two slots just freed, in the same order
+      if (first + 3 < P && ((first + 3) % kQHalfWarps) == hw) issue(first + 3, su);
+      if (first + 4 < P && ((first + 4) % kQHalfWarps) == hw) issue(first + 4, sb);
     }
+    su = su == 0 ? 2 : su - 1;
+    sb = sb == 0 ? 2 : sb - 1;
   };
   const uint32_t full_s = smem_u32(full);
-  auto piece_ready = [&](int piece) {
-    return mbar_wait_all_lanes(full_s + 8u * (uint32_t)(piece % 3), (uint32_t)(piece / 3) & 1u);
-  };
-  auto slot_addr = [&](int piece) { return ring_s + (uint32_t)(piece % 3) * kQPiece; };
+  auto upper_ready = [&]() { return mbar_wait_all_lanes(full_s + 8u * (uint32_t)su, su == 1 ? 1u : 0u); };
+  auto bottom_ready = [&]() { return mbar_wait_all_lanes(full_s + 8u * (uint32_t)sb, sb != 1 ? 1u : 0u); };
 
   // Leaf values come straight from L2, but not in the walk's lane assignment: there the 32
   // lanes of a warp sit in 32 different trees, i.e. 32 different lines of the leaf plane
@@ -348,11 +350,11 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
     if (gi_prev >= 0) fetch_leaves(gi_prev, gprev, (uint32_t)(k - 1) & 1u);
 
     // upper levels 0 .. depth-2
-    ok = piece_ready(q);
+    ok = upper_ready();
     if (ok) {
 #pragma unroll
       for (int w = 0; w < 2; ++w) {
-        const uint32_t colbase = slot_addr(q) + col[w] * 4u;
+        const uint32_t colbase = ring_s + (uint32_t)su * kQPiece + col[w] * 4u;
         bool tie;
         uint32_t s;
         if constexpr (UD > 0)
@@ -368,11 +370,11 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
     }
 
     // bottom decision level; the leaf number goes into the table
-    if (ok) ok = piece_ready(q + 1);
+    if (ok) ok = bottom_ready();
     if (ok) {
 #pragma unroll
       for (int w = 0; w < 2; ++w) {
-        const uint32_t node = lds_u32(slot_addr(q + 1) + idx[w] * 128u + col[w] * 4u);
+        const uint32_t node = lds_u32(ring_s + (uint32_t)sb * kQPiece + idx[w] * 128u + col[w] * 4u);
         const uint32_t f = node >> 16, kt = node & 0xffffu;
         const uint32_t kx = lds_u16(keys_lane + f * 64u);
         bool right = kx < kt;
