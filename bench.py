@@ -34,7 +34,7 @@ HBM_FALLBACK_GBS = 6650.0
 # DRAM bytes per row (dram__bytes_read.sum + dram__bytes_write.sum) of the walk kernel, from
 # one ncu capture per workload on a reduced batch (see profiles/); traffic grows in
 # proportion to the rows, so a launch's traffic is this figure times its rows.
-NCU_DRAM_BYTES_PER_ROW = {"c3": 8186.0, "c2": 118.2, "c4": 76.3}
+NCU_DRAM_BYTES_PER_ROW = {"c3": 8189.0, "c2": 118.2, "c4": 76.3}
 
 
 def bytes_per_row(cfg):
