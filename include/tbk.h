@@ -170,7 +170,8 @@ TBK_EXPORT int tbk_predict_host(tbk_forest *forest, const float *h_rows, int64_t
  *     streams, or different forests) race on it.  Serialise them.  Nothing in it needs
  *     clearing between calls: every element read by the second pass is written by the walk
  *     of the same call.
- *   - Forests in the 16-bit key layout are not covered (TBK_ERR_UNSUPPORTED). */
+ *   - Forests in a 16-bit key layout (wide rows, deep trees) are not covered
+ *     (TBK_ERR_UNSUPPORTED). */
 TBK_EXPORT int tbk_predict_noalloc(tbk_forest *forest, const float *d_rows, int64_t n_rows, int64_t ld,
                                    void *d_out, int32_t out_kind, void *stream);
 
