@@ -72,6 +72,7 @@ struct tbk_forest {
   bool deep = false;
   tb::DeepForest df;
   int deep_row_warps = 0, deep_slots = 0;
+  int uniform_depth = 0; // key layouts: depth shared by all groups / pairs, 0 = mixed
   // host pipeline
   float *d_in[2] = {nullptr, nullptr};
   unsigned char *d_res[2] = {nullptr, nullptr};
@@ -212,12 +213,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   // kernels specialised for forests whose groups all have 8 (or 6) levels; generic otherwise
   using QuantKernel = void (*)(const tb::QuantParams);
   const bool ids = mode == kLeafIds;
-  uint32_t dmin = 0xffffffffu, dmax = 0;
-  for (const auto &g : q.groups) {
-    dmin = std::min(dmin, g.depth);
-    dmax = std::max(dmax, g.depth);
-  }
-  const int ud = (dmin == dmax && (dmin == 8 || dmin == 6)) ? (int)dmin : 0;
+  const int ud = (f->uniform_depth == 8 || f->uniform_depth == 6) ? f->uniform_depth : 0;
   const QuantKernel qkernel =
       ud == 8 ? (ids ? tb::tb_walk_quant_kernel<8, true> : tb::tb_walk_quant_kernel<8, false>)
       : ud == 6 ? (ids ? tb::tb_walk_quant_kernel<6, true> : tb::tb_walk_quant_kernel<6, false>)
@@ -341,12 +337,7 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
   // up to 20 warps the compiler may use 96 registers per thread, beyond that 64
   // specialised for forests whose pairs all have 12 levels; generic otherwise
   using DeepKernel = void (*)(const tb::DeepParams);
-  uint32_t dmin = 0xffffffffu, dmax = 0;
-  for (const auto &g : q.pairs) {
-    dmin = std::min(dmin, g.depth);
-    dmax = std::max(dmax, g.depth);
-  }
-  const bool d12 = dmin == 12 && dmax == 12, ids = mode == kLeafIds, small = plan.threads <= 640;
+  const bool d12 = f->uniform_depth == 12, ids = mode == kLeafIds, small = plan.threads <= 640;
   const DeepKernel kernel =
       small ? (d12 ? (ids ? tb::tb_walk_deep_kernel<640, 12, true> : tb::tb_walk_deep_kernel<640, 12, false>)
                    : (ids ? tb::tb_walk_deep_kernel<640, 0, true> : tb::tb_walk_deep_kernel<640, 0, false>))
@@ -499,6 +490,12 @@ int upload_key_planes(tbk_forest *f, const std::vector<uint32_t> &node, const st
                       const std::vector<float> &lo, const std::vector<float> &scale, int num_features) {
   const size_t n = node.size();
   static_assert(sizeof(tb::QuantGroup) == sizeof(tb::DevQuantGroup), "group metadata layout");
+  uint32_t dmin = 0xffffffffu, dmax = 0;
+  for (const auto &g : groups) {
+    dmin = std::min(dmin, g.depth);
+    dmax = std::max(dmax, g.depth);
+  }
+  f->uniform_depth = dmin == dmax ? (int)dmin : 0;
   CUDA_TRY(cudaMalloc(&f->d_qnode, n * 4));
   CUDA_TRY(cudaMalloc(&f->d_qleaf, n * 4));
   CUDA_TRY(cudaMalloc(&f->d_qexact, n * 4));
