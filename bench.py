@@ -106,6 +106,15 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def host_threads():
+    """Host threads this process may use.  torch.distributed.run exports OMP_NUM_THREADS=1
+    for its workers; the CPU arms size their OpenMP teams from the affinity mask instead."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def dist_env():
     return (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),
             int(os.environ.get("WORLD_SIZE", 1)))
@@ -119,11 +128,13 @@ def run_reference(args, cfg):
     rank, _, world = dist_env()
     if rank != 0:
         return
+    # before the OpenMP runtime starts: the reference's walker takes its team size from here
+    os.environ["OMP_NUM_THREADS"] = str(host_threads())
     from oracle import oracle
     forest, marg, n_full = synth.make_config(args.workload, rows=args.rows)
     n_full = args.rows or n_full
     use_ref = oracle.ref_lib() is not None and not args.port
-    threads = oracle.max_threads()
+    threads = host_threads()
     if use_ref:
         engine = oracle.RefForest(forest)
         run = engine.predict
@@ -328,7 +339,7 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import oracle
-        threads = oracle.max_threads()
+        threads = host_threads()
         base = oracle.CpuBaseline(forest)
         pilot = max(256, threads * 8)
         t0 = time.perf_counter()
