@@ -24,7 +24,7 @@ std::string pack_deep(const Forest &f, DeepForest *out) {
   if (!err.empty()) return err;
 
   std::vector<int32_t> depth(T);
-#pragma omp parallel for schedule(dynamic, 64)
+#pragma omp parallel for schedule(dynamic, 64) num_threads(pack_threads())
   for (int64_t t = 0; t < T; ++t) depth[t] = tree_depth(f, t);
   for (int64_t t = 0; t < T; ++t) q.max_depth = std::max(q.max_depth, depth[t]);
   if (q.max_depth > kDeepMaxDepth)
@@ -49,7 +49,7 @@ std::string pack_deep(const Forest &f, DeepForest *out) {
   q.exact_plane.assign(elems, 0.f);
   q.orig_leaf.assign(elems, -1);
 
-#pragma omp parallel for schedule(dynamic, 16)
+#pragma omp parallel for schedule(dynamic, 16) num_threads(pack_threads())
   for (int64_t g = 0; g < P; ++g) {
     const QuantGroup &gm = q.pairs[g];
     for (int c = 0; c < 2; ++c) {

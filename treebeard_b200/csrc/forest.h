@@ -34,4 +34,10 @@ std::string validate(const Forest &f);
 // Decision levels on the longest root-to-leaf path of tree t (a single leaf: 0).
 int32_t tree_depth(const Forest &f, int64_t t);
 
+// Threads for the packers' parallel loops: the machine's hardware threads (at most 32), not
+// the OpenMP default, which process launchers commonly pin to 1 (torch.distributed.run
+// exports OMP_NUM_THREADS=1 for its workers) although packing a large forest is the one
+// host-side step that takes seconds.  TBK_PACK_THREADS overrides.
+int pack_threads();
+
 } // namespace tb

@@ -10,6 +10,8 @@
 #include <map>
 #include <numeric>
 #include <queue>
+#include <cstdlib>
+#include <thread>
 
 namespace tb {
 
@@ -56,6 +58,15 @@ std::string validate(const Forest &f) {
     }
   }
   return "";
+}
+
+int pack_threads() {
+  if (const char *env = std::getenv("TBK_PACK_THREADS")) {
+    const int n = std::atoi(env);
+    if (n > 0) return n;
+  }
+  const unsigned hw = std::thread::hardware_concurrency();
+  return (int)std::min(32u, std::max(1u, hw));
 }
 
 int32_t tree_depth(const Forest &f, int64_t t) {
@@ -309,7 +320,7 @@ std::string pack_forest(const Forest &f, const PackOptions &opt, PackedForest *o
   std::vector<int32_t> tdepth(T);   // tile levels of each tree
   std::vector<int64_t> tcount(T);   // tiles of each tree
   int32_t max_depth = 0;
-#pragma omp parallel for schedule(dynamic, 16) reduction(max : max_depth)
+#pragma omp parallel for schedule(dynamic, 16) reduction(max : max_depth) num_threads(pack_threads())
   for (int64_t t = 0; t < T; ++t) {
     if (ts == 1) {
       tdepth[t] = tree_depth(f, t);
@@ -395,7 +406,7 @@ std::string pack_forest(const Forest &f, const PackOptions &opt, PackedForest *o
   p.blob.assign(blob_bytes, 0);
   p.orig_node.assign(orig_elems, -1);
 
-#pragma omp parallel for schedule(dynamic, 4)
+#pragma omp parallel for schedule(dynamic, 4) num_threads(pack_threads())
   for (int64_t g = 0; g < G; ++g) {
     const GroupMeta &gm = p.groups[g];
     TiledTree tt;

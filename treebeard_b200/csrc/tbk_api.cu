@@ -602,7 +602,7 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
     if (!verr.empty()) return bail(fail(TBK_ERR_INVALID, "%s", verr.c_str()));
   }
   int max_depth = 0;
-#pragma omp parallel for reduction(max : max_depth) schedule(dynamic, 64)
+#pragma omp parallel for reduction(max : max_depth) schedule(dynamic, 64) num_threads(tb::pack_threads())
   for (int64_t t = 0; t < T; ++t) max_depth = std::max(max_depth, (int)tb::tree_depth(host, t));
   bool want_quant = (bits == 16 && max_depth <= tb::kQuantMaxDepth) ||
                     (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits);
