@@ -204,10 +204,14 @@ TBK_EXPORT int tbk_host_layout_check(const tbk_forest_arrays *forest, const tbk_
 /* Host-only view of the launch-shape selector for a forest of the given shape (what the
  * reference's auto-scheduler decides in src/mlir/GPUAutoSchedule.cpp:318-472).  info
  * receives the schedule, shared-memory bytes and threads per block (reserved[0] = rows
- * cached in shared memory, reserved[1] = grid.x, reserved[2] = groups per tree chunk). */
+ * cached in shared memory, reserved[1] = grid.x, reserved[2] = groups per tree chunk,
+ * reserved[3] = 1 when class sums stay in registers, i.e. the block has no class table).
+ * partial_sums != 0 asks for the plan of a launch that writes per-row partial sums
+ * (tbk_predict_partial, tbk_predict_noalloc) instead of predictions. */
 TBK_EXPORT int tbk_plan_launch(int32_t num_features, int32_t num_classes, int64_t num_groups,
                                int64_t max_group_bytes, int32_t lut_bytes, const tbk_schedule *schedule,
-                               int64_t n_rows, int32_t smem_limit, int32_t num_sms, tbk_forest_info *info);
+                               int64_t n_rows, int32_t smem_limit, int32_t num_sms, int32_t partial_sums,
+                               tbk_forest_info *info);
 
 TBK_EXPORT const char *tbk_last_error(void);
 

@@ -396,3 +396,53 @@ def test_multiclass_with_an_empty_class(rows):
     want = (sums.shape[1] - 1 - np.argmax(sums[:, ::-1], axis=1)).astype(np.float32)  # last maximum
     assert_predictions_close(got[pick], want, forest, sums)
     assert (want == 7).any() and (want != 7).any()     # the empty class wins on some rows only
+
+
+def test_two_streams_share_one_forest():
+    """Calls on one forest from two streams reuse the forest's tree-chunk scratch: the second
+    stream must wait for the first call's second pass before its walk overwrites the sums."""
+    from treebeard_b200 import kernels
+    forest, X = small_config("c2", rows=8192)
+    other = np.ascontiguousarray(X[::-1])
+    want_a, want_b = oracle.predict(forest, X), oracle.predict(forest, other)
+    df = kernels.DeviceForest(forest, representation="sparse", tree_chunks=4, batch_hint=len(X))
+    a, b = _dev(X), _dev(other)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    outs = []
+    for it in range(6):
+        with torch.cuda.stream(s1):
+            oa = df.predict(a, stream=s1)
+        with torch.cuda.stream(s2):
+            ob = df.predict(b, stream=s2)
+        outs.append((oa, ob))
+    torch.cuda.synchronize()
+    df.check_status()
+    for oa, ob in outs:
+        assert_predictions_close(oa.cpu().numpy(), want_a)
+        assert_predictions_close(ob.cpu().numpy(), want_b)
+
+
+def test_runner_rejects_buffers_on_different_sides(tmp_path):
+    """Device buffers are an extension of the reference API: input and result must then both be
+    on the device (a host result buffer would be written by the kernel)."""
+    from treebeard_b200 import synth, treebeard
+    from treebeard_b200.treebeard import treebeardAPI
+    forest, X = small_config("c1")
+    runner = treebeard.TreebeardInferenceRunner.FromForestArrays(forest, treebeard.CompilerOptions(1024, 1))
+    host_out = np.zeros(1024, np.float32)
+    dev_in, dev_out = _dev(X), torch.zeros(1024, device="cuda")
+    with pytest.raises(treebeard.TreebeardRuntimeError, match="host memory"):
+        treebeardAPI.RunInference(runner.inferenceRunner, dev_in.data_ptr(), host_out.ctypes.data)
+    with pytest.raises(treebeard.TreebeardRuntimeError, match="device memory"):
+        treebeardAPI.RunInference(runner.inferenceRunner, X.ctypes.data, dev_out.data_ptr())
+    with pytest.raises(treebeard.TreebeardRuntimeError, match="shape"):
+        runner.RunInference(X[:, :4].copy())
+    assert_predictions_close(runner.RunInference(X), oracle.predict(forest, X))
+
+
+def test_sixteen_bit_keys_refuse_what_they_do_not_cover():
+    from treebeard_b200 import kernels
+    forest, _ = small_config("c4")
+    with pytest.raises(kernels.TbkError):
+        kernels.DeviceForest(forest, representation="auto", feature_bits=16)

@@ -110,3 +110,23 @@ def test_launch_plan_honours_user_schedule():
     assert info.schedule.tree_chunks == 3 and info.schedule.rows_per_thread == 2
     with pytest.raises(kernels.TbkError):
         kernels.plan_launch(128, 0, 1000, 1048448, 4096, cache_trees=1)
+
+
+@pytest.mark.parametrize("classes", [2, 3, 6, 26])
+def test_partial_sum_plans_always_hold_the_class_table(classes):
+    """A launch that writes per-class partial sums (tree shards, the entry point that does not
+    allocate) sums classes through a per-warp table in shared memory.  At large batches the
+    selector keeps class sums in registers and drops that table -- but never for such a launch:
+    its shared-memory size must include warps x classes x 32 floats."""
+    F, groups, gbytes = 28, 20, 20000
+    rows = 400000                                     # > 2 x 148 SMs x 32 warps x 32 rows
+    direct = kernels.plan_launch(F, classes, groups, gbytes, rows)
+    assert direct.reserved[3] == 1                    # predictions: class sums in registers
+    part = kernels.plan_launch(F, classes, groups, gbytes, rows, partial_sums=True)
+    assert part.reserved[3] == 0
+    warps = part.threads_per_block // 32
+    rt = 32 * part.schedule.rows_per_thread
+    table = warps * classes * rt * 4
+    rows_cache = (part.schedule.rows_per_block // rt) * (F + 1) * rt * 4
+    assert part.smem_bytes >= table + rows_cache
+    assert part.smem_bytes <= 232448

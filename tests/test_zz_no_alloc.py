@@ -66,3 +66,27 @@ def test_noalloc_multiclass_and_limits():
     keys = kernels.DeviceForest(wide, representation="auto")
     with pytest.raises(kernels.TbkError, match="16-bit key"):
         _noalloc(keys, torch.from_numpy(Xw).cuda())
+
+
+@pytest.mark.parametrize("classes", [2, 3])
+def test_noalloc_large_multiclass_batch_with_the_default_schedule(classes):
+    """A batch large enough for tbk_predict to keep class sums in registers (no class table in
+    shared memory): the entry point that does not allocate always writes partial sums, so its
+    launch plan must keep the table.  Same class ids as tbk_predict, twice in a row."""
+    from treebeard_b200 import kernels, synth
+    marg = synth.Marginal("int16", 16)
+    forest = synth.generate_forest(4321 + classes, 8 * classes, 6, 16, 0.1, 0.1, marg,
+                                   transform=synth.SOFTMAX, num_classes=classes)
+    rng = np.random.Generator(np.random.PCG64(99))
+    X = marg.sample_rows(rng, 320 * 1024)             # > 2 x 148 SMs x 32 warps x 32 rows
+    df = kernels.DeviceForest(forest, representation="sparse", batch_hint=len(X))
+    rows = torch.from_numpy(X).cuda()
+    want = df.predict(rows, int8=True)
+    for _ in range(2):
+        got = _noalloc(df, rows, int8=True)
+        torch.cuda.synchronize()
+        df.check_status()
+        assert torch.equal(got, want)
+    sample = slice(0, 2048)
+    ref, sums = oracle.predict(forest, X[sample], class_sums=True)
+    assert_predictions_close(got[sample].cpu().numpy(), ref, forest, sums)

@@ -124,6 +124,7 @@ struct InferenceRunner {
   int32_t inputWidth = 32, returnWidth = 32;
   bool returnFloat = true;
   int32_t numClasses = 0;
+  int32_t device = 0;
   int64_t kernelMicros = 0;
 };
 
@@ -220,6 +221,7 @@ InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &o
   r->returnWidth = opt.returnTypeWidth;
   r->returnFloat = opt.returnTypeFloatType;
   r->numClasses = forest.num_classes;
+  r->device = g_device;
   if (g_measure_kernel_time) tbk_set_timing(kf, 1);
   return r;
 }
@@ -298,10 +300,27 @@ bool write_compiled_model(const tb::Forest &forest, const CompilerOptions &opt, 
 
 void run_batch(InferenceRunner *r, void *inputs, void *results, int64_t rows) {
   const int32_t kind = (!r->returnFloat && r->returnWidth == 8) ? TBK_OUT_I8 : TBK_OUT_F32;
-  cudaPointerAttributes attr{};
-  const bool on_device = cudaPointerGetAttributes(&attr, inputs) == cudaSuccess &&
-                         (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged);
-  cudaGetLastError();
+  // Device buffers are an extension of the reference API (which only takes host buffers):
+  // inputs and results must then lie on the same side, and device buffers on the runner's GPU.
+  auto side = [](const void *ptr, int *device) {
+    cudaPointerAttributes attr{};
+    const bool ok = cudaPointerGetAttributes(&attr, ptr) == cudaSuccess;
+    cudaGetLastError();
+    *device = ok ? attr.device : -1;
+    return ok && (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged);
+  };
+  int in_dev = -1, out_dev = -1;
+  const bool on_device = side(inputs, &in_dev);
+  const bool out_on_device = side(results, &out_dev);
+  if (on_device != out_on_device) {
+    set_error(TBK_ERR_INVALID, on_device ? "inputs are in device memory but results are in host memory"
+                                         : "inputs are in host memory but results are in device memory");
+    return;
+  }
+  if (on_device && (in_dev != r->device || out_dev != r->device)) {
+    set_error(TBK_ERR_INVALID, "device buffers are not on the runner's GPU");
+    return;
+  }
   int rc = TBK_OK;
   const int runs = g_measure_kernel_time ? std::max(1, g_kernel_runs) : 1;
   if (on_device) {

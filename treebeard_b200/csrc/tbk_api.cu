@@ -58,8 +58,12 @@ struct tbk_forest {
   unsigned long long *d_orig_off = nullptr;
   int8_t *d_lut = nullptr;
   int32_t *d_status = nullptr;
-  float *d_scratch = nullptr; // tree-chunk partials
+  float *d_scratch = nullptr; // tree-chunk partials, two slots
   size_t scratch_bytes = 0;
+  // a slot's last user: a call on another stream waits for it before reusing the slot
+  cudaEvent_t scratch_done[2] = {nullptr, nullptr};
+  cudaStream_t scratch_stream[2] = {nullptr, nullptr};
+  bool scratch_used[2] = {false, false};
   // 16-bit-key layout (wide rows)
   bool quant = false;
   tb::QuantForest qf;
@@ -127,6 +131,22 @@ int ensure_scratch(tbk_forest *f, size_t bytes) {
   return TBK_OK;
 }
 
+// The tree-chunk partial sums of a call live in a slot of the forest's scratch buffer from the
+// walk until the second pass has read them.  Calls on one stream are ordered anyway; a call on
+// another stream first waits (on the device) for the slot's previous user.
+int scratch_acquire(tbk_forest *f, int slot, cudaStream_t stream) {
+  if (f->scratch_used[slot] && f->scratch_stream[slot] != stream)
+    CUDA_TRY(cudaStreamWaitEvent(stream, f->scratch_done[slot], 0));
+  return TBK_OK;
+}
+int scratch_release(tbk_forest *f, int slot, cudaStream_t stream) {
+  if (!f->scratch_done[slot]) CUDA_TRY(cudaEventCreateWithFlags(&f->scratch_done[slot], cudaEventDisableTiming));
+  CUDA_TRY(cudaEventRecord(f->scratch_done[slot], stream));
+  f->scratch_stream[slot] = stream;
+  f->scratch_used[slot] = true;
+  return TBK_OK;
+}
+
 int ensure_orig(tbk_forest *f) {
   if (f->d_orig_node) return TBK_OK;
   const auto &p = f->packed;
@@ -174,6 +194,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
 
   const bool need_partials = mode == kPartial || (mode == kPredict && chunks > 1);
   float *partial_dst = nullptr;
+  bool uses_scratch = false;
   if (need_partials) {
     if (mode == kPartial && chunks == 1) {
       partial_dst = d_partial;
@@ -182,6 +203,9 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
       int rc = ensure_scratch(f, 2 * need);
       if (rc) return rc;
       partial_dst = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(f->d_scratch) + (size_t)slot * (f->scratch_bytes / 2));
+      rc = scratch_acquire(f, slot, stream);
+      if (rc) return rc;
+      uses_scratch = true;
     }
   }
   tb::QuantParams p{};
@@ -239,6 +263,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
     CUDA_TRY(cudaEventRecord(f->ev1, stream));
     f->ev_pending = true;
   }
+  if (uses_scratch) return scratch_release(f, slot, stream);
   return TBK_OK;
 }
 
@@ -297,6 +322,7 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
 
   const bool need_partials = mode == kPartial || (mode == kPredict && chunks > 1);
   float *partial_dst = nullptr;
+  bool uses_scratch = false;
   if (need_partials) {
     if (mode == kPartial && chunks == 1) {
       partial_dst = d_partial;
@@ -305,6 +331,9 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
       int rc = ensure_scratch(f, 2 * need);
       if (rc) return rc;
       partial_dst = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(f->d_scratch) + (size_t)slot * (f->scratch_bytes / 2));
+      rc = scratch_acquire(f, slot, stream);
+      if (rc) return rc;
+      uses_scratch = true;
     }
   }
   tb::DeepParams p{};
@@ -364,6 +393,7 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
     CUDA_TRY(cudaEventRecord(f->ev1, stream));
     f->ev_pending = true;
   }
+  if (uses_scratch) return scratch_release(f, slot, stream);
   return TBK_OK;
 }
 
@@ -394,6 +424,7 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
   const int W = std::max(1, pk.num_classes);
   const bool need_partials = mode == kPartial || (mode == kPredict && plan.chunks > 1);
   float *partial_dst = nullptr;
+  bool uses_scratch = false;
   if (mode == kLeafIds) {
     int rc = ensure_orig(f);
     if (rc) return rc;
@@ -406,6 +437,9 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
       int rc = ensure_scratch(f, 2 * need);
       if (rc) return rc;
       partial_dst = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(f->d_scratch) + (size_t)slot * (f->scratch_bytes / 2));
+      rc = scratch_acquire(f, slot, stream);
+      if (rc) return rc;
+      uses_scratch = true;
     }
   }
 
@@ -467,6 +501,7 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
     CUDA_TRY(cudaEventRecord(f->ev1, stream));
     f->ev_pending = true;
   }
+  if (uses_scratch) return scratch_release(f, slot, stream);
   return TBK_OK;
 }
 
@@ -660,6 +695,10 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
                        max_depth, host.num_features));
     }
   }
+  if (bits == 16 && !want_quant)
+    return bail(fail(TBK_ERR_UNSUPPORTED, "16-bit feature keys cover single-output forests of at most %d levels, tile size 1 "
+                                          "(this forest: %d levels, %d classes, tile size %d)",
+                     tb::kDeepMaxDepth, max_depth, host.num_classes, ts));
   if (rep == TBK_REP_AUTO) rep = TBK_REP_SPARSE;
   if (want_quant) {
     const auto &q = f->qf;
@@ -745,6 +784,8 @@ int tbk_forest_free(tbk_forest *f) {
   cudaFree(f->d_qlo);
   cudaFree(f->d_qscale);
   cudaFree(f->d_ties);
+  for (int i = 0; i < 2; ++i)
+    if (f->scratch_done[i]) cudaEventDestroy(f->scratch_done[i]);
   if (f->ev0) cudaEventDestroy(f->ev0);
   if (f->ev1) cudaEventDestroy(f->ev1);
   delete f;
@@ -994,8 +1035,12 @@ extern "C" int tbk_predict_noalloc(tbk_forest *f, const float *d_rows, int64_t n
   tb::ForestShape shape{pk.num_features, pk.num_classes, (int64_t)pk.groups.size(), pk.max_group_bytes,
                         (int32_t)pk.lut.size(), pk.representation, pk.tile_size};
   tb::LaunchPlan plan;
-  std::string why = tb::select_launch(shape, f->user, n_rows, f->max_smem_optin, f->num_sms, false, &plan);
+  // this call always writes partial sums, so the plan must be one for partial output: its
+  // shared memory then includes the per-warp class table of a multiclass forest
+  std::string why = tb::select_launch(shape, f->user, n_rows, f->max_smem_optin, f->num_sms, false, &plan, true);
   if (!why.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", why.c_str());
+  if (plan.class_regs)
+    return fail(TBK_ERR_UNSUPPORTED, "tbk_predict_noalloc: launch plan keeps class sums in registers and cannot write partial sums");
   const int W = std::max(1, pk.num_classes);
   const size_t need = (size_t)plan.chunks * (size_t)n_rows * (size_t)W;
   if (need > kNoAllocScratchFloats)
@@ -1030,6 +1075,7 @@ extern "C" int tbk_predict_noalloc(tbk_forest *f, const float *d_rows, int64_t n
   p.stage_bytes = plan.staged ? plan.stage_bytes : 0;
   p.vec4_ok = (pk.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
   p.status = f->d_status;
+  p.class_regs = 0; // class sums go through the shared-memory table the plan has sized
   KernelFn fn = pick_kernel(pk.representation, pk.tile_size, plan.rows_per_lane, plan.staged, plan.cache_rows);
   CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
   dim3 grid((unsigned)plan.grid_x, (unsigned)plan.chunks), block((unsigned)plan.threads);
@@ -1132,14 +1178,14 @@ int tbk_host_layout_check(const tbk_forest_arrays *fa, const tbk_schedule *sched
 
 int tbk_plan_launch(int32_t num_features, int32_t num_classes, int64_t num_groups, int64_t max_group_bytes,
                     int32_t lut_bytes, const tbk_schedule *schedule, int64_t n_rows, int32_t smem_limit,
-                    int32_t num_sms, tbk_forest_info *info) {
+                    int32_t num_sms, int32_t partial_sums, tbk_forest_info *info) {
   if (!info) return fail(TBK_ERR_INVALID, "null argument");
   tbk_schedule user{};
   if (schedule) user = *schedule;
   tb::ForestShape shape{num_features, num_classes, num_groups, (uint64_t)max_group_bytes, lut_bytes,
                         user.representation, user.tile_size > 0 ? user.tile_size : 1};
   tb::LaunchPlan pl;
-  std::string why = tb::select_launch(shape, user, n_rows, smem_limit, num_sms, false, &pl);
+  std::string why = tb::select_launch(shape, user, n_rows, smem_limit, num_sms, false, &pl, partial_sums != 0);
   if (!why.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", why.c_str());
   std::memset(info, 0, sizeof *info);
   info->schedule = user;
@@ -1154,6 +1200,7 @@ int tbk_plan_launch(int32_t num_features, int32_t num_classes, int64_t num_group
   info->reserved[0] = pl.cache_rows;
   info->reserved[1] = (int32_t)std::min<int64_t>(pl.grid_x, 0x7fffffff);
   info->reserved[2] = pl.groups_per_chunk;
+  info->reserved[3] = pl.class_regs;
   return TBK_OK;
 }
 

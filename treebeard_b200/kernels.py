@@ -74,7 +74,7 @@ def lib():
         L.tbk_launch_count.restype = i64
         L.tbk_check_status.argtypes = [vp]
         L.tbk_host_layout_check.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp]
-        L.tbk_plan_launch.argtypes = [i32, i32, i64, i64, i32, vp, i64, i32, i32, vp]
+        L.tbk_plan_launch.argtypes = [i32, i32, i64, i64, i32, vp, i64, i32, i32, i32, vp]
         _bound = True
     return L
 
@@ -240,10 +240,10 @@ def host_layout_check(forest, rows: Optional[np.ndarray], **schedule):
 
 def plan_launch(num_features: int, num_classes: int, num_groups: int, max_group_bytes: int,
                 n_rows: int, lut_bytes: int = 2, smem_limit: int = 232448, num_sms: int = 148,
-                **schedule) -> ForestInfoC:
+                partial_sums: bool = False, **schedule) -> ForestInfoC:
     sched = make_schedule(**schedule)
     info = ForestInfoC()
     _check(lib().tbk_plan_launch(num_features, num_classes, num_groups, max_group_bytes, lut_bytes,
                                  ctypes.byref(sched), n_rows, smem_limit, num_sms,
-                                 ctypes.byref(info)))
+                                 1 if partial_sums else 0, ctypes.byref(info)))
     return info

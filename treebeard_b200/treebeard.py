@@ -342,14 +342,25 @@ class TreebeardInferenceRunner:
     def _is_int8(self):
         return _rt.TB_GetReturnTypeBitWidth(self.inferenceRunner) == 8
 
+    def _check_shape(self, inputs, rows):
+        """The library reads rows x GetRowSize floats: a smaller buffer would be overrun."""
+        shape = tuple(inputs.shape)
+        ok = (len(shape) == 2 and shape[1] == self.rowSize and (rows is None or shape[0] == rows)) or \
+             (len(shape) == 1 and rows is not None and shape[0] == rows * self.rowSize)
+        if not ok:
+            want = f"({rows if rows is not None else 'n'}, {self.rowSize})"
+            raise TreebeardRuntimeError(f"inputs have shape {shape}, the runner expects {want}")
+
     def RunInference(self, inputs, resultType=numpy.float32):
         if isinstance(inputs, numpy.ndarray):
             assert inputs.dtype == numpy.float32 and inputs.flags.c_contiguous
+            self._check_shape(inputs, self.batchSize)
             results = numpy.zeros((self.batchSize), resultType)
             self.treebeardAPI.RunInference(self.inferenceRunner, inputs.ctypes.data, results.ctypes.data)
             return results
         import torch  # device-resident path
         assert inputs.is_cuda and inputs.dtype == torch.float32 and inputs.is_contiguous()
+        self._check_shape(inputs, self.batchSize)
         results = torch.zeros(self.batchSize, device=inputs.device,
                               dtype=torch.int8 if self._is_int8() else torch.float32)
         self.treebeardAPI.RunInference(self.inferenceRunner, inputs.data_ptr(), results.data_ptr())
@@ -357,6 +368,8 @@ class TreebeardInferenceRunner:
 
     def RunInferenceOnMultipleBatches(self, inputs, resultType=numpy.float32):
         assert type(inputs) is numpy.ndarray
+        assert inputs.dtype == numpy.float32 and inputs.flags.c_contiguous
+        self._check_shape(inputs, None)
         numRows = inputs.shape[0]
         results = numpy.zeros((numRows), resultType)
         self.treebeardAPI.RunInferenceOnMultipleBatches(self.inferenceRunner, inputs.ctypes.data,
