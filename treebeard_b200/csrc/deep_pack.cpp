@@ -20,7 +20,7 @@ std::string pack_deep(const Forest &f, DeepForest *out) {
   q.initial_value = f.initial_value;
   q.num_trees = T;
   q.num_nodes = f.num_nodes();
-  err = quant_feature_ranges(f, &q.lo, &q.scale);
+  err = quant_feature_ranges(f, kKey16Span, &q.lo, &q.scale);
   if (!err.empty()) return err;
 
   std::vector<int32_t> depth(T);

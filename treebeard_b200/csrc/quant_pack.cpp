@@ -6,7 +6,7 @@
 
 namespace tb {
 
-std::string quant_feature_ranges(const Forest &f, std::vector<float> *lo_out, std::vector<float> *scale_out) {
+std::string quant_feature_ranges(const Forest &f, float span, std::vector<float> *lo_out, std::vector<float> *scale_out) {
   const int F = f.num_features;
   std::vector<float> lo(F + 1, std::numeric_limits<float>::infinity());
   std::vector<float> hi(F + 1, -std::numeric_limits<float>::infinity());
@@ -22,9 +22,9 @@ std::string quant_feature_ranges(const Forest &f, std::vector<float> *lo_out, st
     if (!(hi[i] >= lo[i])) continue; // feature not used by any split
     (*lo_out)[i] = lo[i];
     // a single threshold needs no range: any huge slope separates everything but x == t
-    // 65531 (not 65532) keeps the key of the largest threshold at >= 1 under rounding, so
-    // that it never ties with the saturated key 0 of everything above it
-    float s = hi[i] > lo[i] ? 65531.0f / (hi[i] - lo[i]) : 0x1p40f;
+    // the span is two steps short of the key range, which keeps the keys of the smallest and
+    // the largest threshold off the two saturated keys under rounding
+    float s = hi[i] > lo[i] ? span / (hi[i] - lo[i]) : 0x1p40f;
     if (!std::isfinite(s) || s <= 0.f) s = 0x1p40f;
     (*scale_out)[i] = s;
   }
@@ -35,7 +35,7 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
   std::string err = validate(f);
   if (!err.empty()) return err;
   if (f.num_classes > 0) return "16-bit feature keys are implemented for single-output forests only";
-  if (f.num_features > 65534) return "more than 65534 features";
+  if (f.num_features > kQuantMaxFeatures) return "more than " + std::to_string(kQuantMaxFeatures) + " features";
   const int64_t T = f.num_trees();
   const int F = f.num_features;
 
@@ -47,7 +47,7 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
   q.num_trees = T;
   q.num_nodes = f.num_nodes();
 
-  err = quant_feature_ranges(f, &q.lo, &q.scale);
+  err = quant_feature_ranges(f, kKey15Span, &q.lo, &q.scale);
   if (!err.empty()) return err;
 
   std::vector<int32_t> depth(T);
@@ -72,7 +72,7 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
     q.groups[g] = QuantGroup{elems, d, 1u << d};
     elems += (uint64_t)(1u << d) * kQuantCols;
   }
-  const uint32_t pass_through = (uint32_t)F << 16; // sentinel feature, key 0: always left
+  const uint32_t pass_through = quant_feature_code((uint32_t)F) << 16; // sentinel feature, key 0: always left
   q.node_plane.assign(elems, pass_through);
   q.leaf_plane.assign(elems, 0.f);
   q.exact_plane.assign(elems, 0.f);
@@ -101,7 +101,7 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
         const int32_t ft = f.feat[a + it.node];
         const float thr = f.thr[a + it.node];
         const uint64_t e = gm.elem_off + (uint64_t)quant_plane_slot(it.slot, it.level, gm.depth) * kQuantCols + c;
-        q.node_plane[e] = ((uint32_t)ft << 16) | quant_key(thr, q.lo[ft], q.scale[ft]);
+        q.node_plane[e] = (quant_feature_code((uint32_t)ft) << 16) | quant_key15(thr, q.lo[ft], q.scale[ft]);
         q.exact_plane[e] = thr;
         stack.push_back({f.left[a + it.node], 2 * it.slot + 1, it.level + 1});
         stack.push_back({f.right[a + it.node], 2 * it.slot + 2, it.level + 1});
@@ -118,8 +118,8 @@ void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows,
   std::vector<uint16_t> keys(F + 1);
   for (int64_t r = 0; r < n_rows; ++r) {
     const float *row = rows + r * ld;
-    for (int i = 0; i < F; ++i) keys[i] = quant_key(row[i], q.lo[i], q.scale[i]);
-    keys[F] = 65535;
+    for (int i = 0; i < F; ++i) keys[i] = quant_key15(row[i], q.lo[i], q.scale[i]);
+    keys[F] = (uint16_t)kKey15Max;
     float acc = 0.f;
     for (size_t g = 0; g < q.groups.size(); ++g) {
       const QuantGroup &gm = q.groups[g];
@@ -130,7 +130,7 @@ void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows,
         for (uint32_t d = 0; d < gm.depth; ++d) {
           const uint64_t e = gm.elem_off + (uint64_t)quant_plane_slot(n, d, gm.depth) * kQuantCols + c;
           const uint32_t node = q.node_plane[e];
-          const uint32_t ft = node >> 16, kt = node & 0xffffu, kx = keys[ft];
+          const uint32_t ft = quant_feature_of_code(node >> 16), kt = node & 0x7fffu, kx = keys[ft];
           bool right = kx < kt;
           if (kx == kt) {
             ++tie_count;

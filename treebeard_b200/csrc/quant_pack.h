@@ -8,21 +8,29 @@
 // node-major planes, every tree padded to a complete tree, implicit children 2n+1+k)
 // per group of 32 trees:
 //
-//   node plane   u32 [2^D slots][32 columns]   (feature index << 16) | threshold key
+//   node plane   u32 [2^D slots][32 columns]   (feature code << 16) | threshold key
 //   leaf plane   f32 [32 columns][2^D leaves]  leaf values, column-major: the leaves that a
 //                                              warp needs for ONE tree lie within 1 KB
 //   exact plane  f32 [2^D slots][32 columns]   fp32 thresholds (global memory only)
 //
-// Keys.  For feature f with thresholds in [lo_f, hi_f]:
-//     key(v) = sat_u16( floor( fma(v - lo_f, -a_f, 65533) ) ),  a_f = 65531 / (hi_f - lo_f)
-// a non-increasing map (NaN -> 0, +inf -> 0, -inf -> 65535).  For a row value x and a
-// threshold t of the same feature:  key(x) > key(t)  =>  x < t  (left);
-// key(x) < key(t)  =>  x > t  (right);  equal keys decide nothing, and the kernel then
-// compares the exact fp32 values.  Leaf selection is therefore exactly that of the fp32
-// walk; only speed depends on how often keys tie.
+// Keys are 15-bit integers in [1024, 31743], i.e. bit patterns of positive, finite, normal
+// half-precision numbers, so that the kernel can compare the low halves of two registers
+// with ONE half2 comparison (no mask, no shift) and bit 15 of a node word is always 0.
+// For feature f with thresholds in [lo_f, hi_f]:
+//     key(v) = floor( min( max( fma(v - lo_f, -a_f, 31741), 1024 ), 31743 ) ),
+//     a_f = 30715 / (hi_f - lo_f)
+// a non-increasing map (NaN -> 1024, +inf -> 1024, -inf -> 31743; thresholds land in
+// [1025, 31742]).  For a row value x and a threshold t of the same feature:
+// key(x) > key(t)  =>  x < t  (left);  key(x) < key(t)  =>  x > t  (right);  equal keys
+// decide nothing, and the kernel then compares the exact fp32 values.  Leaf selection is
+// therefore exactly that of the fp32 walk; only speed depends on how often keys tie.
+//
+// The feature code of feature f is (f >> 1) * 64 + (f & 1): twice that is the byte offset of
+// the feature's key inside a lane's column of the kernel's key tile, which keeps features
+// 2m and 2m+1 of one row in one 32-bit word (see walk_quant.cuh).
 //
 // A leaf above the bottom level becomes a chain of pass-through nodes that name the
-// sentinel feature (index num_features, staged key 65535) with key 0: always left.
+// sentinel feature (index num_features, staged key 31743) with key 0: always left.
 #pragma once
 #include "forest.h"
 
@@ -35,6 +43,7 @@ namespace tb {
 
 constexpr int kQuantCols = 32;
 constexpr int kQuantMaxDepth = 8; // node planes of at most 2^8 * 128 B = 32 KB: two 16 KB stages
+constexpr int kQuantMaxFeatures = 2046; // feature codes (sentinel included) fit 16 bits
 
 struct QuantGroup {
   uint64_t elem_off; // offset of the group's planes, in elements (same for all planes)
@@ -70,8 +79,9 @@ inline uint64_t quant_leaf_elem(const QuantGroup &g, uint64_t leaf, uint32_t col
   return g.elem_off + (uint64_t)col * g.slots + leaf;
 }
 
-// host restatement of the key function (the device computes keys with the same
-// arithmetic: one subtraction, one fused multiply-add, one floor-and-saturate)
+// host restatement of the 16-bit key function of the deep-tree layout (deep_pack.h; the
+// device computes keys with the same arithmetic: one subtraction, one fused multiply-add,
+// one floor-and-saturate)
 inline uint16_t quant_key(float v, float lo, float scale) {
   const float y = std::fmaf(v - lo, -scale, 65533.0f);
   if (std::isnan(y)) return 0;
@@ -81,10 +91,23 @@ inline uint16_t quant_key(float v, float lo, float scale) {
   return (uint16_t)fl;
 }
 
+// 15-bit keys of this layout (see the head of the file); same arithmetic on the device.
+constexpr float kKey15Top = 31741.0f, kKey15Min = 1024.0f, kKey15Max = 31743.0f;
+constexpr float kKey15Span = 30715.0f; // keys between the smallest and the largest threshold
+constexpr float kKey16Span = 65531.0f;
+inline uint16_t quant_key15(float v, float lo, float scale) {
+  float y = std::fmaf(v - lo, -scale, kKey15Top);
+  y = std::fmin(std::fmax(y, kKey15Min), kKey15Max); // fmax first: NaN becomes the smallest key
+  return (uint16_t)std::floor(y);
+}
+inline uint32_t quant_feature_code(uint32_t f) { return (f >> 1) * 64u + (f & 1u); }
+inline uint32_t quant_feature_of_code(uint32_t code) { return (code >> 6) * 2u + (code & 1u); }
+
 // Per-feature key parameters (entries 0..num_features; the last belongs to the sentinel
-// feature): lo = smallest threshold of the feature, scale = a_f above.  Fails on a
-// non-finite threshold or leaf value.
-std::string quant_feature_ranges(const Forest &f, std::vector<float> *lo, std::vector<float> *scale);
+// feature): lo = smallest threshold of the feature, scale = span / (hi - lo), span being
+// the number of key steps between the smallest and the largest threshold (kKey15Span here,
+// kKey16Span in the deep-tree layout).  Fails on a non-finite threshold or leaf value.
+std::string quant_feature_ranges(const Forest &f, float span, std::vector<float> *lo, std::vector<float> *scale);
 
 // Empty string on success.  Fails (so that the caller can fall back to another layout)
 // for multiclass forests, trees deeper than kQuantMaxDepth, or non-finite thresholds.

@@ -159,12 +159,11 @@ int ensure_orig(tbk_forest *f) {
 
 enum Mode { kPredict, kPartial, kLeafIds };
 
-int quant_meta_bytes(int groups_per_chunk) { return (groups_per_chunk * 8 + 127) / 128 * 128; }
-int quant_smem_bytes(int num_features, int groups_per_chunk = tb::kQMaxGroupsPerChunk) {
-  return 128 + quant_meta_bytes(groups_per_chunk) + tb::kQRingBytes + tb::kQLeafTableBytes + (num_features + 1) * 64;
+int quant_smem_bytes(int num_features) {
+  return 128 + tb::kQRingBytes + tb::kQLeafTableBytes + tb::quant_key_tile_bytes(num_features);
 }
 
-// One prediction with the 16-bit-key kernel (one block per 32 rows, 32 warps).
+// One prediction with the 16-bit-key kernel (one block per 32 rows: 16 walker warps, 2 producers).
 int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
               float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot) {
   const auto &q = f->qf;
@@ -173,22 +172,20 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   int64_t chunks = 1;
   if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
   else if (grid_x < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + grid_x - 1) / grid_x;
-  // the group table of a chunk lives in shared memory: bound the groups per chunk
-  chunks = std::max<int64_t>(chunks, (G + tb::kQMaxGroupsPerChunk - 1) / tb::kQMaxGroupsPerChunk);
   chunks = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(chunks, G), 65535));
   const int gpc = (int)((G + chunks - 1) / chunks);
   chunks = (G + gpc - 1) / gpc;
   tb::LaunchPlan plan;
   plan.row_warps = 1;
-  plan.tree_threads = 32;
+  plan.tree_threads = tb::kQWalkers;
   plan.rows_per_lane = 1;
   plan.chunks = (int32_t)chunks;
   plan.groups_per_chunk = gpc;
   plan.staged = 1;
   plan.cache_rows = 1;
   plan.stage_bytes = tb::kQPiece;
-  plan.smem_bytes = quant_smem_bytes(q.num_features, gpc);
-  plan.threads = 1024;
+  plan.smem_bytes = quant_smem_bytes(q.num_features);
+  plan.threads = tb::kQThreads;
   plan.grid_x = grid_x;
   f->last_plan = plan;
 
@@ -233,7 +230,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   p.vec4_ok = (q.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
   p.status = f->d_status;
   p.tie_count = f->d_ties;
-  p.meta_bytes = quant_meta_bytes(gpc);
+  p.meta_bytes = 0;
   // kernels specialised for forests whose groups all have 8 (or 6) levels; generic otherwise
   using QuantKernel = void (*)(const tb::QuantParams);
   const bool ids = mode == kLeafIds;
@@ -245,7 +242,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   CUDA_TRY(cudaFuncSetAttribute((const void *)qkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
   if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
   dim3 grid((unsigned)grid_x, (unsigned)chunks);
-  qkernel<<<grid, 1024, plan.smem_bytes, stream>>>(p);
+  qkernel<<<grid, tb::kQThreads, plan.smem_bytes, stream>>>(p);
   CUDA_TRY(cudaGetLastError());
   ++f->launches;
   const int tpb = 256;
@@ -522,7 +519,7 @@ int check_status(tbk_forest *f) {
 int upload_key_planes(tbk_forest *f, const std::vector<uint32_t> &node, const std::vector<float> &leaf,
                       const std::vector<float> &exact, const std::vector<int32_t> &orig,
                       const std::vector<tb::QuantGroup> &groups, const std::vector<int32_t> &tree_index,
-                      const std::vector<float> &lo, const std::vector<float> &scale, int num_features) {
+                      const std::vector<float> &lo, const std::vector<float> &scale, int num_features, bool wide) {
   const size_t n = node.size();
   static_assert(sizeof(tb::QuantGroup) == sizeof(tb::DevQuantGroup), "group metadata layout");
   uint32_t dmin = 0xffffffffu, dmax = 0;
@@ -554,7 +551,7 @@ int upload_key_planes(tbk_forest *f, const std::vector<uint32_t> &node, const st
   CUDA_TRY(cudaMemcpy(f->d_qlo, lo.data(), lo.size() * 4, cudaMemcpyHostToDevice));
   CUDA_TRY(cudaMemcpy(f->d_qscale, scale.data(), scale.size() * 4, cudaMemcpyHostToDevice));
   tb::tb_quant_fill_keys<<<(unsigned)((n + 255) / 256), 256>>>(f->d_qnode, f->d_qexact, f->d_qlo, f->d_qscale,
-                                                             (unsigned long long)n, num_features);
+                                                             (unsigned long long)n, num_features, wide ? 1 : 0);
   CUDA_TRY(cudaGetLastError());
   CUDA_TRY(cudaDeviceSynchronize());
   ++f->launches;
@@ -676,7 +673,7 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
         f->packed.num_nodes = q.num_nodes;
         f->packed.max_depth = q.max_depth;
         int urc = upload_key_planes(f, q.node_plane, q.leaf_plane, q.exact_plane, q.orig_leaf, q.pairs, q.tree_index,
-                                    q.lo, q.scale, q.num_features);
+                                    q.lo, q.scale, q.num_features, false);
         if (urc != TBK_OK) return bail(urc);
         std::vector<uint32_t>().swap(q.node_plane);
         std::vector<float>().swap(q.leaf_plane);
@@ -714,7 +711,7 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
     f->packed.num_nodes = q.num_nodes;
     f->packed.max_depth = q.max_depth;
     int urc = upload_key_planes(f, q.node_plane, q.leaf_plane, q.exact_plane, q.orig_leaf, q.groups, q.tree_index,
-                                q.lo, q.scale, q.num_features);
+                                q.lo, q.scale, q.num_features, true);
     if (urc != TBK_OK) return bail(urc);
     // host copies of the big planes are no longer needed
     std::vector<uint32_t>().swap(f->qf.node_plane);
@@ -722,8 +719,8 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
     std::vector<float>().swap(f->qf.exact_plane);
     std::vector<int32_t>().swap(f->qf.orig_leaf);
     tb::LaunchPlan &pl = f->last_plan;
-    pl.row_warps = 1; pl.tree_threads = 32; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
-    pl.stage_bytes = tb::kQPiece; pl.smem_bytes = quant_smem_bytes(q.num_features); pl.threads = 1024;
+    pl.row_warps = 1; pl.tree_threads = tb::kQWalkers; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
+    pl.stage_bytes = tb::kQPiece; pl.smem_bytes = quant_smem_bytes(q.num_features); pl.threads = tb::kQThreads;
     *out = f;
     return TBK_OK;
   }

@@ -1,10 +1,12 @@
 // Walk kernel for the 16-bit-key layout (quant_pack.h): forests over rows too wide for
 // an fp32 row tile.
 //
-// One block = 32 warps = one tile of 32 rows, staged ONCE per block as 16-bit keys,
-// transposed (keys[feature][row]).  Lane = row.  The block works as TWO independent halves
-// of 16 warps: half h takes the groups h, h+2, ... of the chunk for all 32 rows; warp w of
-// a half walks, in every group of 32 trees, the columns (lane + w) mod 32 and
+// One block = 32 warps = one tile of 32 rows, staged ONCE per block as 15-bit keys,
+// transposed and paired: line m of the key tile (128 bytes) holds, for row j in word j, the
+// keys of features 2m (low half) and 2m+1 (high half).  Lane = row, so a key load of a warp
+// touches 32 distinct banks whatever the features are.  The block works as TWO independent
+// halves of 16 warps: half h takes the groups h, h+2, ... of the chunk for all 32 rows; warp
+// w of a half walks, in every group of 32 trees, the columns (lane + w) mod 32 and
 // (lane + w + 16) mod 32 in lock-step, so the 32 lanes of a warp read 32 distinct columns
 // of the node plane (one shared-memory wavefront per load) and the half covers every
 // (row, tree) pair of the group exactly once.  While one half waits for a piece or sits in
@@ -20,10 +22,14 @@
 // all 32 rows (see fetch_leaves).  Per-row sums live in registers and are combined across
 // the 32 warps once, at the end.
 //
-// The walk is fully unrolled per depth: one key load, one compare, one node load per level.
-// Key ties are only flagged on the fast path; a flagged (row, tree)
-// pair is then re-walked on the exact fp32 values from global memory.  Every lane polls
-// the stage barrier itself (mbarrier.try_wait, bounded).
+// The walk is fully unrolled per depth and written in PTX, both columns of a lane
+// interleaved.  A level costs one key load, two half2 comparisons on the low halves of
+// (key, node word) -- "less than" picks the child, "equal" accumulates the tie flag -- one
+// shift-add, one predicated add and one node load; the key's address is the node word
+// shifted right by 15 plus the lane's base (bit 15 of a node word is 0, the feature code in
+// the upper half is the key's byte offset halved).  Key ties are only flagged on the fast
+// path; a flagged (row, tree) pair is then re-walked on the exact fp32 values from global
+// memory.  Every lane polls the stage barrier itself (mbarrier.try_wait, bounded).
 //
 // Reference counterparts: the walk of src/mlir/CodeGenStateMachine.cpp:149-243 over the
 // reorg layout (src/gpu/ReorgForestRepresentation.cpp:495-571), the unrolled walk of
@@ -60,20 +66,28 @@ struct QuantParams {
   int32_t num_groups, groups_per_chunk, num_features, transform;
   float initial_value;
   int32_t vec4_ok;
-  int32_t meta_bytes;            // shared-memory bytes reserved for the group table
+  int32_t meta_bytes;            // unused (kept for the layout of the parameter block)
   int32_t *status;
   unsigned long long *tie_count; // optional statistics
 };
 
 constexpr int kQRingBytes = 6 * 16384; // two half-blocks x three 16 KB pieces
-constexpr int kQMaxGroupsPerChunk = 160;
 constexpr int kQLeafTableBytes = 4096; // [2 halves][2 buffers][32 columns][32 rows] leaf numbers
 constexpr uint32_t kQWaitTries = 1u << 20;
 
+// 16-bit keys of the deep-tree layout (walk_deep.cuh).
 __device__ __forceinline__ uint32_t quant_key_dev(float v, float lo, float sc) {
   const float y = __fmaf_rn(__fsub_rn(v, lo), -sc, 65533.0f);
   unsigned short h;
   asm("cvt.rmi.u16.f32 %0, %1;" : "=h"(h) : "f"(y)); // floor, clamp to [0, 65535], NaN -> 0
+  return h;
+}
+// 15-bit keys of this layout: integers in [1024, 31743] (quant_pack.h); NaN -> 1024.
+__device__ __forceinline__ uint32_t quant_key15_dev(float v, float lo, float sc) {
+  float y = __fmaf_rn(__fsub_rn(v, lo), -sc, 31741.0f);
+  y = fminf(fmaxf(y, 1024.0f), 31743.0f);
+  unsigned short h;
+  asm("cvt.rmi.u16.f32 %0, %1;" : "=h"(h) : "f"(y));
   return h;
 }
 
@@ -109,105 +123,187 @@ __device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t 
   return false;
 }
 
-// Fast walk of DEPTH levels of one column of a staged node plane.  Returns the byte
-// address of the slot reached (colbase + 128 * slot); *tie is set when any key
-// comparison on the path tied (the result is then not to be trusted).
+// ---------------------------------------------------------------------------
+// The walk of four columns in lock-step, in PTX.  Operands of every block:
+//   %0..%3    byte addresses of the current nodes of columns 0..3 (updated)
+//   %4..%7    node words (updated)
+//   %8        tie flags, bit i = column i (updated)
+//   %9        the lane's base in the key tile
+//   %10..%13  address constants of the step per column, see quant_upper4
+// A node at address A has its children at 2A + c (left) and 2A + c + 128 (right).
+#define TBQ_FLAG_IN(i, bit) "and.b32 ka" #i ", %8, " #bit ";\n setp.ne.u32 t" #i ", ka" #i ", 0;\n"
+#define TBQ_DECL                                                                          \
+  ".reg .b32 ka0, ka1, ka2, ka3, kx0, kx1, kx2, kx3;\n"                                   \
+  ".reg .pred p0, p1, p2, p3, t0, t1, t2, t3, q;\n"                                       \
+  TBQ_FLAG_IN(0, 1) TBQ_FLAG_IN(1, 2) TBQ_FLAG_IN(2, 4) TBQ_FLAG_IN(3, 8)
+#define TBQ_KEY(i, n) "shr.u32 ka" #i ", " n ", 15;\n add.u32 ka" #i ", ka" #i ", %9;\n ld.shared.u16 kx" #i ", [ka" #i "];\n"
+#define TBQ_CMP(i, n) "setp.lt.f16x2 p" #i "|q, kx" #i ", " n ";\n setp.eq.or.f16x2 t" #i "|q, kx" #i ", " n ", t" #i ";\n"
+#define TBQ_ADV(i, a, c) "shl.b32 " a ", " a ", 1;\n add.u32 " a ", " a ", " c ";\n @p" #i " add.u32 " a ", " a ", 128;\n"
+#define TBQ_LD(a, n) "ld.shared.u32 " n ", [" a "];\n"
+#define TBQ_LEAF(i, a, c) "sub.u32 " a ", " a ", " c ";\n shr.u32 " a ", " a ", 6;\n @p" #i " add.u32 " a ", " a ", 1;\n"
+#define TBQ_COMPARE                                                                       \
+  TBQ_KEY(0, "%4") TBQ_KEY(1, "%5") TBQ_KEY(2, "%6") TBQ_KEY(3, "%7")                     \
+  TBQ_CMP(0, "%4") TBQ_CMP(1, "%5") TBQ_CMP(2, "%6") TBQ_CMP(3, "%7")
+#define TBQ_ADVANCE TBQ_ADV(0, "%0", "%10") TBQ_ADV(1, "%1", "%11") TBQ_ADV(2, "%2", "%12") TBQ_ADV(3, "%3", "%13")
+#define TBQ_LOAD TBQ_LD("%0", "%4") TBQ_LD("%1", "%5") TBQ_LD("%2", "%6") TBQ_LD("%3", "%7")
+#define TBQ_LEAVES TBQ_LEAF(0, "%0", "%10") TBQ_LEAF(1, "%1", "%11") TBQ_LEAF(2, "%2", "%12") TBQ_LEAF(3, "%3", "%13")
+#define TBQ_TIES "selp.u32 %8, 1, 0, t0;\n @t1 or.b32 %8, %8, 2;\n @t2 or.b32 %8, %8, 4;\n @t3 or.b32 %8, %8, 8;\n"
+#define TBQ_STEP TBQ_COMPARE TBQ_ADVANCE TBQ_LOAD
+#define TBQ_OPERANDS                                                                      \
+  : "+r"(A[0]), "+r"(A[1]), "+r"(A[2]), "+r"(A[3]), "+r"(n[0]), "+r"(n[1]), "+r"(n[2]), "+r"(n[3]), "+r"(ties)      \
+  : "r"(keys_lane), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3])
+
+// STEPS levels inside the upper-level piece: compare, move to the child, load it.
+template <int STEPS>
+__device__ __forceinline__ void quant_steps4(uint32_t (&A)[4], uint32_t (&n)[4], uint32_t &ties, uint32_t keys_lane,
+                                             const uint32_t (&c)[4]) {
+  static_assert(STEPS >= 0 && STEPS <= 6, "at most six levels above the last upper level");
+  if constexpr (STEPS == 1)
+    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
+  else if constexpr (STEPS == 2)
+    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
+  else if constexpr (STEPS == 3)
+    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
+  else if constexpr (STEPS == 4)
+    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
+  else if constexpr (STEPS == 5)
+    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
+  else if constexpr (STEPS == 6)
+    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
+}
+// The last upper level: compare and compute the address in the bottom-level piece (the
+// constants carry the change of piece); nothing is loaded, the piece may not have arrived.
+__device__ __forceinline__ void quant_cross4(uint32_t (&A)[4], uint32_t (&n)[4], uint32_t &ties, uint32_t keys_lane,
+                                             const uint32_t (&c)[4]) {
+  asm volatile("{\n" TBQ_DECL TBQ_COMPARE TBQ_ADVANCE TBQ_TIES "}" TBQ_OPERANDS);
+}
+// The bottom level: load the node, compare; A[i] becomes the leaf number
+// ((A - c) >> 6) + went right, c = address of the column's first bottom-level node.
+__device__ __forceinline__ void quant_bottom4(uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane,
+                                              const uint32_t (&c)[4]) {
+  uint32_t n[4] = {0, 0, 0, 0};
+  asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_COMPARE TBQ_LEAVES TBQ_TIES "}" TBQ_OPERANDS);
+}
+
+// Upper levels 0 .. DEPTH-2 of four columns of a group of DEPTH levels (DEPTH >= 2).
+// In: A[i] = address of the root in the upper-level piece.  Out: the address of the
+// bottom-level node reached.  cu = 128 - (root address), cx = cu + (first bottom-level
+// node's address) - (root address) - 128 * (2^(DEPTH-1) - 1), per column.
 template <int DEPTH>
-__device__ __forceinline__ uint32_t quant_walk(uint32_t colbase, uint32_t keys_lane, bool *tie) {
-  uint32_t A = colbase;
-  bool t = false;
-  if (DEPTH > 0) {
-    uint32_t node = lds_u32(A);
-    const uint32_t cL = 128u - colbase;
+__device__ __forceinline__ void quant_upper4(uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane,
+                                             const uint32_t (&cu)[4], const uint32_t (&cx)[4]) {
+  uint32_t n[4];
 #pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      // one key load and one node load per level: the kernel is bound by the SM's load/store
-      // path, so fetching both children ahead of the comparison costs more than it hides
-      const uint32_t kx = lds_u16(keys_lane + (node >> 16) * 64u);
-      const uint32_t kt = node & 0xffffu;
-      t |= (kx == kt);
-      A = 2u * A + cL + (kx < kt ? 128u : 0u);
-      if (d + 1 < DEPTH) node = lds_u32(A);
-    }
-  }
-  *tie = t;
-  return A;
+  for (int i = 0; i < 4; ++i) n[i] = lds_u32(A[i]);
+  quant_steps4<DEPTH - 2>(A, n, ties, keys_lane, cu);
+  quant_cross4(A, n, ties, keys_lane, cx);
 }
-
-__device__ __forceinline__ uint32_t quant_walk_any(uint32_t depth, uint32_t colbase, uint32_t keys_lane, bool *tie) {
+__device__ __forceinline__ void quant_upper4_any(uint32_t depth, uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane,
+                                                 const uint32_t (&cu)[4], const uint32_t (&cx)[4]) {
   switch (depth) {
-  case 0: return quant_walk<0>(colbase, keys_lane, tie);
-  case 1: return quant_walk<1>(colbase, keys_lane, tie);
-  case 2: return quant_walk<2>(colbase, keys_lane, tie);
-  case 3: return quant_walk<3>(colbase, keys_lane, tie);
-  case 4: return quant_walk<4>(colbase, keys_lane, tie);
-  case 5: return quant_walk<5>(colbase, keys_lane, tie);
-  case 6: return quant_walk<6>(colbase, keys_lane, tie);
-  case 7: return quant_walk<7>(colbase, keys_lane, tie);
-  default: return quant_walk<8>(colbase, keys_lane, tie);
+  case 2: return quant_upper4<2>(A, ties, keys_lane, cu, cx);
+  case 3: return quant_upper4<3>(A, ties, keys_lane, cu, cx);
+  case 4: return quant_upper4<4>(A, ties, keys_lane, cu, cx);
+  case 5: return quant_upper4<5>(A, ties, keys_lane, cu, cx);
+  case 6: return quant_upper4<6>(A, ties, keys_lane, cu, cx);
+  case 7: return quant_upper4<7>(A, ties, keys_lane, cu, cx);
+  default: return quant_upper4<8>(A, ties, keys_lane, cu, cx);
   }
 }
 
-// Re-walk of one (row, tree) pair behind a key tie: the staged keys decide wherever they
-// can, and only the tied comparisons read the exact fp32 values from global memory.
-// Returns the slot reached (level-order numbering of the planes).
-__device__ __noinline__ uint32_t quant_walk_exact(uint32_t colbase, uint32_t keys_lane, const float *exact_plane,
-                                                  size_t plane_row, uint32_t depth, uint32_t col,
-                                                  const float *rowp) {
-  uint32_t s = 0;
-  for (uint32_t d = 0; d < depth; ++d) {
-    const uint32_t node = lds_u32(colbase + s * 128u);
-    const uint32_t f = node >> 16, kt = node & 0xffffu;
-    const uint32_t kx = lds_u16(keys_lane + f * 64u);
+// Re-walks behind a key tie: the staged keys decide wherever they can, and only the tied
+// comparisons read the exact fp32 values from global memory.
+// Upper levels 0 .. depth-2 of the column at address `up` of the upper-level piece; returns
+// the number of the bottom-level node reached (0 .. 2^(depth-1) - 1).
+__device__ __noinline__ uint32_t quant_upper_exact(uint32_t up, uint32_t keys_lane, const float *exact_plane,
+                                                   size_t plane_row, uint32_t depth, uint32_t col,
+                                                   const float *rowp) {
+  uint32_t s = 0; // level-order number of the node
+  for (uint32_t d = 0; d + 1 < depth; ++d) {
+    const uint32_t node = lds_u32(up + s * 128u);
+    const uint32_t code = node >> 16, kt = node & 0x7fffu;
+    const uint32_t kx = lds_u16(keys_lane + 2u * code);
     bool right = kx < kt;
-    if (kx == kt) right = !(__ldg(rowp + f) < __ldg(exact_plane + (plane_row + s) * 32u + col));
+    if (kx == kt) {
+      const uint32_t f = (code >> 6) * 2u + (code & 1u);
+      right = !(__ldg(rowp + f) < __ldg(exact_plane + (plane_row + s) * 32u + col));
+    }
     s = 2u * s + 1u + (right ? 1u : 0u);
   }
-  return s;
+  return s - ((1u << (depth - 1)) - 1u);
+}
+// The bottom level: node j of the column at address `bot` of the bottom-level piece;
+// returns the leaf number.
+__device__ __noinline__ uint32_t quant_bottom_exact(uint32_t bot, uint32_t j, uint32_t keys_lane,
+                                                    const float *exact_plane, size_t plane_row, uint32_t depth,
+                                                    uint32_t col, const float *rowp) {
+  const uint32_t node = lds_u32(bot + j * 128u);
+  const uint32_t code = node >> 16, kt = node & 0x7fffu;
+  const uint32_t kx = lds_u16(keys_lane + 2u * code);
+  bool right = kx < kt;
+  if (kx == kt) {
+    const uint32_t f = (code >> 6) * 2u + (code & 1u);
+    // the bottom level fills the second half of the planes (quant_plane_slot)
+    right = !(__ldg(rowp + f) < __ldg(exact_plane + (plane_row + (1u << (depth - 1)) + j) * 32u + col));
+  }
+  return 2u * j + (right ? 1u : 0u);
 }
 
 // Fills the key field of every split node from its exact threshold (run once at upload,
 // so that thresholds and row values are quantised by the very same device arithmetic).
+// wide = 1: the 15-bit keys and feature codes of the wide-row layout (quant_pack.h);
+// 0: the 16-bit keys and plain feature indices of the deep-tree layout (deep_pack.h).
 __global__ void tb_quant_fill_keys(uint32_t *node_plane, const float *exact_plane, const float *lo,
-                                   const float *scale, unsigned long long n, int num_features) {
+                                   const float *scale, unsigned long long n, int num_features, int wide) {
   const unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const uint32_t node = node_plane[i], f = node >> 16;
-  if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_key_dev(exact_plane[i], lo[f], scale[f]);
+  const uint32_t node = node_plane[i];
+  if (wide) {
+    const uint32_t code = node >> 16, f = (code >> 6) * 2u + (code & 1u);
+    if (f < (uint32_t)num_features) node_plane[i] = (code << 16) | quant_key15_dev(exact_plane[i], lo[f], scale[f]);
+  } else {
+    const uint32_t f = node >> 16;
+    if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_key_dev(exact_plane[i], lo[f], scale[f]);
+  }
 }
 
 constexpr int kQPiece = 16384;  // one ring slot: half a plane of a group of 8 levels
-constexpr int kQHalfWarps = 16; // warps per half-block
+constexpr int kQSetWarps = 8;   // walker warps per set
+constexpr int kQWalkers = 2 * kQSetWarps;
+constexpr int kQThreads = 32 * (kQWalkers + 2); // sixteen walker warps and two producer warps
 
-// Barrier over the 512 threads of one half-block that also ORs a predicate across them.
-__device__ __forceinline__ bool half_barrier_or(int id, bool pred) {
-  uint32_t r;
-  asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.or.pred p, %2, 512, q;\n"
-               " selp.u32 %0, 1, 0, p;\n}"
-               : "=r"(r)
-               : "r"((uint32_t)pred), "r"(id)
-               : "memory");
-  return r != 0;
+__device__ __forceinline__ void mbar_arrive(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
 }
 
-// UD: depth shared by every group of the forest (0 = mixed depths, decided per group at run
-// time; with a constant depth the walk is called directly and piece sizes fold).
+// Shared-memory bytes of the key tile: one 128-byte line per pair of features, the
+// sentinel feature (index num_features) included.
+__host__ __device__ constexpr int quant_key_tile_bytes(int num_features) { return (num_features + 2) / 2 * 128; }
+
+// UD: depth shared by every group of the forest (0 = mixed depths, read per group at run
+// time; with a constant depth the walk is called directly and plane offsets are computed).
 // LEAF_IDS: the launch records leaf ids instead of predictions.
+//
+// Shared memory: [0,128) sixteen mbarriers -- full[set][3], empty[set][3], table[set][2];
+// the ring of six 16 KB pieces (three per set); the leaf-number tables (two per set, 1 KB
+// each); the key tile.
 template <int UD, bool LEAF_IDS>
-__global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int half = warp / kQHalfWarps, hw = warp % kQHalfWarps;
+  const bool producer = warp >= kQWalkers;
+  const int set = producer ? warp - kQWalkers : warp / kQSetWarps, sw = warp % kQSetWarps;
   const int F = p.num_features;
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw) + half * 3; // [2 halves][3 slots]
-  // group table of this chunk: {plane offset in 32-element rows, depth}
-  uint2 *gtab = reinterpret_cast<uint2 *>(smem_raw + 128);
-  unsigned char *ring = smem_raw + 128 + p.meta_bytes + (size_t)half * 3 * kQPiece;
+  const uint32_t bars_s = smem_u32(smem_raw);
+  const uint32_t full_s = bars_s + (uint32_t)set * 24u, empty_s = bars_s + 48u + (uint32_t)set * 24u;
+  const uint32_t table_s = bars_s + 96u + (uint32_t)set * 16u;
+  unsigned char *ring = smem_raw + 128 + (size_t)set * 3 * kQPiece;
   const uint32_t ring_s = smem_u32(ring);
-  // leaf numbers of a group, exchanged between the warps of a half (see below)
-  const uint32_t ltab_s = smem_u32(smem_raw + 128 + p.meta_bytes) + 6 * kQPiece + (uint32_t)half * 2048u;
-  const uint32_t keys_s = smem_u32(smem_raw + 128 + p.meta_bytes) + 6 * kQPiece + kQLeafTableBytes; // u16 [F+1][32]
-  const uint32_t keys_lane = keys_s + lane * 2;
+  // leaf numbers of a group, exchanged between the warps of a set (see below)
+  const uint32_t ltab_s = smem_u32(smem_raw + 128) + 6 * kQPiece + (uint32_t)set * 2048u;
+  // key tile: line m = features 2m | 2m+1 << 16 for the 32 rows
+  const uint32_t keys_s = smem_u32(smem_raw + 128) + 6 * kQPiece + kQLeafTableBytes;
+  const uint32_t keys_lane = keys_s + lane * 4;
 
   const long long row = (long long)blockIdx.x * 32 + lane;
   const bool live = row < p.n_rows;
@@ -215,45 +311,74 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
   const int g0 = blockIdx.y * p.groups_per_chunk;
   const int g1 = min(p.num_groups, g0 + p.groups_per_chunk);
   const int NG = g1 - g0;
-  const int NGh = (NG - half + 1) / 2; // groups half, half + 2, ... of the chunk
-  const int P = 2 * NGh;               // pieces of this half: upper levels and bottom level of the node planes
+  const int NGs = (NG - set + 1) / 2; // groups set, set + 2, ... of the chunk
+  const int P = 2 * NGs;              // pieces of this set: upper levels and bottom level of the node planes
 
   if (tid == 0) {
-    for (int i = 0; i < 6; ++i) mbar_init(reinterpret_cast<uint64_t *>(smem_raw) + i, 1);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
+    for (int i = 0; i < 6; ++i) mbar_init(bars + i, 1);                  // full: the copy's bytes
+    for (int i = 6; i < 12; ++i) mbar_init(bars + i, kQSetWarps);        // empty: one arrival per walker warp
+    for (int i = 12; i < 16; ++i) mbar_init(bars + i, kQSetWarps);       // leaf-number table complete
     fence_barrier_init();
-  }
-  for (int i = tid; i < NG; i += blockDim.x) {
-    const DevQuantGroup gm = p.groups[g0 + i];
-    gtab[i] = make_uint2((uint32_t)(gm.elem_off >> 5), gm.depth);
   }
   __syncthreads();
 
-  auto issue = [&](int piece, int slot) { // slot = piece % 3
-    const uint2 gm = gtab[2 * (piece >> 1) + half];
-    const uint32_t hs = UD ? (1u << (UD ? UD - 1 : 0)) : 1u << (gm.y - 1); // slots per piece
-    const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
-    uint64_t *bar = &full[slot];
-    mbar_expect_tx(bar, hs * 128u);
-    bulk_g2s(ring + (size_t)slot * kQPiece, p.node_plane + off, hs * 128u, bar);
+  // plane offset (in rows of 32 elements) and depth of group gi of the chunk
+  auto group_of = [&](int gi) -> uint2 {
+    if constexpr (UD > 0) return make_uint2((uint32_t)(g0 + gi) << UD, (uint32_t)UD);
+    const DevQuantGroup gm = p.groups[g0 + gi];
+    return make_uint2((uint32_t)(gm.elem_off >> 5), gm.depth);
   };
-  if (lane == 0 && hw < 3 && hw < P) issue(hw, hw);
 
-  // ---- stage the row tile as keys: keys[f][row]
-  {
+  bool ok = true;
+  if (producer) {
+    // ---- the set's producer: streams the node planes through the set's three slots.  Piece
+    // q (upper levels of group q/2 for even q, its bottom level for odd q) goes to slot q mod 3
+    // as soon as every walker warp has released the piece that was there.
+    int slot = 0;
+    uint32_t round_parity = 1; // parity of the previous phase of empty[slot]: passes at once in round 0
+    auto issue = [&](int piece) {
+      const uint2 gm = group_of(2 * (piece >> 1) + set);
+      const uint32_t hs = 1u << (gm.y - 1); // slots per piece
+      const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
+      uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw) + set * 3 + slot;
+      mbar_expect_tx(bar, hs * 128u);
+      bulk_g2s(ring + (size_t)slot * kQPiece, p.node_plane + off, hs * 128u, bar);
+    };
+    for (int piece = 0; piece < P && ok; ++piece) {
+      if (piece >= 3) ok = mbar_wait_all_lanes(empty_s + 8u * (uint32_t)slot, round_parity);
+      if (ok && lane == 0) issue(piece);
+      if (++slot == 3) {
+        slot = 0;
+        if (piece >= 3) round_parity ^= 1u;
+      }
+      if (piece == 2) { // the walkers stage the row tile meanwhile; join them at its barrier
+        round_parity = 0;
+        __syncthreads();
+      }
+    }
+    if (P < 3) __syncthreads();
+  } else {
+    // ---- stage the row tile as keys
     // A warp takes a block of 32 consecutive features: every load instruction reads 128
     // contiguous bytes of ONE row (lane = feature), so DRAM sees whole lines and adjacent
-    // warps continue the same rows.  A lane thus collects its feature for all 32 rows,
-    // packs the 32 keys into 64 bytes and writes them with four 16-byte stores.  Loads
-    // go to L2 only (the unified L1 is almost entirely shared memory here); sixteen are
-    // in flight per thread.
+    // warps continue the same rows.  A lane thus collects its feature for all 32 rows and
+    // packs the keys two to a register; neighbouring lanes (features 2m, 2m+1) then swap
+    // halves through a shuffle, so that the even lane holds the finished words of rows
+    // 0..15 and the odd lane those of rows 16..31, 64 contiguous bytes each, written with
+    // four 16-byte stores.  Loads go to L2 only (the unified L1 is almost entirely shared
+    // memory here); sixteen are in flight per thread.
     const long long row0 = (long long)blockIdx.x * 32;
     const int live_rows = (int)min((long long)32, p.n_rows - row0);
     const float *tile = p.rows + row0 * p.ld;
-    for (int f0 = warp * 32; f0 < F; f0 += 32 * 32) {
+    const bool odd = lane & 1;
+    // byte selectors: the even feature's packed keys are operand a on even lanes, b on odd
+    const uint32_t sel_lo = odd ? 0x1054u : 0x5410u, sel_hi = odd ? 0x3276u : 0x7632u;
+    for (int f0 = warp * 32; f0 <= F; f0 += kQWalkers * 32) {
       const int f = f0 + lane;
       const bool fok = f < F;
       const float lo = fok ? __ldg(p.lo + f) : 0.f, sc = fok ? __ldg(p.scale + f) : 0.f;
-      uint32_t packed[16];
+      uint32_t packed[16]; // keys of rows 2i | 2i+1 << 16 of this lane's feature
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         float x[16];
@@ -264,154 +389,190 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_quant_kernel(const QuantParam
         }
 #pragma unroll
         for (int r = 0; r < 16; r += 2)
-          packed[part * 8 + r / 2] = quant_key_dev(x[r], lo, sc) | (quant_key_dev(x[r + 1], lo, sc) << 16);
+          packed[part * 8 + r / 2] = quant_key15_dev(x[r], lo, sc) | (quant_key15_dev(x[r + 1], lo, sc) << 16);
       }
-      if (fok) {
-        const uint32_t dst = keys_s + (uint32_t)f * 64u;
+      if (f == F) { // the sentinel feature: the largest key for every row
+#pragma unroll
+        for (int i = 0; i < 16; ++i) packed[i] = 0x7bff7bffu;
+      }
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t own = odd ? packed[8 + i] : packed[i];
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? packed[i] : packed[8 + i], 1);
+        w[2 * i] = __byte_perm(own, got, sel_lo);
+        w[2 * i + 1] = __byte_perm(own, got, sel_hi);
+      }
+      if (f <= F + (odd ? 1 : 0)) { // lanes of a pair that holds at least one real feature
+        const uint32_t dst = keys_s + (uint32_t)(f >> 1) * 128u + (odd ? 64u : 0u);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 16u * c), "r"(packed[4 * c]),
-                       "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3]));
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 16u * c), "r"(w[4 * c]),
+                       "r"(w[4 * c + 1]), "r"(w[4 * c + 2]), "r"(w[4 * c + 3]));
       }
     }
+    __syncthreads();
   }
-  if (warp == 0) sts_u16(keys_lane + (uint32_t)F * 64u, 65535u); // sentinel feature
-  __syncthreads();
 
-  // the two columns this lane walks in every group of its half
-  const uint32_t col[2] = {(uint32_t)(lane + hw) & 31u, (uint32_t)(lane + hw + 16) & 31u};
   float acc = 0.f;
-  float pend[2] = {0.f, 0.f}; // leaf values of the previous group, on their way from L2
-  bool ok = true, failed = false;
-  unsigned ties = 0;
-
-  // One barrier per group over the half-block (it also carries any wait failure to its 512
-  // threads, so that their exit is uniform) frees the group's two slots; the refills are
-  // issued by two rotating warps.
-  // Two pieces per group through three slots: the slots of a group's pieces rotate with period
-  // three -- (0,1), (2,0), (1,2) -- and so do the phases of their barriers -- (0,0), (0,1),
-  // (1,1) -- whatever the group number; both follow from two counters, without divisions.
-  int su = 0, sb = 1; // ring slots of the current group's upper-level and bottom-level pieces
-  auto release = [&](int first) {
-    failed = half_barrier_or(1 + half, !ok);
-    if (!failed && lane == 0) {
-      // pieces first+3 and first+4 land in the two slots just freed, in the same order
-      if (first + 3 < P && ((first + 3) % kQHalfWarps) == hw) issue(first + 3, su);
-      if (first + 4 < P && ((first + 4) % kQHalfWarps) == hw) issue(first + 4, sb);
-    }
-    su = su == 0 ? 2 : su - 1;
-    sb = sb == 0 ? 2 : sb - 1;
-  };
-  const uint32_t full_s = smem_u32(full);
-  auto upper_ready = [&]() { return mbar_wait_all_lanes(full_s + 8u * (uint32_t)su, su == 1 ? 1u : 0u); };
-  auto bottom_ready = [&]() { return mbar_wait_all_lanes(full_s + 8u * (uint32_t)sb, sb != 1 ? 1u : 0u); };
-
-  // Leaf values come straight from L2, but not in the walk's lane assignment: there the 32
-  // lanes of a warp sit in 32 different trees, i.e. 32 different lines of the leaf plane
-  // whatever its layout.  The walkers therefore drop their leaf NUMBERS (one byte each) into
-  // a [column][row] table in shared memory; after the group's barrier warp w of the half
-  // picks up columns 2w and 2w+1 for all 32 rows and loads those leaves from the
-  // column-major leaf plane, where one tree's 256 leaves span 1 KB: at most 8 lines per
-  // warp load instead of 32.  Lane = row on both sides, so the sum stays in the lane's
-  // register; the loads are consumed one group later.
-  // (element offsets fit 32 bits: the host refuses planes of 2^32 elements or more)
-  const uint32_t my_cols_s = ltab_s + (2u * (uint32_t)hw) * 32u + (uint32_t)lane;
-  auto fetch_leaves = [&](int gi_prev, uint2 gprev, uint32_t buf) {
-    const uint32_t slots = UD ? (1u << UD) : 2u << (gprev.y - 1);
+  unsigned tie_count = 0;
+  if (!producer) {
+    // the four columns this lane walks in every group of its set: warp w takes the columns
+    // (lane + w + 8c) mod 32, so a load of the warp touches 32 distinct columns (banks) and
+    // the eight warps of the set cover every (row, tree) pair of the group exactly once
+    uint32_t col[4], colb[4];
 #pragma unroll
-    for (int w = 0; w < 2; ++w) {
-      const uint32_t c = 2u * (uint32_t)hw + (uint32_t)w;
-      uint32_t leaf;
-      asm volatile("ld.shared.u8 %0, [%1];" : "=r"(leaf) : "r"(my_cols_s + buf * 1024u + (uint32_t)w * 32u));
-      const uint32_t e = gprev.x * 32u + c * slots + leaf;
-      if (LEAF_IDS) {
-        if (live) {
-          const int t = p.tree_index[(g0 + gi_prev) * 32 + (int)c];
-          if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
+    for (int c = 0; c < 4; ++c) {
+      col[c] = (uint32_t)(lane + sw + 8 * c) & 31u;
+      colb[c] = ring_s + col[c] * 4u; // the column's address in slot 0
+    }
+    float pend[4] = {0.f, 0.f, 0.f, 0.f}; // leaf values of the previous group, on their way from L2
+
+    // Leaf values come straight from L2, but not in the walk's lane assignment: there the 32
+    // lanes of a warp sit in 32 different trees, i.e. 32 different lines of the leaf plane
+    // whatever its layout.  The walkers therefore drop their leaf NUMBERS (one byte each) into
+    // a [column][row] table in shared memory and arrive on the table's barrier; one group
+    // later warp w of the set picks up columns 4w .. 4w+3 for all 32 rows and loads those
+    // leaves from the column-major leaf plane, where one tree's 256 leaves span 1 KB: at most
+    // 8 lines per warp load instead of 32.  Lane = row on both sides, so the sum stays in the
+    // lane's register; the loads are consumed one group later still.  Two tables alternate:
+    // table k mod 2 is rewritten in group k+2 after the wait for that group's bottom-level
+    // piece, whose slot every warp of the set has released after reading table k.
+    // (element offsets fit 32 bits: the host refuses planes of 2^32 elements or more)
+    const uint32_t my_cols_s = ltab_s + (4u * (uint32_t)sw) * 32u + (uint32_t)lane;
+    auto fetch_leaves = [&](int gi_prev, uint2 gprev, uint32_t buf) {
+      const uint32_t slots = 2u << (gprev.y - 1);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t c = 4u * (uint32_t)sw + (uint32_t)w;
+        uint32_t leaf;
+        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(leaf) : "r"(my_cols_s + buf * 1024u + (uint32_t)w * 32u));
+        const uint32_t e = gprev.x * 32u + c * slots + leaf;
+        if (LEAF_IDS) {
+          if (live) {
+            const int t = p.tree_index[(g0 + gi_prev) * 32 + (int)c];
+            if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
+          }
+        } else {
+          pend[w] = __ldg(p.leaf_plane + e);
         }
-      } else {
-        pend[w] = __ldg(p.leaf_plane + e);
       }
-    }
-  };
-  uint2 gprev = make_uint2(0, 0);
-  int gi_prev = -1;
-  // where this lane drops the leaf numbers of its two walks (buffer 0)
-  const uint32_t drop_s[2] = {ltab_s + col[0] * 32u + (uint32_t)lane, ltab_s + col[1] * 32u + (uint32_t)lane};
-
-  for (int k = 0; k < NGh; ++k) {
-    const int gi = 2 * k + half;
-    const uint2 gm = gtab[gi];
-    const uint32_t depth = UD ? (uint32_t)UD : gm.y, hs = 1u << (depth - 1);
-    const int q = 2 * k;
-    uint32_t idx[2] = {0, 0};
-
-    // leaves of the previous group (its table is complete: the barrier has been passed)
-    if (gi_prev >= 0) fetch_leaves(gi_prev, gprev, (uint32_t)(k - 1) & 1u);
-
-    // upper levels 0 .. depth-2
-    ok = upper_ready();
-    if (ok) {
+    };
+    uint2 gprev = make_uint2(0, 0);
+    int gi_prev = -1;
+    // where this lane drops the leaf numbers of its four walks (table 0)
+    uint32_t drop_s[4];
 #pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const uint32_t colbase = ring_s + (uint32_t)su * kQPiece + col[w] * 4u;
-        bool tie;
-        uint32_t s;
-        if constexpr (UD > 0)
-          s = (quant_walk<UD - 1>(colbase, keys_lane, &tie) - colbase) >> 7;
+    for (int c = 0; c < 4; ++c) drop_s[c] = ltab_s + col[c] * 32u + (uint32_t)lane;
+
+    // pieces are consumed in order: slot and phase of the next piece follow from counters
+    int slot = 0;
+    uint32_t parity = 0;
+    const bool elected = lane == 0;
+
+    for (int k = 0; k < NGs && ok; ++k) {
+      const int gi = 2 * k + set;
+      const uint2 gm = group_of(gi);
+      const uint32_t depth = UD ? (uint32_t)UD : gm.y, hs = 1u << (depth - 1);
+
+      // leaves of the previous group, once its table is complete
+      if (gi_prev >= 0) {
+        ok = mbar_wait_all_lanes(table_s + 8u * ((uint32_t)(k - 1) & 1u), ((uint32_t)(k - 1) >> 1) & 1u);
+        if (!ok) break;
+        acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
+        fetch_leaves(gi_prev, gprev, (uint32_t)(k - 1) & 1u);
+      }
+
+      // the two pieces of this group
+      const uint32_t su = (uint32_t)slot, pu = parity;
+      if (++slot == 3) { slot = 0; parity ^= 1u; }
+      const uint32_t sb = (uint32_t)slot, pb = parity;
+      if (++slot == 3) { slot = 0; parity ^= 1u; }
+      uint32_t A[4], bot[4], ties = 0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        bot[c] = colb[c] + sb * kQPiece;
+        A[c] = bot[c];
+      }
+
+      // upper levels 0 .. depth-2: ends at the addresses of the bottom-level nodes
+      ok = mbar_wait_all_lanes(full_s + 8u * su, pu);
+      if (!ok) break;
+      if (depth >= 2) {
+        uint32_t cu[4], cx[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          A[c] = colb[c] + su * kQPiece;
+          cu[c] = 128u - A[c];
+          cx[c] = cu[c] + bot[c] - A[c] - 128u * (hs - 1u);
+        }
+        if constexpr (UD >= 2)
+          quant_upper4<UD>(A, ties, keys_lane, cu, cx);
         else
-          s = (quant_walk_any(depth - 1, colbase, keys_lane, &tie) - colbase) >> 7;
-        if (tie) {
-          s = quant_walk_exact(colbase, keys_lane, p.exact_plane, gm.x, depth - 1, col[w], rowp);
-          ++ties;
-        }
-        idx[w] = s - (hs - 1u); // position inside the bottom decision level
-      }
-    }
-
-    // bottom decision level; the leaf number goes into the table
-    if (ok) ok = bottom_ready();
-    if (ok) {
+          quant_upper4_any(depth, A, ties, keys_lane, cu, cx);
+        if (ties) { // rare: the tied column is walked again on exact values
 #pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const uint32_t node = lds_u32(ring_s + (uint32_t)sb * kQPiece + idx[w] * 128u + col[w] * 4u);
-        const uint32_t f = node >> 16, kt = node & 0xffffu;
-        const uint32_t kx = lds_u16(keys_lane + f * 64u);
-        bool right = kx < kt;
-        if (kx == kt) {
-          right = !(__ldg(rowp + f) < __ldg(p.exact_plane + ((size_t)gm.x + hs + idx[w]) * 32u + col[w]));
-          ++ties;
+          for (int c = 0; c < 4; ++c)
+            if (ties & (1u << c)) {
+              A[c] = bot[c] + 128u * quant_upper_exact(colb[c] + su * kQPiece, keys_lane, p.exact_plane, gm.x, depth,
+                                                       col[c], rowp);
+              ++tie_count;
+            }
+          ties = 0;
         }
-        const uint32_t leaf = 2u * idx[w] + (right ? 1u : 0u);
-        asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop_s[w] + ((uint32_t)k & 1u) * 1024u), "r"(leaf));
       }
-      acc += pend[0] + pend[1]; // previous group's leaves have had a whole walk to arrive
-      pend[0] = pend[1] = 0.f;
+      __syncwarp();
+      if (elected) mbar_arrive(empty_s + 8u * su);
+
+      // bottom decision level; the leaf numbers go into the table
+      ok = mbar_wait_all_lanes(full_s + 8u * sb, pb);
+      if (!ok) break;
+      quant_bottom4(A, ties, keys_lane, bot);
+      if (ties) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (ties & (1u << c)) {
+            A[c] = quant_bottom_exact(bot[c], A[c] >> 1, keys_lane, p.exact_plane, gm.x, depth, col[c], rowp);
+            ++tie_count;
+          }
+      }
+      const uint32_t buf = ((uint32_t)k & 1u) * 1024u;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop_s[c] + buf), "r"(A[c]) : "memory");
+      __syncwarp();
+      if (elected) {
+        mbar_arrive(empty_s + 8u * sb);
+        mbar_arrive(table_s + 8u * ((uint32_t)k & 1u));
+      }
+      gprev = gm;
+      gi_prev = gi;
     }
-    release(q);
-    if (failed) break;
-    gprev = gm;
-    gi_prev = gi;
+    if (ok && gi_prev >= 0) {
+      ok = mbar_wait_all_lanes(table_s + 8u * ((uint32_t)(NGs - 1) & 1u), ((uint32_t)(NGs - 1) >> 1) & 1u);
+      if (ok) {
+        acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
+        pend[0] = pend[1] = pend[2] = pend[3] = 0.f;
+        fetch_leaves(gi_prev, gprev, (uint32_t)(NGs - 1) & 1u);
+        acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
+      }
+    }
   }
-  if (!failed && gi_prev >= 0) {
-    fetch_leaves(gi_prev, gprev, (uint32_t)(NGh - 1) & 1u);
-    acc += pend[0] + pend[1];
-  }
-  if (__syncthreads_or(failed)) {
+  // every wait above is bounded: a wait that gave up ends the launch with a status word
+  if (__syncthreads_or(!ok)) {
     if (tid == 0) atomicExch(p.status, 4);
     return;
   }
-  if (p.tie_count != nullptr && ties) atomicAdd(p.tie_count, (unsigned long long)ties);
-  if (LEAF_IDS) return;
+  if (p.tie_count != nullptr && tie_count) atomicAdd(p.tie_count, (unsigned long long)tie_count);
+  if (LEAF_IDS || producer) return;
 
-  // ---- combine the 32 warps (one partial per row each)
-  float *red = reinterpret_cast<float *>(smem_raw + 128 + p.meta_bytes);
+  // ---- combine the walker warps (one partial per row each)
+  float *red = reinterpret_cast<float *>(smem_raw + 128);
   red[warp * 32 + lane] = acc;
-  __syncthreads();
+  asm volatile("bar.sync 1, %0;" ::"r"(32 * kQWalkers) : "memory");
   if (warp != 0 || !live) return;
   float s = 0.f;
-#pragma unroll 8
-  for (int w = 0; w < 32; ++w) s += red[w * 32 + lane];
+#pragma unroll
+  for (int w = 0; w < kQWalkers; ++w) s += red[w * 32 + lane];
   if (p.write_partial)
     p.partial[(long long)blockIdx.y * p.n_rows + row] = s;
   else
