@@ -33,8 +33,31 @@ HBM_FALLBACK_GBS = 6650.0
 
 # DRAM bytes per row (dram__bytes_read.sum + dram__bytes_write.sum) of the walk kernel, from
 # one ncu capture per workload on a reduced batch (see profiles/); traffic grows in
-# proportion to the rows, so a launch's traffic is this figure times its rows.
-NCU_DRAM_BYTES_PER_ROW = {"c3": 8189.0, "c2": 118.2, "c4": 76.3}
+# proportion to the rows, so a launch's traffic is this figure times its rows.  Each figure
+# belongs to the kernel sources it was captured on: it is reported only while their hash
+# (kernel_source_hash) still matches.
+NCU_DRAM_BYTES_PER_ROW = {"c3": (8189.0, ""), "c2": (118.2, ""), "c4": (76.3, "")}
+KERNEL_SOURCES = ("walk_kernels.cuh", "walk_quant.cuh", "walk_deep.cuh", "tbk_api.cu")
+
+
+def kernel_source_hash():
+    import hashlib
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, "treebeard_b200", "csrc", name), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic(workload, n_rows, custom):
+    """(bytes per launch or None, where the figure comes from / why there is none)."""
+    if custom or workload not in NCU_DRAM_BYTES_PER_ROW:
+        return None, "no ncu capture for this workload"
+    per_row, captured_on = NCU_DRAM_BYTES_PER_ROW[workload]
+    now = kernel_source_hash()
+    if captured_on != now:
+        return None, f"kernel sources changed since the ncu capture (captured on {captured_on or 'an earlier build'}, now {now})"
+    return per_row * n_rows, "ncu dram bytes per row on a reduced batch x rows (profiles/)"
 
 
 def bytes_per_row(cfg):
@@ -45,6 +68,15 @@ def bytes_per_row(cfg):
 def visits_per_row(cfg):
     """Node visits of the fixed-depth walk: trees x decision levels."""
     return cfg["T"] * cfg["D"]
+
+
+def useful_visits_per_row(forest, leaf_ids):
+    """Node visits a walk that stops at its leaf needs: the depth of the selected leaf, summed
+    over trees, averaged over the sampled rows (leaf_ids: [rows, trees] node ids from the
+    GPU's leaf-id pass)."""
+    depth = synth.node_depths(forest)
+    glob = leaf_ids.astype(np.int64) + forest.tree_off[:-1][None, :]
+    return float(depth[glob].sum(axis=1).mean())
 
 
 def measured_peak():
@@ -187,6 +219,75 @@ def workload_config(args, cfg, n_rows, world):
 # the B200 arm
 
 
+def tree_sharded_c5(args, torch, dist, kernels, rank, world, dev):
+    """The large forest (T=16 000, D=12, F=128) over all 4 194 304 rows with its trees
+    partitioned evenly across the ranks: every rank walks its trees over ALL rows into per-row
+    partial sums, one NCCL reduce (fp32, 16 MiB per rank, onto rank 0) adds them, rank 0 adds
+    the initial value.  Beside it the row-sharded run of the same forest (every rank the whole
+    forest and 1/world of the rows, no collective).  Device times, max over ranks."""
+    steps, warmup = 5, 3
+    forest, marg, n_rows = synth.make_config("c5", trees=args.c5_trees, rows=args.c5_rows)
+    X = torch.from_numpy(synth.config_rows("c5", marg, n_rows)).to(dev)
+    T = forest.num_trees
+    mine = forest.tree_slice(rank * T // world, (rank + 1) * T // world)
+    df = kernels.DeviceForest(mine, device=dev.index, batch_hint=n_rows, representation="auto")
+    partial = torch.empty((n_rows, 1), device=dev)
+    out = torch.empty(n_rows, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, marks):
+        for _ in range(warmup):
+            fn(None)
+        sync()
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(marks)] for _ in range(steps)]
+        for i in range(steps):
+            fn(ev[i])
+        sync()
+        spans = np.array([[ev[i][j].elapsed_time(ev[i][j + 1]) for j in range(marks - 1)] for i in range(steps)])
+        t = torch.tensor(spans.mean(axis=0).tolist() + [spans.sum(axis=1).mean()], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def tree_step(ev):
+        if ev: ev[0].record(stream)
+        df.predict_partial(X, out=partial)
+        if ev: ev[1].record(stream)
+        if world > 1:
+            dist.reduce(partial, dst=0, op=dist.ReduceOp.SUM)
+        if ev: ev[2].record(stream)
+        if rank == 0:
+            df.finalize(partial, out=out)
+        if ev: ev[3].record(stream)
+
+    walk_ms, reduce_ms, finalize_ms, total_ms = timed(tree_step, 4)
+    df.check_status()
+    res = {"workload": f"c5: {synth.CONFIGS['c5']['desc']}, {n_rows} rows, {T} trees over {world} GPU(s)",
+           "ms_per_step": total_ms, "rows_per_s": n_rows / (total_ms * 1e-3), "walk_ms": walk_ms,
+           "reduce_ms": reduce_ms, "finalize_ms": finalize_ms, "steps": steps, "warmup": warmup,
+           "collective": (f"ncclReduce fp32 {n_rows * 4 / 2**20:.0f} MiB -> rank 0" if world > 1 else "none (one GPU)"),
+           "row_sharded_ms": None}
+    if world > 1:
+        del df
+        full = kernels.DeviceForest(forest, device=dev.index, batch_hint=n_rows // world, representation="auto")
+        lo, hi = rank * n_rows // world, (rank + 1) * n_rows // world
+        Xs, outs = X[lo:hi], out[lo:hi]
+
+        def row_step(ev):
+            if ev: ev[0].record(stream)
+            full.predict(Xs, out=outs)
+            if ev: ev[1].record(stream)
+
+        res["row_sharded_ms"] = timed(row_step, 2)[-1]
+        full.check_status()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -207,6 +308,9 @@ def main():
     ap.add_argument("--port", action="store_true", help="reference arm: force the C restatement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-c5", action="store_true", help="skip the tree-sharded large-forest section")
+    ap.add_argument("--c5-trees", type=int, default=None)
+    ap.add_argument("--c5-rows", type=int, default=None)
     args = ap.parse_args()
     cfg = dict(synth.CONFIGS[args.workload])
     if args.trees:
@@ -299,19 +403,22 @@ def main():
     rows_per_step = n_rows if tree_sharded else n_rows * world
     value = rows_per_step / (ms_per_step * 1e-3)
 
-    # roofline of the walk kernel: algorithmic bytes per launch over its device time
+    # roofline of the walk kernel on ONE GPU (this rank's launch): algorithmic bytes per launch
+    # over its device time
     peak, peak_src = measured_peak()
     kernel_ms = statistics.mean(per_step_ms)
     bpr = bytes_per_row(cfg)
     achieved = n_rows * bpr / (kernel_ms * 1e-3) / 1e9
-    per_row = NCU_DRAM_BYTES_PER_ROW.get(args.workload) if not args.trees else None
+    traffic, traffic_src = ncu_traffic(args.workload, n_rows, bool(args.trees) or tree_sharded)
+    sample = min(n_rows, 2048)
+    useful = useful_visits_per_row(my_forest, df.predict_leaf_ids(X[:sample]).cpu().numpy())
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak,
-                "traffic": per_row * n_rows if per_row else None,
-                "traffic_source": "ncu dram bytes per row on a reduced batch x rows" if per_row else None,
-                "peak_source": f"hbm_gbs of {peak_src}",
+                "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src,
+                "peak_source": f"hbm_gbs of {peak_src}", "per": "GPU",
                 "algorithmic_bytes_per_row": bpr, "kernel_ms": kernel_ms,
-                "node_visits_per_s": n_rows * visits_per_row(cfg) / (kernel_ms * 1e-3)}
+                "node_visits_per_s": n_rows * my_forest.num_trees * cfg["D"] / (kernel_ms * 1e-3),
+                "useful_node_visits_per_s": n_rows * useful / (kernel_ms * 1e-3),
+                "useful_visits_per_row": useful}
 
     # end to end through the host-buffer entry point: pinned host rows in, host results out
     e2e = None
@@ -355,14 +462,21 @@ def main():
                          f"reference's parallel CPU schedule ({threads} OpenMP threads)",
                "max_abs_diff_vs_gpu": float(np.abs(ref_out - gpu_out).max())}
 
+    info = df.info()
+    c5 = None
+    if not args.no_c5 and args.workload == "c3" and not args.trees and not args.rows and not tree_sharded:
+        del df, X, out
+        torch.cuda.empty_cache()
+        c5 = tree_sharded_c5(args, torch, dist, kernels, rank, world, dev)
+
     if rank == 0:
-        info = df.info()
         line = {"metric": "rows_per_second", "value": value, "unit": "rows/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
                 "higher_is_better": True, "scaling": "strong" if tree_sharded else "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": workload_config(args, cfg, n_rows, world),
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "tree_sharded": c5,
+                "gpu_launches": launches,
                 "clocks": clocks, "wall_ms_per_step": t_wall * 1e3 / args.steps,
                 "schedule": {"rows_per_block": info.schedule.rows_per_block,
                              "rows_per_thread": info.schedule.rows_per_thread,

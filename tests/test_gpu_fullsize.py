@@ -17,8 +17,9 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 # name, rows on the device, rows checked against the oracle, rows for the leaf-id matrix
-FULL = [("c1", 1024, 1024, 1024), ("c2", 1048576, 65536, 2048), ("c3", 262144, 4096, 512),
-        ("c4", 1048576, 16384, 1024)]
+# (the three batch sizes of the binary classifier select three different launch shapes)
+FULL = [("c1", 1024, 1024, 1024), ("c2", 4096, 4096, 1024), ("c2", 65536, 65536, 2048),
+        ("c2", 1048576, 65536, 2048), ("c3", 262144, 65536, 4096), ("c4", 1048576, 16384, 1024)]
 
 
 @pytest.mark.parametrize("name,rows,check,leaf_rows", FULL)
@@ -85,11 +86,12 @@ def test_full_size_large_forest_c5():
     assert df.info().schedule.feature_bits == 16
     got = df.predict(dX).cpu().numpy()
     df.check_status()
-    pick = np.sort(np.random.Generator(np.random.PCG64(11)).choice(rows, size=1024, replace=False))
-    want, want_ids = oracle.predict(forest, X[pick], leaf_ids=True)
+    pick = np.sort(np.random.Generator(np.random.PCG64(11)).choice(rows, size=8192, replace=False))
+    want = oracle.predict(forest, X[pick])
     assert_predictions_close(got[pick], want)
-    ids = df.predict_leaf_ids(torch.from_numpy(X[pick[:128]]).cuda()).cpu().numpy()
-    assert np.array_equal(ids, want_ids[:128])
+    _, want_ids = oracle.predict(forest, X[pick[:1024]], leaf_ids=True)
+    ids = df.predict_leaf_ids(torch.from_numpy(X[pick[:1024]]).cuda()).cpu().numpy()
+    assert np.array_equal(ids, want_ids)
     k = rows // 3 + 1
     parts = torch.cat([df.predict(dX[:k]), df.predict(dX[k:])]).cpu().numpy()
     assert_predictions_close(parts, got)

@@ -160,21 +160,27 @@ int ensure_orig(tbk_forest *f) {
 enum Mode { kPredict, kPartial, kLeafIds };
 
 int quant_smem_bytes(int num_features) {
-  return 128 + tb::kQRingBytes + tb::kQLeafTableBytes + tb::quant_key_tile_bytes(num_features);
+  return tb::kQBarBytes + tb::kQRingBytes + tb::kQLeafTableBytes + tb::quant_key_tile_bytes(num_features);
 }
 
-// One prediction with the 16-bit-key kernel (one block per 32 rows: 16 walker warps, 2 producers).
+// One prediction with the 16-bit-key kernel (persistent blocks of 16 warps over tiles of 32 rows).
 int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
               float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot) {
   const auto &q = f->qf;
   const int64_t G = (int64_t)q.groups.size();
-  const int64_t grid_x = (n_rows + 31) / 32;
+  const int64_t tiles = (n_rows + 31) / 32;
   int64_t chunks = 1;
   if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
-  else if (grid_x < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + grid_x - 1) / grid_x;
+  else if (tiles < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + tiles - 1) / tiles;
   chunks = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(chunks, G), 65535));
   const int gpc = (int)((G + chunks - 1) / chunks);
   chunks = (G + gpc - 1) / gpc;
+  const bool vec4 = q.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0;
+  // One block per SM (shared memory allows no more).  With more tiles than blocks a block is
+  // persistent and stages its next tile in tensor memory while it walks the current one; that
+  // path reads rows with 16-byte loads.
+  const int64_t blocks_x = std::max<int64_t>(1, (int64_t)f->num_sms / chunks);
+  const int64_t grid_x = (vec4 && tiles > blocks_x) ? blocks_x : tiles;
   tb::LaunchPlan plan;
   plan.row_warps = 1;
   plan.tree_threads = tb::kQWalkers;
@@ -227,7 +233,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   p.num_features = q.num_features;
   p.transform = q.transform;
   p.initial_value = (float)q.initial_value;
-  p.vec4_ok = (q.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
+  p.vec4_ok = vec4 ? 1 : 0;
   p.status = f->d_status;
   p.tie_count = f->d_ties;
   p.meta_bytes = 0;

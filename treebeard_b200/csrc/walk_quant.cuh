@@ -270,10 +270,29 @@ __global__ void tb_quant_fill_keys(uint32_t *node_plane, const float *exact_plan
 constexpr int kQPiece = 16384;  // one ring slot: half a plane of a group of 8 levels
 constexpr int kQSetWarps = 8;   // walker warps per set
 constexpr int kQWalkers = 2 * kQSetWarps;
-constexpr int kQThreads = 32 * (kQWalkers + 2); // sixteen walker warps and two producer warps
+constexpr int kQStagers = 4;             // warps 16..19: one per lane quarter of tensor memory
+constexpr int kQThreads = 32 * (kQWalkers + kQStagers);
+constexpr int kQBarBytes = 256;          // mbarriers and a few control words
+constexpr uint32_t kQTmemCols = 256;     // 128 lanes x 256 columns x 4 bytes = the 128 KB of a key tile
+constexpr int kQStagerPairs = 256;       // feature pairs per stager = columns of its lane quarter
+constexpr int kQUnitPairs = 8;           // pairs per staging unit: 16 features of all 32 rows
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar_addr) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_store8(uint32_t taddr, const uint32_t (&w)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+               "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&w)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+               "%14, %15}, [%16];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]),
+                 "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]), "=r"(w[14]), "=r"(w[15])
+               : "r"(taddr)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // Shared-memory bytes of the key tile: one 128-byte line per pair of features, the
@@ -284,44 +303,82 @@ __host__ __device__ constexpr int quant_key_tile_bytes(int num_features) { retur
 // time; with a constant depth the walk is called directly and plane offsets are computed).
 // LEAF_IDS: the launch records leaf ids instead of predictions.
 //
-// Shared memory: [0,128) sixteen mbarriers -- full[set][3], empty[set][3], table[set][2];
-// the ring of six 16 KB pieces (three per set); the leaf-number tables (two per set, 1 KB
-// each); the key tile.
+// A block is persistent: it takes the 32-row tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+// and is specialised by warp:
+//   warps 0..15   walkers, two sets of eight (set s takes the groups s, s+2, ... of the chunk).
+//                 The node planes stream through three 16 KB slots per set, filled by bulk
+//                 copies; the walker warp that is the last of its set to leave a slot issues
+//                 the copy of the piece that comes three later (a counter per slot tells it).
+//                 Apart from the leaf gathers the walkers touch shared memory only.
+//   warps 16..19  stagers: while a tile is walked they turn the NEXT tile's rows into keys and
+//                 park the finished key words in tensor memory -- the only on-chip space left
+//                 beside the 128 KB key tile -- stager s in lane quarter s (feature pairs
+//                 256 s ...).  The long-latency row loads thus never sit in a walker's
+//                 instruction stream.  At the end of the tile all twenty warps copy the words
+//                 from tensor memory into the key tile with conflict-free stores.
+// The first tile of a block is staged by the walkers themselves, straight into the key tile.
+// All hand-offs go through mbarriers with bounded waits; a wait that gives up ends the
+// launch with a status word instead of a hang.
+//
+// Shared memory: [0,256) mbarriers -- full[set][3], table[set][2], tile_done, sums_ready,
+// keys_ready --, the slot counters and the tensor-memory address; the ring of six 16 KB
+// pieces (three per set); the leaf-number tables (two per set, 1 KB each; they double as the
+// buffer of the cross-warp sum at the end of a tile); the key tile.
 template <int UD, bool LEAF_IDS>
-__global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kQThreads, 1)
+    tb_walk_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool producer = warp >= kQWalkers;
-  const int set = producer ? warp - kQWalkers : warp / kQSetWarps, sw = warp % kQSetWarps;
+  const int tid = threadIdx.x, lane = tid & 31;
+  // the warp's number through a shuffle: the compiler then knows that it -- and every role, set,
+  // slot and feature index derived from it -- is the same for all lanes (uniform registers and
+  // uniform constant loads instead of per-lane ones)
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const bool stager = warp >= kQWalkers;
+  const int set = (warp / kQSetWarps) & 1, sw = warp % kQSetWarps;
   const int F = p.num_features;
   const uint32_t bars_s = smem_u32(smem_raw);
-  const uint32_t full_s = bars_s + (uint32_t)set * 24u, empty_s = bars_s + 48u + (uint32_t)set * 24u;
+  const uint32_t full_s = bars_s + (uint32_t)set * 24u, done_s = bars_s + 48u + (uint32_t)set * 12u;
   const uint32_t table_s = bars_s + 96u + (uint32_t)set * 16u;
-  unsigned char *ring = smem_raw + 128 + (size_t)set * 3 * kQPiece;
+  const uint32_t tile_done_s = bars_s + 128u, sums_ready_s = bars_s + 136u, keys_ready_s = bars_s + 144u;
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_raw + 152);
+  unsigned char *ring = smem_raw + kQBarBytes + (size_t)set * 3 * kQPiece;
   const uint32_t ring_s = smem_u32(ring);
   // leaf numbers of a group, exchanged between the warps of a set (see below)
-  const uint32_t ltab_s = smem_u32(smem_raw + 128) + 6 * kQPiece + (uint32_t)set * 2048u;
+  const uint32_t ltab0_s = smem_u32(smem_raw + kQBarBytes) + 6 * kQPiece;
+  const uint32_t ltab_s = ltab0_s + (uint32_t)set * 2048u;
   // key tile: line m = features 2m | 2m+1 << 16 for the 32 rows
-  const uint32_t keys_s = smem_u32(smem_raw + 128) + 6 * kQPiece + kQLeafTableBytes;
+  const uint32_t keys_s = ltab0_s + kQLeafTableBytes;
   const uint32_t keys_lane = keys_s + lane * 4;
 
-  const long long row = (long long)blockIdx.x * 32 + lane;
-  const bool live = row < p.n_rows;
-  const float *rowp = p.rows + (live ? row : 0) * p.ld;
+  const long long num_tiles = (p.n_rows + 31) / 32;
+  const int my_tiles = (int)((num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+  const bool use_tmem = my_tiles > 1; // the host launches fewer blocks than tiles only for rows that 16-byte loads can read
   const int g0 = blockIdx.y * p.groups_per_chunk;
   const int g1 = min(p.num_groups, g0 + p.groups_per_chunk);
   const int NG = g1 - g0;
   const int NGs = (NG - set + 1) / 2; // groups set, set + 2, ... of the chunk
-  const int P = 2 * NGs;              // pieces of this set: upper levels and bottom level of the node planes
+  const int P = 2 * NGs;              // pieces of this set per tile: upper levels and bottom level of the node planes
+  const int NP = (F + 2) / 2;         // feature pairs = lines of the key tile
 
   if (tid == 0) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
-    for (int i = 0; i < 6; ++i) mbar_init(bars + i, 1);                  // full: the copy's bytes
-    for (int i = 6; i < 12; ++i) mbar_init(bars + i, kQSetWarps);        // empty: one arrival per walker warp
-    for (int i = 12; i < 16; ++i) mbar_init(bars + i, kQSetWarps);       // leaf-number table complete
+    for (int i = 0; i < 6; ++i) mbar_init(bars + i, 1);            // full: the copy's bytes
+    for (int i = 0; i < 6; ++i) reinterpret_cast<uint32_t *>(smem_raw + 48)[i] = 0; // warps that have left a slot
+    for (int i = 12; i < 16; ++i) mbar_init(bars + i, kQSetWarps); // leaf-number table complete
+    mbar_init(bars + 16, kQWalkers + kQStagers);                   // tile_done: the tile is walked, the next one's keys are staged
+    mbar_init(bars + 17, kQWalkers);                               // sums_ready: every walker's partial sums
+    mbar_init(bars + 18, kQWalkers + kQStagers);                   // keys_ready: every warp has copied its share of the keys
     fence_barrier_init();
   }
+  if (warp == 0 && use_tmem) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars_s + 152u), "r"(kQTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
   __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = use_tmem ? *tmem_slot : 0u;
 
   // plane offset (in rows of 32 elements) and depth of group gi of the chunk
   auto group_of = [&](int gi) -> uint2 {
@@ -331,252 +388,411 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
   };
 
   bool ok = true;
-  if (producer) {
-    // ---- the set's producer: streams the node planes through the set's three slots.  Piece
-    // q (upper levels of group q/2 for even q, its bottom level for odd q) goes to slot q mod 3
-    // as soon as every walker warp has released the piece that was there.
-    int slot = 0;
-    uint32_t round_parity = 1; // parity of the previous phase of empty[slot]: passes at once in round 0
-    auto issue = [&](int piece) {
-      const uint2 gm = group_of(2 * (piece >> 1) + set);
-      const uint32_t hs = 1u << (gm.y - 1); // slots per piece
-      const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
-      uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw) + set * 3 + slot;
-      mbar_expect_tx(bar, hs * 128u);
-      bulk_g2s(ring + (size_t)slot * kQPiece, p.node_plane + off, hs * 128u, bar);
-    };
-    for (int piece = 0; piece < P && ok; ++piece) {
-      if (piece >= 3) ok = mbar_wait_all_lanes(empty_s + 8u * (uint32_t)slot, round_parity);
-      if (ok && lane == 0) issue(piece);
-      if (++slot == 3) {
-        slot = 0;
-        if (piece >= 3) round_parity ^= 1u;
-      }
-      if (piece == 2) { // the walkers stage the row tile meanwhile; join them at its barrier
-        round_parity = 0;
-        __syncthreads();
-      }
-    }
-    if (P < 3) __syncthreads();
-  } else {
-    // ---- stage the row tile as keys
-    // A warp takes a block of 32 consecutive features: every load instruction reads 128
-    // contiguous bytes of ONE row (lane = feature), so DRAM sees whole lines and adjacent
-    // warps continue the same rows.  A lane thus collects its feature for all 32 rows and
-    // packs the keys two to a register; neighbouring lanes (features 2m, 2m+1) then swap
-    // halves through a shuffle, so that the even lane holds the finished words of rows
-    // 0..15 and the odd lane those of rows 16..31, 64 contiguous bytes each, written with
-    // four 16-byte stores.  Loads go to L2 only (the unified L1 is almost entirely shared
-    // memory here); sixteen are in flight per thread.
-    const long long row0 = (long long)blockIdx.x * 32;
-    const int live_rows = (int)min((long long)32, p.n_rows - row0);
-    const float *tile = p.rows + row0 * p.ld;
-    const bool odd = lane & 1;
-    // byte selectors: the even feature's packed keys are operand a on even lanes, b on odd
-    const uint32_t sel_lo = odd ? 0x1054u : 0x5410u, sel_hi = odd ? 0x3276u : 0x7632u;
-    for (int f0 = warp * 32; f0 <= F; f0 += kQWalkers * 32) {
-      const int f = f0 + lane;
-      const bool fok = f < F;
-      const float lo = fok ? __ldg(p.lo + f) : 0.f, sc = fok ? __ldg(p.scale + f) : 0.f;
-      uint32_t packed[16]; // keys of rows 2i | 2i+1 << 16 of this lane's feature
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        float x[16];
-#pragma unroll
-        for (int r = 0; r < 16; ++r) {
-          const int rr = part * 16 + r;
-          x[r] = (fok && rr < live_rows) ? __ldcg(tile + (long long)rr * p.ld + f) : 0.f;
-        }
-#pragma unroll
-        for (int r = 0; r < 16; r += 2)
-          packed[part * 8 + r / 2] = quant_key15_dev(x[r], lo, sc) | (quant_key15_dev(x[r + 1], lo, sc) << 16);
-      }
-      if (f == F) { // the sentinel feature: the largest key for every row
-#pragma unroll
-        for (int i = 0; i < 16; ++i) packed[i] = 0x7bff7bffu;
-      }
-      uint32_t w[16];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t own = odd ? packed[8 + i] : packed[i];
-        const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? packed[i] : packed[8 + i], 1);
-        w[2 * i] = __byte_perm(own, got, sel_lo);
-        w[2 * i + 1] = __byte_perm(own, got, sel_hi);
-      }
-      if (f <= F + (odd ? 1 : 0)) { // lanes of a pair that holds at least one real feature
-        const uint32_t dst = keys_s + (uint32_t)(f >> 1) * 128u + (odd ? 64u : 0u);
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 16u * c), "r"(w[4 * c]),
-                       "r"(w[4 * c + 1]), "r"(w[4 * c + 2]), "r"(w[4 * c + 3]));
-      }
-    }
-    __syncthreads();
-  }
-
-  float acc = 0.f;
   unsigned tie_count = 0;
-  if (!producer) {
+  // Copy of piece `piece` of a tile (upper levels of group piece/2 of the set for even
+  // numbers, its bottom level for odd ones) into ring slot `slot` of the set.
+  auto issue = [&](int piece, int slot) {
+    const uint2 gm = group_of(2 * (piece >> 1) + set);
+    const uint32_t hs = 1u << (gm.y - 1); // slots per piece
+    const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw) + set * 3 + slot;
+    mbar_expect_tx(bar, hs * 128u);
+    bulk_g2s(ring + (size_t)slot * kQPiece, p.node_plane + off, hs * 128u, bar);
+  };
+  // Staging of a tile's keys through tensor memory.  Lane quarter q (= warp mod 4) belongs to
+  // stager q and holds the feature pairs [256 q, 256 q + 256), in units of eight pairs (16
+  // features) of all 32 rows.  Within a unit lane 4a + j loads 16 bytes -- features 4j .. 4j+3
+  // of the unit -- of the rows a, a+8, a+16, a+24: four neighbouring lanes read 64 contiguous
+  // bytes of a row (8 lines per load instruction instead of the 32 of a lane = row pattern),
+  // and the lane's key parameters are one 16-byte load each.  A lane thus finishes the words of
+  // pairs 2j, 2j+1 for four rows; it stores them rotated by j (slot s holds row
+  // a + 8 ((s + j) mod 4)), so that when the columns are copied into the key tile the 32 lanes
+  // of a store hit 32 different rows, i.e. banks.
+  const int pair0 = (warp & 3) * kQStagerPairs;
+  const uint32_t taddr = tmem_base + ((uint32_t)(warp & 3) * 32u << 16);
+  const int sa = lane >> 2, sj = lane & 3;
+  struct Unit { // a staging unit in flight
+    float4 x[4], lo, sc;
+  };
+  // loads of unit u of the tile whose first row is at `base`, `live_rows` of them real
+  auto unit_load = [&](const float *base, int live_rows, int u, Unit &un) {
+    const int f = 2 * (pair0 + kQUnitPairs * u) + 4 * sj; // a multiple of 4, like F: f < F covers f + 3
+    const bool in = f < F;                                // p.lo / p.scale are padded to a multiple of four entries
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = sa + 8 * q;
+      un.x[q] = (in && r < live_rows) ? __ldg(reinterpret_cast<const float4 *>(base + (long long)r * p.ld + f))
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    un.lo = in ? __ldg(reinterpret_cast<const float4 *>(p.lo + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    un.sc = in ? __ldg(reinterpret_cast<const float4 *>(p.scale + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+  // keys of unit u into the quarter's columns of tensor memory
+  auto unit_store = [&](int u, const Unit &un) {
+    const int f = 2 * (pair0 + kQUnitPairs * u) + 4 * sj;
+    uint32_t w[4][2];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t k0 = quant_key15_dev(un.x[q].x, un.lo.x, un.sc.x), k1 = quant_key15_dev(un.x[q].y, un.lo.y, un.sc.y);
+      uint32_t k2 = quant_key15_dev(un.x[q].z, un.lo.z, un.sc.z), k3 = quant_key15_dev(un.x[q].w, un.lo.w, un.sc.w);
+      if (f >= F) k0 = k1 = k2 = k3 = 0x7bffu; // the sentinel feature (and padding): the largest key
+      w[q][0] = k0 | (k1 << 16);
+      w[q][1] = k2 | (k3 << 16);
+    }
+    // rotate the four rows left by j: slot s <- row index (s + j) mod 4
+    uint32_t t[4][2], o[8];
+#pragma unroll
+    for (int s4 = 0; s4 < 4; ++s4)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) t[s4][e] = (sj & 1) ? w[(s4 + 1) & 3][e] : w[s4][e];
+#pragma unroll
+    for (int s4 = 0; s4 < 4; ++s4)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) o[2 * s4 + e] = (sj & 2) ? t[(s4 + 2) & 3][e] : t[s4][e];
+    tmem_store8(taddr + (uint32_t)(kQUnitPairs * u), o);
+  };
+  // This warp's share of the copy from tensor memory into the key tile: the quarter's columns
+  // in chunks of 16 (two units), dealt to the quarter's five warps (rank = warp / 4).  Column
+  // 8u + 2s + e of lane 4a + j is the word of pair 256 q + 8u + 2j + e for row a + 8 ((s + j) mod 4).
+  auto copy_keys_out = [&]() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t rowoff[4];
+#pragma unroll
+    for (int s4 = 0; s4 < 4; ++s4) rowoff[s4] = (uint32_t)(sa + 8 * ((s4 + sj) & 3)) * 4u;
+#pragma unroll 1
+    for (int c0 = 16 * (warp >> 2); c0 < kQStagerPairs && pair0 + c0 < NP; c0 += 16 * 5) {
+      uint32_t w[16];
+      tmem_load16(taddr + (uint32_t)c0, w);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int m = pair0 + c0 + 8 * (i >> 3) + 2 * sj + (i & 1);
+        if (m < NP)
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(keys_s + (uint32_t)m * 128u + rowoff[(i >> 1) & 3]), "r"(w[i]) : "memory");
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  };
+
+  if (stager) {
+    // ---- stagers: keys of the next tile into tensor memory, three units in flight
+    const int NU = max(0, (min(NP, pair0 + kQStagerPairs) - pair0 + kQUnitPairs - 1) / kQUnitPairs);
+    for (int it = 0; it < my_tiles && ok; ++it) {
+      const bool has_next = it + 1 < my_tiles;
+      if (has_next) {
+        const long long tile = blockIdx.x + (long long)it * gridDim.x;
+        const long long row0_next = (tile + gridDim.x) * 32;
+        const float *base = p.rows + row0_next * p.ld;
+        const int live_rows = (int)min((long long)32, p.n_rows - row0_next);
+        if (it + 2 < my_tiles && warp == kQWalkers) { // the rows of the tile after that are pulled into L2
+          const long long row_after = (tile + 2ll * gridDim.x) * 32 + lane;
+          if (row_after < p.n_rows)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.rows + row_after * p.ld), "r"((uint32_t)F * 4u)
+                         : "memory");
+        }
+        Unit ua, ub, uc;
+        if (0 < NU) unit_load(base, live_rows, 0, ua);
+        if (1 < NU) unit_load(base, live_rows, 1, ub);
+        if (2 < NU) unit_load(base, live_rows, 2, uc);
+#pragma unroll 1
+        for (int u = 0; u < NU; u += 3) {
+          unit_store(u, ua);
+          if (u + 3 < NU) unit_load(base, live_rows, u + 3, ua);
+          if (u + 1 < NU) {
+            unit_store(u + 1, ub);
+            if (u + 4 < NU) unit_load(base, live_rows, u + 4, ub);
+          }
+          if (u + 2 < NU) {
+            unit_store(u + 2, uc);
+            if (u + 5 < NU) unit_load(base, live_rows, u + 5, uc);
+          }
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tile_done_s);
+      ok = mbar_wait_all_lanes(tile_done_s, (uint32_t)it & 1u);
+      if (!ok) break;
+      if (has_next) copy_keys_out();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(keys_ready_s);
+      ok = mbar_wait_all_lanes(keys_ready_s, (uint32_t)it & 1u); // the copy is complete: tensor memory may be rewritten
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+  } else {
+    // ---- the walk
     // the four columns this lane walks in every group of its set: warp w takes the columns
     // (lane + w + 8c) mod 32, so a load of the warp touches 32 distinct columns (banks) and
     // the eight warps of the set cover every (row, tree) pair of the group exactly once
-    uint32_t col[4], colb[4];
+    uint32_t col[4], colb[4], drop_s[4];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       col[c] = (uint32_t)(lane + sw + 8 * c) & 31u;
-      colb[c] = ring_s + col[c] * 4u; // the column's address in slot 0
+      colb[c] = ring_s + col[c] * 4u;                     // the column's address in slot 0
+      drop_s[c] = ltab_s + col[c] * 32u + (uint32_t)lane; // where its leaf number goes (table 0)
     }
-    float pend[4] = {0.f, 0.f, 0.f, 0.f}; // leaf values of the previous group, on their way from L2
-
-    // Leaf values come straight from L2, but not in the walk's lane assignment: there the 32
-    // lanes of a warp sit in 32 different trees, i.e. 32 different lines of the leaf plane
-    // whatever its layout.  The walkers therefore drop their leaf NUMBERS (one byte each) into
-    // a [column][row] table in shared memory and arrive on the table's barrier; one group
-    // later warp w of the set picks up columns 4w .. 4w+3 for all 32 rows and loads those
-    // leaves from the column-major leaf plane, where one tree's 256 leaves span 1 KB: at most
-    // 8 lines per warp load instead of 32.  Lane = row on both sides, so the sum stays in the
-    // lane's register; the loads are consumed one group later still.  Two tables alternate:
-    // table k mod 2 is rewritten in group k+2 after the wait for that group's bottom-level
-    // piece, whose slot every warp of the set has released after reading table k.
-    // (element offsets fit 32 bits: the host refuses planes of 2^32 elements or more)
+    // pieces are consumed in order, tile after tile: slot and phase of the next piece, and the
+    // phase of the leaf-number tables, follow from counters
+    int slot = 0;
+    uint32_t parity = 0, kk = 0; // kk: groups this warp has walked so far
+    const bool elected = lane == 0;
     const uint32_t my_cols_s = ltab_s + (4u * (uint32_t)sw) * 32u + (uint32_t)lane;
-    auto fetch_leaves = [&](int gi_prev, uint2 gprev, uint32_t buf) {
-      const uint32_t slots = 2u << (gprev.y - 1);
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const uint32_t c = 4u * (uint32_t)sw + (uint32_t)w;
-        uint32_t leaf;
-        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(leaf) : "r"(my_cols_s + buf * 1024u + (uint32_t)w * 32u));
-        const uint32_t e = gprev.x * 32u + c * slots + leaf;
-        if (LEAF_IDS) {
-          if (live) {
-            const int t = p.tree_index[(g0 + gi_prev) * 32 + (int)c];
-            if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
+    // A warp is done with the piece in `slot` (piece number `piece` of tile `it`): the last of
+    // the set's eight warps to say so starts the copy of the piece three later into the slot.
+    auto release = [&](uint32_t slot, int piece, int it) {
+      __syncwarp();
+      if (elected) {
+        const uint32_t cnt = done_s + 4u * slot;
+        uint32_t old;
+        asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(cnt) : "memory");
+        if (old == kQSetWarps - 1) {
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt), "r"(0u) : "memory");
+          int next = piece + 3;
+          while (next >= P) {
+            next -= P;
+            ++it;
           }
-        } else {
-          pend[w] = __ldg(p.leaf_plane + e);
+          if (it < my_tiles) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // reads of the slot before the copy's writes
+            issue(next, (int)slot);
+          }
         }
       }
     };
-    uint2 gprev = make_uint2(0, 0);
-    int gi_prev = -1;
-    // where this lane drops the leaf numbers of its four walks (table 0)
-    uint32_t drop_s[4];
+    // the first three pieces of the block (a tile may have fewer than three)
+    if (sw == 0 && elected)
+      for (int q = 0, piece = 0, it = 0; q < 3 && P > 0; ++q, ++piece) {
+        if (piece >= P) {
+          piece = 0;
+          ++it;
+        }
+        if (it < my_tiles) issue(piece, q);
+      }
+
+    // ---- the first tile: the walkers stage the rows themselves
+    {
+      // A warp takes a block of 32 consecutive features: every load instruction reads 128
+      // contiguous bytes of ONE row (lane = feature), so DRAM sees whole lines and adjacent
+      // warps continue the same rows.  A lane thus collects its feature for all 32 rows and
+      // packs the keys two to a register; neighbouring lanes (features 2m, 2m+1) then swap
+      // halves through a shuffle, so that the even lane holds the finished words of rows
+      // 0..15 and the odd lane those of rows 16..31, 64 contiguous bytes each, written with
+      // four 16-byte stores.  Loads go to L2 only; sixteen are in flight per thread.
+      const long long row0 = (long long)blockIdx.x * 32;
+      const int live_rows = (int)min((long long)32, p.n_rows - row0);
+      const float *tile = p.rows + row0 * p.ld;
+      const bool odd = lane & 1;
+      // byte selectors: the even feature's packed keys are operand a on even lanes, b on odd
+      const uint32_t sel_lo = odd ? 0x1054u : 0x5410u, sel_hi = odd ? 0x3276u : 0x7632u;
+      for (int f0 = warp * 32; f0 <= F; f0 += kQWalkers * 32) {
+        const int f = f0 + lane;
+        const bool fok = f < F;
+        const float lo = fok ? __ldg(p.lo + f) : 0.f, sc = fok ? __ldg(p.scale + f) : 0.f;
+        uint32_t packed[16]; // keys of rows 2i | 2i+1 << 16 of this lane's feature
 #pragma unroll
-    for (int c = 0; c < 4; ++c) drop_s[c] = ltab_s + col[c] * 32u + (uint32_t)lane;
+        for (int part = 0; part < 2; ++part) {
+          float x[16];
+#pragma unroll
+          for (int r = 0; r < 16; ++r) {
+            const int rr = part * 16 + r;
+            x[r] = (fok && rr < live_rows) ? __ldcg(tile + (long long)rr * p.ld + f) : 0.f;
+          }
+#pragma unroll
+          for (int r = 0; r < 16; r += 2)
+            packed[part * 8 + r / 2] = quant_key15_dev(x[r], lo, sc) | (quant_key15_dev(x[r + 1], lo, sc) << 16);
+        }
+        if (f == F) { // the sentinel feature: the largest key for every row
+#pragma unroll
+          for (int i = 0; i < 16; ++i) packed[i] = 0x7bff7bffu;
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t own = odd ? packed[8 + i] : packed[i];
+          const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? packed[i] : packed[8 + i], 1);
+          w[2 * i] = __byte_perm(own, got, sel_lo);
+          w[2 * i + 1] = __byte_perm(own, got, sel_hi);
+        }
+        if (f <= F + (odd ? 1 : 0)) { // lanes of a pair that holds at least one real feature
+          const uint32_t dst = keys_s + (uint32_t)(f >> 1) * 128u + (odd ? 64u : 0u);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 16u * c), "r"(w[4 * c]),
+                         "r"(w[4 * c + 1]), "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
+                         : "memory");
+        }
+      }
+      // only the walkers take part, and nothing can have failed yet
+      asm volatile("bar.sync 1, %0;" ::"r"(32 * kQWalkers) : "memory");
+    }
 
-    // pieces are consumed in order: slot and phase of the next piece follow from counters
-    int slot = 0;
-    uint32_t parity = 0;
-    const bool elected = lane == 0;
+    for (int it = 0; it < my_tiles && ok; ++it) {
+      const long long tile = blockIdx.x + (long long)it * gridDim.x;
+      const long long row = tile * 32 + lane;
+      const bool live = row < p.n_rows;
+      const float *rowp = p.rows + (live ? row : 0) * p.ld;
+      float acc = 0.f;
+      float pend[4] = {0.f, 0.f, 0.f, 0.f}; // leaf values on their way from L2
+      const bool has_next = it + 1 < my_tiles;
 
-    for (int k = 0; k < NGs && ok; ++k) {
-      const int gi = 2 * k + set;
-      const uint2 gm = group_of(gi);
-      const uint32_t depth = UD ? (uint32_t)UD : gm.y, hs = 1u << (depth - 1);
-
-      // leaves of the previous group, once its table is complete
-      if (gi_prev >= 0) {
-        ok = mbar_wait_all_lanes(table_s + 8u * ((uint32_t)(k - 1) & 1u), ((uint32_t)(k - 1) >> 1) & 1u);
-        if (!ok) break;
+      // Leaf values come straight from L2, but not in the walk's lane assignment: there the 32
+      // lanes of a warp sit in 32 different trees, i.e. 32 different lines of the leaf plane
+      // whatever its layout.  The walkers therefore drop their leaf NUMBERS (one byte each) into
+      // a [column][row] table in shared memory and arrive on the table's barrier; one group
+      // later -- after the upper levels, so that the table has long been completed -- warp w
+      // of the set picks up columns 4w .. 4w+3 for all 32 rows and loads those leaves from the
+      // column-major leaf plane, where one tree's 256 leaves span 1 KB: at most 8 lines per
+      // warp load instead of 32.  Lane = row on both sides, so the sum stays in the lane's
+      // register; the loads are consumed one group later still.  Two tables alternate: table
+      // k mod 2 is rewritten in group k+2 after the wait for that group's bottom-level piece,
+      // whose slot every warp of the set has released only after reading table k.
+      // (element offsets fit 32 bits: the host refuses planes of 2^32 elements or more)
+      auto fetch_leaves = [&](int gi_prev, uint2 gprev, uint32_t buf) {
+        const uint32_t slots = 2u << (gprev.y - 1);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const uint32_t c = 4u * (uint32_t)sw + (uint32_t)w;
+          uint32_t leaf;
+          asm volatile("ld.shared.u8 %0, [%1];" : "=r"(leaf) : "r"(my_cols_s + buf * 1024u + (uint32_t)w * 32u) : "memory");
+          const uint32_t e = gprev.x * 32u + c * slots + leaf;
+          if (LEAF_IDS) {
+            if (live) {
+              const int t = p.tree_index[(g0 + gi_prev) * 32 + (int)c];
+              if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
+            }
+          } else {
+            pend[w] = __ldg(p.leaf_plane + e);
+          }
+        }
+      };
+      // waits for the table of the group walked before this one and fetches its leaves
+      auto previous_leaves = [&](int gi_prev, uint2 gprev) -> bool {
+        const uint32_t kprev = kk - 1u;
+        if (!mbar_wait_all_lanes(table_s + 8u * (kprev & 1u), (kprev >> 1) & 1u)) return false;
         acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
-        fetch_leaves(gi_prev, gprev, (uint32_t)(k - 1) & 1u);
-      }
+        fetch_leaves(gi_prev, gprev, kprev & 1u);
+        return true;
+      };
+      uint2 gprev = make_uint2(0, 0);
+      int gi_prev = -1;
 
-      // the two pieces of this group
-      const uint32_t su = (uint32_t)slot, pu = parity;
-      if (++slot == 3) { slot = 0; parity ^= 1u; }
-      const uint32_t sb = (uint32_t)slot, pb = parity;
-      if (++slot == 3) { slot = 0; parity ^= 1u; }
-      uint32_t A[4], bot[4], ties = 0;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        bot[c] = colb[c] + sb * kQPiece;
-        A[c] = bot[c];
-      }
+      for (int k = 0; k < NGs && ok; ++k, ++kk) {
+        const int gi = 2 * k + set;
+        const uint2 gm = group_of(gi);
+        const uint32_t depth = UD ? (uint32_t)UD : gm.y, hs = 1u << (depth - 1);
 
-      // upper levels 0 .. depth-2: ends at the addresses of the bottom-level nodes
-      ok = mbar_wait_all_lanes(full_s + 8u * su, pu);
-      if (!ok) break;
-      if (depth >= 2) {
-        uint32_t cu[4], cx[4];
+        // the two pieces of this group
+        const uint32_t su = (uint32_t)slot, pu = parity;
+        if (++slot == 3) { slot = 0; parity ^= 1u; }
+        const uint32_t sb = (uint32_t)slot, pb = parity;
+        if (++slot == 3) { slot = 0; parity ^= 1u; }
+        uint32_t A[4], bot[4], ties = 0;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          A[c] = colb[c] + su * kQPiece;
-          cu[c] = 128u - A[c];
-          cx[c] = cu[c] + bot[c] - A[c] - 128u * (hs - 1u);
+          bot[c] = colb[c] + sb * kQPiece;
+          A[c] = bot[c];
         }
-        if constexpr (UD >= 2)
-          quant_upper4<UD>(A, ties, keys_lane, cu, cx);
-        else
-          quant_upper4_any(depth, A, ties, keys_lane, cu, cx);
-        if (ties) { // rare: the tied column is walked again on exact values
+
+        // upper levels 0 .. depth-2: ends at the addresses of the bottom-level nodes
+        ok = mbar_wait_all_lanes(full_s + 8u * su, pu);
+        if (!ok) break;
+        if (depth >= 2) {
+          uint32_t cu[4], cx[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            A[c] = colb[c] + su * kQPiece;
+            cu[c] = 128u - A[c];
+            cx[c] = cu[c] + bot[c] - A[c] - 128u * (hs - 1u);
+          }
+          if constexpr (UD >= 2)
+            quant_upper4<UD>(A, ties, keys_lane, cu, cx);
+          else
+            quant_upper4_any(depth, A, ties, keys_lane, cu, cx);
+          if (ties) { // rare: the tied column is walked again on exact values
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              if (ties & (1u << c)) {
+                A[c] = bot[c] + 128u * quant_upper_exact(colb[c] + su * kQPiece, keys_lane, p.exact_plane, gm.x, depth,
+                                                         col[c], rowp);
+                ++tie_count;
+              }
+            ties = 0;
+          }
+        }
+        // leaves of the previous group (before the upper-level piece is released: see above)
+        if (gi_prev >= 0) {
+          ok = previous_leaves(gi_prev, gprev);
+          if (!ok) break;
+        }
+        release(su, 2 * k, it);
+
+        // bottom decision level; the leaf numbers go into the table
+        ok = mbar_wait_all_lanes(full_s + 8u * sb, pb);
+        if (!ok) break;
+        quant_bottom4(A, ties, keys_lane, bot);
+        if (ties) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
             if (ties & (1u << c)) {
-              A[c] = bot[c] + 128u * quant_upper_exact(colb[c] + su * kQPiece, keys_lane, p.exact_plane, gm.x, depth,
-                                                       col[c], rowp);
+              A[c] = quant_bottom_exact(bot[c], A[c] >> 1, keys_lane, p.exact_plane, gm.x, depth, col[c], rowp);
               ++tie_count;
             }
-          ties = 0;
+        }
+        const uint32_t buf = (kk & 1u) * 1024u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop_s[c] + buf), "r"(A[c]) : "memory");
+        release(sb, 2 * k + 1, it);
+        if (elected) mbar_arrive(table_s + 8u * (kk & 1u));
+        gprev = gm;
+        gi_prev = gi;
+      }
+      if (ok && gi_prev >= 0) {
+        ok = previous_leaves(gi_prev, gprev);
+        if (ok) acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
+      }
+      if (!ok) break;
+
+      // ---- end of the tile.  Every walker and stager arrives; past this barrier the key tile and
+      // the leaf-number tables are free and the next tile's keys are complete in tensor memory.
+      __syncwarp();
+      if (elected) mbar_arrive(tile_done_s);
+      ok = mbar_wait_all_lanes(tile_done_s, (uint32_t)it & 1u);
+      if (!ok) break;
+      if (!LEAF_IDS) { // partial sums of the 16 warps, through the (now free) tables of set 0
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(ltab0_s + (uint32_t)(warp * 32 + lane) * 4u), "f"(acc) : "memory");
+        __syncwarp();
+        if (elected) mbar_arrive(sums_ready_s);
+      }
+      if (has_next) copy_keys_out();
+      if (warp == 0 && !LEAF_IDS) { // fixed-order sum over the warps, then the row's result
+        ok = mbar_wait_all_lanes(sums_ready_s, (uint32_t)it & 1u);
+        if (!ok) break;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < kQWalkers; ++w) s += lds_f32(ltab0_s + (uint32_t)(w * 32 + lane) * 4u);
+        if (live) {
+          if (p.write_partial)
+            p.partial[(long long)blockIdx.y * p.n_rows + row] = s;
+          else
+            reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + s, p.transform);
         }
       }
       __syncwarp();
-      if (elected) mbar_arrive(empty_s + 8u * su);
-
-      // bottom decision level; the leaf numbers go into the table
-      ok = mbar_wait_all_lanes(full_s + 8u * sb, pb);
-      if (!ok) break;
-      quant_bottom4(A, ties, keys_lane, bot);
-      if (ties) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          if (ties & (1u << c)) {
-            A[c] = quant_bottom_exact(bot[c], A[c] >> 1, keys_lane, p.exact_plane, gm.x, depth, col[c], rowp);
-            ++tie_count;
-          }
-      }
-      const uint32_t buf = ((uint32_t)k & 1u) * 1024u;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop_s[c] + buf), "r"(A[c]) : "memory");
-      __syncwarp();
-      if (elected) {
-        mbar_arrive(empty_s + 8u * sb);
-        mbar_arrive(table_s + 8u * ((uint32_t)k & 1u));
-      }
-      gprev = gm;
-      gi_prev = gi;
-    }
-    if (ok && gi_prev >= 0) {
-      ok = mbar_wait_all_lanes(table_s + 8u * ((uint32_t)(NGs - 1) & 1u), ((uint32_t)(NGs - 1) >> 1) & 1u);
-      if (ok) {
-        acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
-        pend[0] = pend[1] = pend[2] = pend[3] = 0.f;
-        fetch_leaves(gi_prev, gprev, (uint32_t)(NGs - 1) & 1u);
-        acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
-      }
+      if (elected) mbar_arrive(keys_ready_s); // past this barrier the tables (the sums' buffer) are rewritten
+      ok = mbar_wait_all_lanes(keys_ready_s, (uint32_t)it & 1u);
     }
   }
   // every wait above is bounded: a wait that gave up ends the launch with a status word
-  if (__syncthreads_or(!ok)) {
+  const bool failed = __syncthreads_or(!ok) != 0;
+  if (warp == 0 && use_tmem) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kQTmemCols) : "memory");
+  }
+  if (failed) {
     if (tid == 0) atomicExch(p.status, 4);
     return;
   }
   if (p.tie_count != nullptr && tie_count) atomicAdd(p.tie_count, (unsigned long long)tie_count);
-  if (LEAF_IDS || producer) return;
-
-  // ---- combine the walker warps (one partial per row each)
-  float *red = reinterpret_cast<float *>(smem_raw + 128);
-  red[warp * 32 + lane] = acc;
-  asm volatile("bar.sync 1, %0;" ::"r"(32 * kQWalkers) : "memory");
-  if (warp != 0 || !live) return;
-  float s = 0.f;
-#pragma unroll
-  for (int w = 0; w < kQWalkers; ++w) s += red[w * 32 + lane];
-  if (p.write_partial)
-    p.partial[(long long)blockIdx.y * p.n_rows + row] = s;
-  else
-    reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + s, p.transform);
 }
 
 } // namespace tb

@@ -169,6 +169,22 @@ def generate_forest(seed: int, T: int, D: int, F: int, p: float, leaf_sigma: flo
                         float(initial), F, base_score)
 
 
+def node_depths(f: ForestArrays) -> np.ndarray:
+    """Decision levels above every node (root 0), for forests whose nodes are numbered in
+    level order with parents before children (what generate_forest produces)."""
+    depth = np.zeros(f.num_nodes, np.int32)
+    base = np.repeat(f.tree_off[:-1], np.diff(f.tree_off))
+    split = np.nonzero(f.left >= 0)[0]
+    # parents precede their children inside a tree, so one pass per level settles everything
+    frontier = split[depth[split] == 0]
+    frontier = frontier[np.isin(frontier, f.tree_off[:-1])]
+    while len(frontier):
+        kids = np.concatenate([base[frontier] + f.left[frontier], base[frontier] + f.right[frontier]])
+        depth[kids] = np.concatenate([depth[frontier], depth[frontier]]) + 1
+        frontier = kids[f.left[kids] >= 0]
+    return depth
+
+
 def generate_rows(seed: int, marginal: Marginal, n_rows: int) -> np.ndarray:
     rng = np.random.Generator(np.random.PCG64(seed))
     return marginal.sample_rows(rng, n_rows)
