@@ -271,8 +271,9 @@ constexpr int kQPiece = 16384;  // one ring slot: half a plane of a group of 8 l
 constexpr int kQSetWarps = 8;   // walker warps per set
 constexpr int kQWalkers = 2 * kQSetWarps;
 constexpr int kQStagers = 4;             // warps 16..19: one per lane quarter of tensor memory
-constexpr int kQThreads = 32 * (kQWalkers + kQStagers);
-constexpr int kQBarBytes = 256;          // mbarriers and a few control words
+constexpr int kQLeafWarps = 2;           // warps 20, 21: leaf gathers and row sums of set 0 / set 1
+constexpr int kQThreads = 32 * (kQWalkers + kQStagers + kQLeafWarps);
+constexpr int kQBarBytes = 512;          // mbarriers, a few control words, one row of partial sums
 constexpr uint32_t kQTmemCols = 256;     // 128 lanes x 256 columns x 4 bytes = the 128 KB of a key tile
 constexpr int kQStagerPairs = 256;       // feature pairs per stager = columns of its lane quarter
 constexpr int kQUnitPairs = 8;           // pairs per staging unit: 16 features of all 32 rows
@@ -309,38 +310,46 @@ __host__ __device__ constexpr int quant_key_tile_bytes(int num_features) { retur
 //                 The node planes stream through three 16 KB slots per set, filled by bulk
 //                 copies; the walker warp that is the last of its set to leave a slot issues
 //                 the copy of the piece that comes three later (a counter per slot tells it).
-//                 Apart from the leaf gathers the walkers touch shared memory only.
+//                 A walker ends a group by dropping its four leaf NUMBERS (one byte each) into
+//                 the set's [column][row] table: walkers touch shared memory only.
 //   warps 16..19  stagers: while a tile is walked they turn the NEXT tile's rows into keys and
 //                 park the finished key words in tensor memory -- the only on-chip space left
 //                 beside the 128 KB key tile -- stager s in lane quarter s (feature pairs
-//                 256 s ...).  The long-latency row loads thus never sit in a walker's
-//                 instruction stream.  At the end of the tile all twenty warps copy the words
-//                 from tensor memory into the key tile with conflict-free stores.
+//                 256 s ...).  At the end of the tile the twenty walker and stager warps copy
+//                 the words from tensor memory into the key tile with conflict-free stores.
+//   warps 20, 21  leaf warps, one per set: pick up each finished table, gather the leaf values
+//                 from the column-major leaf plane in L2 (lane = row; the leaves that the 32
+//                 rows need of ONE tree lie within 1 KB, at most 8 lines per warp load -- in
+//                 the walk's own lane assignment the 32 lanes sit in 32 different trees), keep
+//                 the row sums of their set and write the tile's results.  The long-latency
+//                 loads -- rows and leaves -- thus never sit in a walker's instruction stream.
 // The first tile of a block is staged by the walkers themselves, straight into the key tile.
 // All hand-offs go through mbarriers with bounded waits; a wait that gives up ends the
 // launch with a status word instead of a hang.
 //
-// Shared memory: [0,256) mbarriers -- full[set][3], table[set][2], tile_done, sums_ready,
-// keys_ready --, the slot counters and the tensor-memory address; the ring of six 16 KB
-// pieces (three per set); the leaf-number tables (two per set, 1 KB each; they double as the
-// buffer of the cross-warp sum at the end of a tile); the key tile.
+// Shared memory: [0,512) mbarriers -- full[set][3], table_full[set][2], table_free[set][2],
+// tile_done, keys_ready, sum_ready, sum_free --, the slot counters, the tensor-memory address
+// and the row sums that leaf warp 1 hands to leaf warp 0; the ring of six 16 KB pieces (three
+// per set); the leaf-number tables (two per set, 1 KB each); the key tile.
+// (22 warps: registers are handed out to four warps at a time, so 24 x 32 x 80 fill the register file)
 template <int UD, bool LEAF_IDS>
-__global__ void __launch_bounds__(kQThreads, 1)
-    tb_walk_quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31;
   // the warp's number through a shuffle: the compiler then knows that it -- and every role, set,
   // slot and feature index derived from it -- is the same for all lanes (uniform registers and
   // uniform constant loads instead of per-lane ones)
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-  const bool stager = warp >= kQWalkers;
-  const int set = (warp / kQSetWarps) & 1, sw = warp % kQSetWarps;
+  const bool stager = warp >= kQWalkers && warp < kQWalkers + kQStagers, leafer = warp >= kQWalkers + kQStagers;
+  const int set = leafer ? warp - (kQWalkers + kQStagers) : (warp / kQSetWarps) & 1, sw = warp % kQSetWarps;
   const int F = p.num_features;
   const uint32_t bars_s = smem_u32(smem_raw);
   const uint32_t full_s = bars_s + (uint32_t)set * 24u, done_s = bars_s + 48u + (uint32_t)set * 12u;
   const uint32_t table_s = bars_s + 96u + (uint32_t)set * 16u;
-  const uint32_t tile_done_s = bars_s + 128u, sums_ready_s = bars_s + 136u, keys_ready_s = bars_s + 144u;
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_raw + 152);
+  const uint32_t tile_done_s = bars_s + 128u, keys_ready_s = bars_s + 144u;
+  const uint32_t sum_ready_s = bars_s + 184u, sum_free_s = bars_s + 192u, sums1_s = bars_s + 256u;
+  const uint32_t table_free_s = bars_s + 152u + (uint32_t)set * 16u;
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_raw + 240);
   unsigned char *ring = smem_raw + kQBarBytes + (size_t)set * 3 * kQPiece;
   const uint32_t ring_s = smem_u32(ring);
   // leaf numbers of a group, exchanged between the warps of a set (see below)
@@ -364,14 +373,16 @@ __global__ void __launch_bounds__(kQThreads, 1)
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
     for (int i = 0; i < 6; ++i) mbar_init(bars + i, 1);            // full: the copy's bytes
     for (int i = 0; i < 6; ++i) reinterpret_cast<uint32_t *>(smem_raw + 48)[i] = 0; // warps that have left a slot
-    for (int i = 12; i < 16; ++i) mbar_init(bars + i, kQSetWarps); // leaf-number table complete
+    for (int i = 12; i < 16; ++i) mbar_init(bars + i, kQSetWarps); // table_full: every walker of the set has written
     mbar_init(bars + 16, kQWalkers + kQStagers);                   // tile_done: the tile is walked, the next one's keys are staged
-    mbar_init(bars + 17, kQWalkers);                               // sums_ready: every walker's partial sums
     mbar_init(bars + 18, kQWalkers + kQStagers);                   // keys_ready: every warp has copied its share of the keys
+    for (int i = 19; i < 23; ++i) mbar_init(bars + i, 1);          // table_free: the leaf warp has read the table
+    mbar_init(bars + 23, 1);                                       // sum_ready: leaf warp 1 has written its row sums
+    mbar_init(bars + 24, 1);                                       // sum_free: leaf warp 0 has read them
     fence_barrier_init();
   }
   if (warp == 0 && use_tmem) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars_s + 152u), "r"(kQTmemCols)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars_s + 240u), "r"(kQTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -474,7 +485,7 @@ __global__ void __launch_bounds__(kQThreads, 1)
   };
 
   if (stager) {
-    // ---- stagers: keys of the next tile into tensor memory, three units in flight
+    // ---- stagers: keys of the next tile into tensor memory
     const int NU = max(0, (min(NP, pair0 + kQStagerPairs) - pair0 + kQUnitPairs - 1) / kQUnitPairs);
     for (int it = 0; it < my_tiles && ok; ++it) {
       const bool has_next = it + 1 < my_tiles;
@@ -489,21 +500,16 @@ __global__ void __launch_bounds__(kQThreads, 1)
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.rows + row_after * p.ld), "r"((uint32_t)F * 4u)
                          : "memory");
         }
-        Unit ua, ub, uc;
+        Unit ua, ub; // two units in flight
         if (0 < NU) unit_load(base, live_rows, 0, ua);
         if (1 < NU) unit_load(base, live_rows, 1, ub);
-        if (2 < NU) unit_load(base, live_rows, 2, uc);
 #pragma unroll 1
-        for (int u = 0; u < NU; u += 3) {
+        for (int u = 0; u < NU; u += 2) {
           unit_store(u, ua);
-          if (u + 3 < NU) unit_load(base, live_rows, u + 3, ua);
+          if (u + 2 < NU) unit_load(base, live_rows, u + 2, ua);
           if (u + 1 < NU) {
             unit_store(u + 1, ub);
-            if (u + 4 < NU) unit_load(base, live_rows, u + 4, ub);
-          }
-          if (u + 2 < NU) {
-            unit_store(u + 2, uc);
-            if (u + 5 < NU) unit_load(base, live_rows, u + 5, uc);
+            if (u + 3 < NU) unit_load(base, live_rows, u + 3, ub);
           }
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -518,6 +524,87 @@ __global__ void __launch_bounds__(kQThreads, 1)
       if (lane == 0) mbar_arrive(keys_ready_s);
       ok = mbar_wait_all_lanes(keys_ready_s, (uint32_t)it & 1u); // the copy is complete: tensor memory may be rewritten
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+  } else if (leafer) {
+    // ---- leaf warps: gather the leaf values of every finished table of the set, keep its row
+    // sums; leaf warp 0 adds the two sets' sums and writes the results
+    uint32_t kk = 0; // groups of the set seen so far (tables alternate, their barriers change phase)
+    const uint32_t ltab_lane = ltab_s + (uint32_t)lane;
+    for (int it = 0; it < my_tiles && ok; ++it) {
+      const long long tile = blockIdx.x + (long long)it * gridDim.x;
+      const long long row = tile * 32 + lane;
+      const bool live = row < p.n_rows;
+      // Leaf values are consumed one group after their loads were issued (a ring of 32), and
+      // summed in eight independent accumulators that are combined pairwise at the end: a single
+      // running fp32 sum over a thousand leaves would carry several times the rounding error.
+      float pend[32], acc8[8];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) pend[i] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc8[i] = 0.f;
+      for (int k = 0; k < NGs && ok; ++k, ++kk) {
+        const int gi = 2 * k + set;
+        const uint2 gm = group_of(gi);
+        const uint32_t slots = 2u << (gm.y - 1);
+        ok = mbar_wait_all_lanes(table_s + 8u * (kk & 1u), (kk >> 1) & 1u);
+        if (!ok) break;
+        const uint32_t tab = ltab_lane + (kk & 1u) * 1024u;
+        // (element offsets fit 32 bits: the host refuses planes of 2^32 elements or more)
+#pragma unroll
+        for (int oct = 0; oct < 4; ++oct) {
+          uint32_t e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t c = (uint32_t)(8 * oct + i);
+            uint32_t leaf;
+            asm volatile("ld.shared.u8 %0, [%1];" : "=r"(leaf) : "r"(tab + c * 32u) : "memory");
+            e[i] = gm.x * 32u + c * slots + leaf;
+          }
+          if (oct == 3) { // every column has been read: the table may be rewritten
+            __syncwarp();
+            if (lane == 0) mbar_arrive(table_free_s + 8u * (kk & 1u));
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = 8 * oct + i;
+            if (LEAF_IDS) {
+              if (live) {
+                const int t = p.tree_index[(g0 + gi) * 32 + c];
+                if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e[i]];
+              }
+            } else {
+              acc8[i] += pend[c]; // loaded a group ago
+              pend[c] = __ldg(p.leaf_plane + e[i]);
+            }
+          }
+        }
+      }
+      if (!ok) break;
+      if constexpr (!LEAF_IDS) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc8[i & 7] += pend[i];
+        const float acc = ((acc8[0] + acc8[1]) + (acc8[2] + acc8[3])) + ((acc8[4] + acc8[5]) + (acc8[6] + acc8[7]));
+        // the row's result: leaf warp 1 hands its sums to leaf warp 0 (well off the walkers' path)
+        if (set == 1) {
+          if (it > 0) ok = mbar_wait_all_lanes(sum_free_s, (uint32_t)(it - 1) & 1u);
+          if (!ok) break;
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums1_s + (uint32_t)lane * 4u), "f"(acc) : "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sum_ready_s);
+        } else {
+          ok = mbar_wait_all_lanes(sum_ready_s, (uint32_t)it & 1u);
+          if (!ok) break;
+          const float s = acc + lds_f32(sums1_s + (uint32_t)lane * 4u);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sum_free_s);
+          if (live) {
+            if (p.write_partial)
+              p.partial[(long long)blockIdx.y * p.n_rows + row] = s;
+            else
+              reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + s, p.transform);
+          }
+        }
+      }
     }
   } else {
     // ---- the walk
@@ -536,7 +623,6 @@ __global__ void __launch_bounds__(kQThreads, 1)
     int slot = 0;
     uint32_t parity = 0, kk = 0; // kk: groups this warp has walked so far
     const bool elected = lane == 0;
-    const uint32_t my_cols_s = ltab_s + (4u * (uint32_t)sw) * 32u + (uint32_t)lane;
     // A warp is done with the piece in `slot` (piece number `piece` of tile `it`): the last of
     // the set's eight warps to say so starts the copy of the piece three later into the slot.
     auto release = [&](uint32_t slot, int piece, int it) {
@@ -544,7 +630,8 @@ __global__ void __launch_bounds__(kQThreads, 1)
       if (elected) {
         const uint32_t cnt = done_s + 4u * slot;
         uint32_t old;
-        asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(cnt) : "memory");
+        // (relaxed: the warp's reads of the slot were issued before, and the shared-memory pipe keeps their order)
+        asm volatile("atom.relaxed.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(cnt) : "memory");
         if (old == kQSetWarps - 1) {
           asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt), "r"(0u) : "memory");
           int next = piece + 3;
@@ -631,51 +718,7 @@ __global__ void __launch_bounds__(kQThreads, 1)
       const long long row = tile * 32 + lane;
       const bool live = row < p.n_rows;
       const float *rowp = p.rows + (live ? row : 0) * p.ld;
-      float acc = 0.f;
-      float pend[4] = {0.f, 0.f, 0.f, 0.f}; // leaf values on their way from L2
       const bool has_next = it + 1 < my_tiles;
-
-      // Leaf values come straight from L2, but not in the walk's lane assignment: there the 32
-      // lanes of a warp sit in 32 different trees, i.e. 32 different lines of the leaf plane
-      // whatever its layout.  The walkers therefore drop their leaf NUMBERS (one byte each) into
-      // a [column][row] table in shared memory and arrive on the table's barrier; one group
-      // later -- after the upper levels, so that the table has long been completed -- warp w
-      // of the set picks up columns 4w .. 4w+3 for all 32 rows and loads those leaves from the
-      // column-major leaf plane, where one tree's 256 leaves span 1 KB: at most 8 lines per
-      // warp load instead of 32.  Lane = row on both sides, so the sum stays in the lane's
-      // register; the loads are consumed one group later still.  Two tables alternate: table
-      // k mod 2 is rewritten in group k+2 after the wait for that group's bottom-level piece,
-      // whose slot every warp of the set has released only after reading table k.
-      // (element offsets fit 32 bits: the host refuses planes of 2^32 elements or more)
-      auto fetch_leaves = [&](int gi_prev, uint2 gprev, uint32_t buf) {
-        const uint32_t slots = 2u << (gprev.y - 1);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const uint32_t c = 4u * (uint32_t)sw + (uint32_t)w;
-          uint32_t leaf;
-          asm volatile("ld.shared.u8 %0, [%1];" : "=r"(leaf) : "r"(my_cols_s + buf * 1024u + (uint32_t)w * 32u) : "memory");
-          const uint32_t e = gprev.x * 32u + c * slots + leaf;
-          if (LEAF_IDS) {
-            if (live) {
-              const int t = p.tree_index[(g0 + gi_prev) * 32 + (int)c];
-              if (t >= 0) p.leaf_ids[row * p.num_trees + t] = p.orig_leaf[e];
-            }
-          } else {
-            pend[w] = __ldg(p.leaf_plane + e);
-          }
-        }
-      };
-      // waits for the table of the group walked before this one and fetches its leaves
-      auto previous_leaves = [&](int gi_prev, uint2 gprev) -> bool {
-        const uint32_t kprev = kk - 1u;
-        if (!mbar_wait_all_lanes(table_s + 8u * (kprev & 1u), (kprev >> 1) & 1u)) return false;
-        acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
-        fetch_leaves(gi_prev, gprev, kprev & 1u);
-        return true;
-      };
-      uint2 gprev = make_uint2(0, 0);
-      int gi_prev = -1;
-
       for (int k = 0; k < NGs && ok; ++k, ++kk) {
         const int gi = 2 * k + set;
         const uint2 gm = group_of(gi);
@@ -719,11 +762,6 @@ __global__ void __launch_bounds__(kQThreads, 1)
             ties = 0;
           }
         }
-        // leaves of the previous group (before the upper-level piece is released: see above)
-        if (gi_prev >= 0) {
-          ok = previous_leaves(gi_prev, gprev);
-          if (!ok) break;
-        }
         release(su, 2 * k, it);
 
         // bottom decision level; the leaf numbers go into the table
@@ -738,17 +776,16 @@ __global__ void __launch_bounds__(kQThreads, 1)
               ++tie_count;
             }
         }
+        // the leaf numbers go into table kk mod 2, once the leaf warp has read what group kk - 2 left there
+        if (kk >= 2) {
+          ok = mbar_wait_all_lanes(table_free_s + 8u * (kk & 1u), ((kk >> 1) - 1u) & 1u);
+          if (!ok) break;
+        }
         const uint32_t buf = (kk & 1u) * 1024u;
 #pragma unroll
         for (int c = 0; c < 4; ++c) asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop_s[c] + buf), "r"(A[c]) : "memory");
         release(sb, 2 * k + 1, it);
         if (elected) mbar_arrive(table_s + 8u * (kk & 1u));
-        gprev = gm;
-        gi_prev = gi;
-      }
-      if (ok && gi_prev >= 0) {
-        ok = previous_leaves(gi_prev, gprev);
-        if (ok) acc += (pend[0] + pend[1]) + (pend[2] + pend[3]);
       }
       if (!ok) break;
 
@@ -758,27 +795,9 @@ __global__ void __launch_bounds__(kQThreads, 1)
       if (elected) mbar_arrive(tile_done_s);
       ok = mbar_wait_all_lanes(tile_done_s, (uint32_t)it & 1u);
       if (!ok) break;
-      if (!LEAF_IDS) { // partial sums of the 16 warps, through the (now free) tables of set 0
-        asm volatile("st.shared.f32 [%0], %1;" ::"r"(ltab0_s + (uint32_t)(warp * 32 + lane) * 4u), "f"(acc) : "memory");
-        __syncwarp();
-        if (elected) mbar_arrive(sums_ready_s);
-      }
       if (has_next) copy_keys_out();
-      if (warp == 0 && !LEAF_IDS) { // fixed-order sum over the warps, then the row's result
-        ok = mbar_wait_all_lanes(sums_ready_s, (uint32_t)it & 1u);
-        if (!ok) break;
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < kQWalkers; ++w) s += lds_f32(ltab0_s + (uint32_t)(w * 32 + lane) * 4u);
-        if (live) {
-          if (p.write_partial)
-            p.partial[(long long)blockIdx.y * p.n_rows + row] = s;
-          else
-            reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + s, p.transform);
-        }
-      }
       __syncwarp();
-      if (elected) mbar_arrive(keys_ready_s); // past this barrier the tables (the sums' buffer) are rewritten
+      if (elected) mbar_arrive(keys_ready_s);
       ok = mbar_wait_all_lanes(keys_ready_s, (uint32_t)it & 1u);
     }
   }
