@@ -215,7 +215,7 @@ def test_sixteen_bit_key_kernel_is_exact(name):
     want, want_ids = oracle.predict(forest, X, leaf_ids=True)
     df = kernels.DeviceForest(forest, representation="reorg", feature_bits=16, batch_hint=len(X))
     info = df.info()
-    assert info.schedule.feature_bits == 16 and info.threads_per_block == 704
+    assert info.schedule.feature_bits == 16 and info.threads_per_block == 768
     dX = _dev(X)
     ids = df.predict_leaf_ids(dX).cpu().numpy()
     df.check_status()

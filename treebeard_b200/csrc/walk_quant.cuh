@@ -272,7 +272,8 @@ constexpr int kQSetWarps = 8;   // walker warps per set
 constexpr int kQWalkers = 2 * kQSetWarps;
 constexpr int kQStagers = 4;             // warps 16..19: one per lane quarter of tensor memory
 constexpr int kQLeafWarps = 2;           // warps 20, 21: leaf gathers and row sums of set 0 / set 1
-constexpr int kQThreads = 32 * (kQWalkers + kQStagers + kQLeafWarps);
+constexpr int kQProducers = 2;           // warps 22, 23: ring producers of set 0 / set 1
+constexpr int kQThreads = 32 * (kQWalkers + kQStagers + kQLeafWarps + kQProducers);
 constexpr int kQBarBytes = 512;          // mbarriers, a few control words, one row of partial sums
 constexpr uint32_t kQTmemCols = 256;     // 128 lanes x 256 columns x 4 bytes = the 128 KB of a key tile
 constexpr int kQStagerPairs = 256;       // feature pairs per stager = columns of its lane quarter
@@ -307,9 +308,6 @@ __host__ __device__ constexpr int quant_key_tile_bytes(int num_features) { retur
 // A block is persistent: it takes the 32-row tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 // and is specialised by warp:
 //   warps 0..15   walkers, two sets of eight (set s takes the groups s, s+2, ... of the chunk).
-//                 The node planes stream through three 16 KB slots per set, filled by bulk
-//                 copies; the walker warp that is the last of its set to leave a slot issues
-//                 the copy of the piece that comes three later (a counter per slot tells it).
 //                 A walker ends a group by dropping its four leaf NUMBERS (one byte each) into
 //                 the set's [column][row] table: walkers touch shared memory only.
 //   warps 16..19  stagers: while a tile is walked they turn the NEXT tile's rows into keys and
@@ -323,15 +321,18 @@ __host__ __device__ constexpr int quant_key_tile_bytes(int num_features) { retur
 //                 the walk's own lane assignment the 32 lanes sit in 32 different trees), keep
 //                 the row sums of their set and write the tile's results.  The long-latency
 //                 loads -- rows and leaves -- thus never sit in a walker's instruction stream.
+//   warps 22, 23  ring producers, one per set: the node planes stream through three 16 KB slots
+//                 per set; a producer issues the bulk copy of the piece that comes three later
+//                 as soon as the set's eight walkers have arrived on the slot's barrier.
 // The first tile of a block is staged by the walkers themselves, straight into the key tile.
 // All hand-offs go through mbarriers with bounded waits; a wait that gives up ends the
 // launch with a status word instead of a hang.
 //
-// Shared memory: [0,512) mbarriers -- full[set][3], table_full[set][2], table_free[set][2],
-// tile_done, keys_ready, sum_ready, sum_free --, the slot counters, the tensor-memory address
+// Shared memory: [0,512) mbarriers -- full[set][3], empty[set][3], table_full[set][2],
+// table_free[set][2], tile_done, keys_ready, sum_ready, sum_free --, the tensor-memory address
 // and the row sums that leaf warp 1 hands to leaf warp 0; the ring of six 16 KB pieces (three
 // per set); the leaf-number tables (two per set, 1 KB each); the key tile.
-// (22 warps: registers are handed out to four warps at a time, so 24 x 32 x 80 fill the register file)
+// (24 warps x 32 x 80 registers fill the register file)
 template <int UD, bool LEAF_IDS>
 __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -340,11 +341,15 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
   // slot and feature index derived from it -- is the same for all lanes (uniform registers and
   // uniform constant loads instead of per-lane ones)
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-  const bool stager = warp >= kQWalkers && warp < kQWalkers + kQStagers, leafer = warp >= kQWalkers + kQStagers;
-  const int set = leafer ? warp - (kQWalkers + kQStagers) : (warp / kQSetWarps) & 1, sw = warp % kQSetWarps;
+  const bool stager = warp >= kQWalkers && warp < kQWalkers + kQStagers;
+  const bool leafer = warp >= kQWalkers + kQStagers && warp < kQWalkers + kQStagers + kQLeafWarps;
+  const bool producer = warp >= kQWalkers + kQStagers + kQLeafWarps;
+  // the set this warp works for (walkers: warps 0..7 / 8..15; leaf warps and producers: one per set)
+  const int set = (warp >= kQWalkers + kQStagers ? warp - kQWalkers - kQStagers : warp / kQSetWarps) & 1;
+  const int sw = warp % kQSetWarps;
   const int F = p.num_features;
   const uint32_t bars_s = smem_u32(smem_raw);
-  const uint32_t full_s = bars_s + (uint32_t)set * 24u, done_s = bars_s + 48u + (uint32_t)set * 12u;
+  const uint32_t full_s = bars_s + (uint32_t)set * 24u, empty_s = bars_s + 48u + (uint32_t)set * 24u;
   const uint32_t table_s = bars_s + 96u + (uint32_t)set * 16u;
   const uint32_t tile_done_s = bars_s + 128u, keys_ready_s = bars_s + 144u;
   const uint32_t sum_ready_s = bars_s + 184u, sum_free_s = bars_s + 192u, sums1_s = bars_s + 256u;
@@ -372,7 +377,7 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
   if (tid == 0) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
     for (int i = 0; i < 6; ++i) mbar_init(bars + i, 1);            // full: the copy's bytes
-    for (int i = 0; i < 6; ++i) reinterpret_cast<uint32_t *>(smem_raw + 48)[i] = 0; // warps that have left a slot
+    for (int i = 6; i < 12; ++i) mbar_init(bars + i, kQSetWarps);  // empty: one arrival per walker warp of the set
     for (int i = 12; i < 16; ++i) mbar_init(bars + i, kQSetWarps); // table_full: every walker of the set has written
     mbar_init(bars + 16, kQWalkers + kQStagers);                   // tile_done: the tile is walked, the next one's keys are staged
     mbar_init(bars + 18, kQWalkers + kQStagers);                   // keys_ready: every warp has copied its share of the keys
@@ -525,6 +530,22 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
       ok = mbar_wait_all_lanes(keys_ready_s, (uint32_t)it & 1u); // the copy is complete: tensor memory may be rewritten
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
+  } else if (producer) {
+    // ---- the set's ring producer.  The q-th piece (upper levels of a group for even q, its
+    // bottom level for odd q) goes to slot q mod 3 as soon as every walker warp of the set has
+    // released the piece that was there.
+    int slot = 0;
+    uint32_t round = 0; // how often the slots have wrapped
+    for (int it = 0; it < my_tiles && ok; ++it) {
+      for (int piece = 0; piece < P && ok; ++piece) {
+        if (round > 0) ok = mbar_wait_all_lanes(empty_s + 8u * (uint32_t)slot, (round - 1u) & 1u);
+        if (ok && lane == 0) issue(piece, slot);
+        if (++slot == 3) {
+          slot = 0;
+          ++round;
+        }
+      }
+    }
   } else if (leafer) {
     // ---- leaf warps: gather the leaf values of every finished table of the set, keep its row
     // sums; leaf warp 0 adds the two sets' sums and writes the results
@@ -623,39 +644,6 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
     int slot = 0;
     uint32_t parity = 0, kk = 0; // kk: groups this warp has walked so far
     const bool elected = lane == 0;
-    // A warp is done with the piece in `slot` (piece number `piece` of tile `it`): the last of
-    // the set's eight warps to say so starts the copy of the piece three later into the slot.
-    auto release = [&](uint32_t slot, int piece, int it) {
-      __syncwarp();
-      if (elected) {
-        const uint32_t cnt = done_s + 4u * slot;
-        uint32_t old;
-        // (relaxed: the warp's reads of the slot were issued before, and the shared-memory pipe keeps their order)
-        asm volatile("atom.relaxed.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(cnt) : "memory");
-        if (old == kQSetWarps - 1) {
-          asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt), "r"(0u) : "memory");
-          int next = piece + 3;
-          while (next >= P) {
-            next -= P;
-            ++it;
-          }
-          if (it < my_tiles) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // reads of the slot before the copy's writes
-            issue(next, (int)slot);
-          }
-        }
-      }
-    };
-    // the first three pieces of the block (a tile may have fewer than three)
-    if (sw == 0 && elected)
-      for (int q = 0, piece = 0, it = 0; q < 3 && P > 0; ++q, ++piece) {
-        if (piece >= P) {
-          piece = 0;
-          ++it;
-        }
-        if (it < my_tiles) issue(piece, q);
-      }
-
     // ---- the first tile: the walkers stage the rows themselves
     {
       // A warp takes a block of 32 consecutive features: every load instruction reads 128
@@ -762,7 +750,8 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
             ties = 0;
           }
         }
-        release(su, 2 * k, it);
+        __syncwarp();
+        if (elected) mbar_arrive(empty_s + 8u * su);
 
         // bottom decision level; the leaf numbers go into the table
         ok = mbar_wait_all_lanes(full_s + 8u * sb, pb);
@@ -784,8 +773,11 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
         const uint32_t buf = (kk & 1u) * 1024u;
 #pragma unroll
         for (int c = 0; c < 4; ++c) asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop_s[c] + buf), "r"(A[c]) : "memory");
-        release(sb, 2 * k + 1, it);
-        if (elected) mbar_arrive(table_s + 8u * (kk & 1u));
+        __syncwarp();
+        if (elected) {
+          mbar_arrive(empty_s + 8u * sb);
+          mbar_arrive(table_s + 8u * (kk & 1u));
+        }
       }
       if (!ok) break;
 
