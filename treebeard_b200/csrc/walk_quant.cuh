@@ -279,6 +279,35 @@ constexpr uint32_t kQTmemCols = 256;     // 128 lanes x 256 columns x 4 bytes = 
 constexpr int kQStagerPairs = 256;       // feature pairs per stager = columns of its lane quarter
 constexpr int kQUnitPairs = 8;           // pairs per staging unit: 16 features of all 32 rows
 
+// L2 eviction policies: the forest (2 MB, re-read by every tile of every block) should stay
+// in L2 while the rows (gigabytes, read once) stream through it.
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void *dst, const void *src, uint32_t bytes, uint64_t *bar, uint64_t pol) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+               : "memory");
+}
+__device__ __forceinline__ float4 ldg_f4_hint(const float *ptr, uint64_t pol) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(ptr), "l"(pol));
+  return v;
+}
+__device__ __forceinline__ float ldg_f32_hint(const float *ptr, uint64_t pol) {
+  float v;
+  asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(ptr), "l"(pol));
+  return v;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar_addr) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
 }
@@ -405,6 +434,7 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
 
   bool ok = true;
   unsigned tie_count = 0;
+  const uint64_t keep = l2_policy_keep(), stream = l2_policy_stream();
   // Copy of piece `piece` of a tile (upper levels of group piece/2 of the set for even
   // numbers, its bottom level for odd ones) into ring slot `slot` of the set.
   auto issue = [&](int piece, int slot) {
@@ -413,7 +443,7 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
     const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
     uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw) + set * 3 + slot;
     mbar_expect_tx(bar, hs * 128u);
-    bulk_g2s(ring + (size_t)slot * kQPiece, p.node_plane + off, hs * 128u, bar);
+    bulk_g2s_hint(ring + (size_t)slot * kQPiece, p.node_plane + off, hs * 128u, bar, keep);
   };
   // Staging of a tile's keys through tensor memory.  Lane quarter q (= warp mod 4) belongs to
   // stager q and holds the feature pairs [256 q, 256 q + 256), in units of eight pairs (16
@@ -437,8 +467,7 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int r = sa + 8 * q;
-      un.x[q] = (in && r < live_rows) ? __ldg(reinterpret_cast<const float4 *>(base + (long long)r * p.ld + f))
-                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+      un.x[q] = (in && r < live_rows) ? ldg_f4_hint(base + (long long)r * p.ld + f, stream) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     un.lo = in ? __ldg(reinterpret_cast<const float4 *>(p.lo + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
     un.sc = in ? __ldg(reinterpret_cast<const float4 *>(p.scale + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -502,7 +531,8 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
         if (it + 2 < my_tiles && warp == kQWalkers) { // the rows of the tile after that are pulled into L2
           const long long row_after = (tile + 2ll * gridDim.x) * 32 + lane;
           if (row_after < p.n_rows)
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.rows + row_after * p.ld), "r"((uint32_t)F * 4u)
+            asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(p.rows + row_after * p.ld),
+                         "r"((uint32_t)F * 4u), "l"(stream)
                          : "memory");
         }
         Unit ua, ub; // two units in flight
@@ -595,7 +625,7 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
               }
             } else {
               acc8[i] += pend[c]; // loaded a group ago
-              pend[c] = __ldg(p.leaf_plane + e[i]);
+              pend[c] = ldg_f32_hint(p.leaf_plane + e[i], keep);
             }
           }
         }
