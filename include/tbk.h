@@ -186,6 +186,15 @@ TBK_EXPORT int64_t tbk_last_kernel_time_us(tbk_forest *forest);
  * a bounded wait inside a kernel expired since the last check, else TBK_OK. */
 TBK_EXPORT int tbk_check_status(tbk_forest *forest);
 
+/* Failure drill, for tests of the error path: in the next tbk_predict* launch on this forest the
+ * bulk copy of the first tree stage is never issued and the stage waits give up after a few
+ * thousand polls, so the launch ends by itself with the status word set -- nothing faults or
+ * hangs, the results of that launch are undefined, tbk_check_status() then returns
+ * TBK_ERR_DEVICE_WAIT and the forest stays usable.  (The reference has no counterpart: its
+ * generated kernels have no waits and its host code aborts on errors.)  A launch that stages
+ * no trees (cache_trees = 2) has no such wait and is not affected. */
+TBK_EXPORT int tbk_debug_expire_next_wait(tbk_forest *forest);
+
 /* Number of kernel launches issued on behalf of this forest since creation. */
 TBK_EXPORT int64_t tbk_launch_count(const tbk_forest *forest);
 

@@ -97,8 +97,19 @@ class _CForest(ctypes.Structure):
                 ("num_features", ctypes.c_int32)]
 
 
-def build(ref_root: str | None = "/root/reference") -> None:
-    """Compile liboracle.so and, if the reference checkout exists, _ref/."""
+def reference_root() -> str | None:
+    """Where the reference checkout lies: the TREEBEARD_REF environment variable, else the
+    build container's mount point; None if neither exists."""
+    for root in (os.environ.get("TREEBEARD_REF"), os.path.join(os.sep, "root", "reference")):
+        if root and os.path.isdir(os.path.join(root, "src", "include")):
+            return root
+    return None
+
+
+def build(ref_root: str | None = None) -> None:
+    """Compile liboracle.so and, if a reference checkout is given (argument, else the
+    TREEBEARD_REF environment variable) and exists, the shim around its header in _ref/."""
+    ref_root = ref_root or reference_root()
     subprocess.run(["make", "-s", "-C", _HERE], check=True)
     if ref_root and os.path.isdir(os.path.join(ref_root, "src", "include")):
         subprocess.run(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"], check=True)

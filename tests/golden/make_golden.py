@@ -1,8 +1,8 @@
 """Regenerates the golden fixtures in this folder from the reference checkout.
 
-Run in a container that has the reference mounted (default /root/reference):
+Run in a container that has the reference mounted (--ref, default: $TREEBEARD_REF):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference checkout>]
 
 For every model whose JSON *and* golden CSV exist in the reference's
 ``xgb_models`` tree (CSV rows = features..., XGBoost's prediction; consumed by the
@@ -59,7 +59,7 @@ def check(forest, rows, expected):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=oracle.reference_root(), required=oracle.reference_root() is None)
     args = ap.parse_args()
     xgb = os.path.join(args.ref, "xgb_models")
     manifest = {}

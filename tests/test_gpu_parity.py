@@ -446,3 +446,27 @@ def test_sixteen_bit_keys_refuse_what_they_do_not_cover():
     forest, _ = small_config("c4")
     with pytest.raises(kernels.TbkError):
         kernels.DeviceForest(forest, representation="auto", feature_bits=16)
+
+
+@pytest.mark.parametrize("name,layout", [("c2", dict(representation="sparse")),
+                                         ("c3", dict(representation="auto", feature_bits=16)),
+                                         ("c5", dict(representation="auto", feature_bits=16))])
+def test_expired_device_wait_is_reported_and_survivable(name, layout):
+    """Failure drill on the host's initiative: the first tree stage of one launch is never
+    copied, so the kernel's bounded wait gives up.  The launch must end by itself, the status
+    check must report TBK_ERR_DEVICE_WAIT, and the next prediction must be correct again."""
+    from treebeard_b200 import kernels
+    forest, X = small_config(name)
+    want = oracle.predict(forest, X)
+    df = kernels.DeviceForest(forest, batch_hint=len(X), **layout)
+    dX = _dev(X)
+    assert_predictions_close(df.predict(dX).cpu().numpy(), want)
+    df.check_status()
+    df.expire_next_wait()
+    df.predict(dX)                      # results undefined, but it returns
+    torch.cuda.synchronize()
+    with pytest.raises(kernels.TbkError) as err:
+        df.check_status()
+    assert err.value.status == 4        # TBK_ERR_DEVICE_WAIT
+    assert_predictions_close(df.predict(dX).cpu().numpy(), want)
+    df.check_status()

@@ -9,7 +9,8 @@ from oracle import oracle
 from tests.helpers import small_config
 from treebeard_b200 import synth, treebeard
 
-REF_ONNX = "/root/reference/onnx_models/abalone_onnx_model_save.onnx"
+# the reference's own ONNX model, where its checkout is mounted
+REF_ONNX = os.path.join(oracle.reference_root() or "", "onnx_models", "abalone_onnx_model_save.onnx")
 
 
 def same_function(a, b, X):

@@ -90,6 +90,7 @@ struct tbk_forest {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   bool ev_pending = false;
   int64_t launches = 0;
+  bool expire_next_wait = false; // failure drill (tbk_debug_expire_next_wait)
   std::mutex mu;
 };
 
@@ -236,7 +237,9 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   p.vec4_ok = vec4 ? 1 : 0;
   p.status = f->d_status;
   p.tie_count = f->d_ties;
-  p.meta_bytes = 0;
+  p.skip_first_copy = f->expire_next_wait ? 1 : 0;
+  p.wait_tries = f->expire_next_wait ? 2000u : 0u;
+  f->expire_next_wait = false;
   // kernels specialised for forests whose groups all have 8 (or 6) levels; generic otherwise
   using QuantKernel = void (*)(const tb::QuantParams);
   const bool ids = mode == kLeafIds;
@@ -366,6 +369,9 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
   p.key_stride = 64u * (uint32_t)f->deep_row_warps; // the tile keeps its full width whatever rw is
   p.status = f->d_status;
   p.tie_count = f->d_ties;
+  p.skip_first_copy = f->expire_next_wait ? 1 : 0;
+  p.wait_tries = f->expire_next_wait ? 2000u : 0u;
+  f->expire_next_wait = false;
   // up to 20 warps the compiler may use 96 registers per thread, beyond that 64
   // specialised for forests whose pairs all have 12 levels; generic otherwise
   using DeepKernel = void (*)(const tb::DeepParams);
@@ -475,6 +481,9 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
   p.stage_bytes = plan.staged ? plan.stage_bytes : 0;
   p.vec4_ok = (pk.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0) ? 1 : 0;
   p.status = f->d_status;
+  p.skip_first_copy = (f->expire_next_wait && plan.staged) ? 1 : 0;
+  p.wait_limit = f->expire_next_wait ? 2000u : 0u;
+  f->expire_next_wait = false;
   // the plan's shared-memory size has no class table when class sums live in registers
   if (plan.class_regs && (plan.chunks != 1 || mode == kPartial))
     return fail(TBK_ERR_UNSUPPORTED, "launch plan with register class sums needs a single tree chunk");
@@ -969,6 +978,13 @@ int64_t tbk_launch_count(const tbk_forest *f) { return f ? f->launches : 0; }
 int tbk_check_status(tbk_forest *f) {
   if (!f) return fail(TBK_ERR_INVALID, "null forest");
   return check_status(f);
+}
+
+int tbk_debug_expire_next_wait(tbk_forest *f) {
+  if (!f) return fail(TBK_ERR_INVALID, "null forest");
+  std::lock_guard<std::mutex> lock(f->mu);
+  f->expire_next_wait = true;
+  return TBK_OK;
 }
 
 } // extern "C"

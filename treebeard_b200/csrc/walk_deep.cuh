@@ -46,6 +46,8 @@ struct DeepParams {
   uint32_t key_stride; // bytes per feature in the key tile: 64 * (row warps rounded up to even)
   int32_t *status;
   unsigned long long *tie_count;
+  int32_t skip_first_copy; // failure drill: the first piece's copy is never issued, so its wait expires
+  uint32_t wait_tries;     // polls before a wait gives up (0 = kQWaitTries)
 };
 
 constexpr int kDeepMaxSlots = 8;
@@ -153,7 +155,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
     mbar_expect_tx(bar, gm.slots * 4u);
     bulk_g2s(ring + (size_t)slot * p.slot_bytes, p.node_plane + off, gm.slots * 4u, bar);
   };
-  if (lane == 0 && warp < S && warp < P) issue(warp, warp);
+  if (lane == 0 && warp < S && warp < P && !(p.skip_first_copy && warp == 0)) issue(warp, warp);
   if (RW < S && tid == 0)
     for (int i = RW; i < S && i < P; ++i) issue(i, i);
 
@@ -193,7 +195,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
   const uint32_t full_s = smem_u32(full);
   auto take = [&](int *slot_out) -> uint32_t {
     const int s = slot;
-    if (ok) ok = mbar_wait_all_lanes(full_s + 8u * (uint32_t)s, parity);
+    if (ok) ok = mbar_wait_all_lanes(full_s + 8u * (uint32_t)s, parity, p.wait_tries ? p.wait_tries : kQWaitTries);
     *slot_out = s;
     if (++slot == S) {
       slot = 0;

@@ -66,6 +66,8 @@ struct WalkParams {
   int32_t vec4_ok;      // rows can be read with 16-byte loads
   int32_t class_regs;   // multiclass: class sums in registers, arg-max decided on the fly
   int32_t *status;      // device status word, 0 = ok
+  uint32_t wait_limit;  // polls before a wait on a stage gives up (0 = kWaitLimit)
+  int32_t skip_first_copy; // failure drill: the first stage's copy is never issued, so its wait expires
 };
 
 constexpr int kCols = 16;
@@ -94,8 +96,8 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: gives up after kWaitLimit polls instead of spinning for ever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = kWaitLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_test(bar, parity)) return true;
     if (it > 64) __nanosleep(64);
   }
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_kernel(const WalkParams p) {
   __syncthreads();
 
   if (STAGED && tid == 0) {
-    for (int s = 0; s < 2 && g0 + s < g1; ++s) {
+    for (int s = p.skip_first_copy ? 1 : 0; s < 2 && g0 + s < g1; ++s) {
       const DevGroupMeta gm = p.groups[g0 + s];
       const uint32_t bytes = (gm.slots * kCols * (REP == 2 ? 6u : (uint32_t)(TS == 1 ? 8 : TS == 2 ? 16 : TS == 3 ? 24 : 32)) + 15u) & ~15u;
       mbar_expect_tx(&mbar[s], bytes);
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(1024, 1) tb_walk_kernel(const WalkParams p) {
     if (STAGED) {
       const int s = (g - g0) & 1;
       const uint32_t parity = ((g - g0) >> 1) & 1;
-      const bool ok = mbar_wait_bounded(&mbar[s], parity);
+      const bool ok = mbar_wait_bounded(&mbar[s], parity, p.wait_limit ? p.wait_limit : kWaitLimit);
       if (__syncthreads_or(!ok)) {
         if (tid == 0) atomicExch(p.status, 4);
         return;

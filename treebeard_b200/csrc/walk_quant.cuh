@@ -66,7 +66,8 @@ struct QuantParams {
   int32_t num_groups, groups_per_chunk, num_features, transform;
   float initial_value;
   int32_t vec4_ok;
-  int32_t meta_bytes;            // unused (kept for the layout of the parameter block)
+  int32_t skip_first_copy;       // failure drill: the first piece's copy is never issued, so its wait expires
+  uint32_t wait_tries;           // polls before a wait gives up (0 = kQWaitTries)
   int32_t *status;
   unsigned long long *tie_count; // optional statistics
 };
@@ -110,8 +111,8 @@ __device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v));
 }
 // Bounded wait executed by every lane of the calling warp (no election, no shuffle).
-__device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t parity) {
-  for (uint32_t it = 0; it < kQWaitTries; ++it) {
+__device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t parity, uint32_t tries = kQWaitTries) {
+  for (uint32_t it = 0; it < tries; ++it) {
     uint32_t ok;
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
                  " selp.u32 %0, 1, 0, p;\n}"
@@ -435,6 +436,10 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
   bool ok = true;
   unsigned tie_count = 0;
   const uint64_t keep = l2_policy_keep(), stream = l2_policy_stream();
+  const uint32_t wait_tries = p.wait_tries ? p.wait_tries : kQWaitTries;
+  auto mbar_wait_all_lanes = [wait_tries](uint32_t bar_addr, uint32_t parity) {
+    return tb::mbar_wait_all_lanes(bar_addr, parity, wait_tries);
+  };
   // Copy of piece `piece` of a tile (upper levels of group piece/2 of the set for even
   // numbers, its bottom level for odd ones) into ring slot `slot` of the set.
   auto issue = [&](int piece, int slot) {
@@ -569,7 +574,7 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
     for (int it = 0; it < my_tiles && ok; ++it) {
       for (int piece = 0; piece < P && ok; ++piece) {
         if (round > 0) ok = mbar_wait_all_lanes(empty_s + 8u * (uint32_t)slot, (round - 1u) & 1u);
-        if (ok && lane == 0) issue(piece, slot);
+        if (ok && lane == 0 && !(p.skip_first_copy && it == 0 && piece == 0)) issue(piece, slot);
         if (++slot == 3) {
           slot = 0;
           ++round;

@@ -73,6 +73,7 @@ def lib():
         L.tbk_launch_count.argtypes = [vp]
         L.tbk_launch_count.restype = i64
         L.tbk_check_status.argtypes = [vp]
+        L.tbk_debug_expire_next_wait.argtypes = [vp]
         L.tbk_host_layout_check.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp]
         L.tbk_plan_launch.argtypes = [i32, i32, i64, i64, i32, vp, i64, i32, i32, i32, vp]
         _bound = True
@@ -207,6 +208,10 @@ class DeviceForest:
 
     def check_status(self):
         _check(lib().tbk_check_status(self._h))
+
+    def expire_next_wait(self):
+        """Failure drill: the next launch's first stage copy is skipped, its wait gives up."""
+        _check(lib().tbk_debug_expire_next_wait(self._h))
 
     def set_timing(self, on: bool):
         _check(lib().tbk_set_timing(self._h, 1 if on else 0))
