@@ -114,6 +114,28 @@ typedef struct tbk_forest_info {
 TBK_EXPORT int tbk_forest_create(const tbk_forest_arrays *forest, const tbk_schedule *schedule,
                                  int32_t device, int64_t batch_hint, tbk_forest **out);
 
+/* The two halves of tbk_forest_create.  An image is the packed forest in host memory: the
+ * layout chosen for it and that layout's buffers (what the reference's serializers build with
+ * the host-side lowering of src/utils/TreeTilingUtils.cpp:427-556 before Init_* uploads them).
+ * tbk_image_create needs no device: smem_limit is the shared memory per block the layout is
+ * chosen for (0 = 227 KB, the B200 figure).  An image can be turned into bytes and back, which
+ * is what a compiled-model file caches (the reference reloads its serialized buffers the same
+ * way: src/utils/TreeTilingUtils.cpp:95-170, src/runtime/runtime.cpp:35-54); stale or damaged
+ * bytes are refused with TBK_ERR_IO.  tbk_image_matches tells whether an image was packed for
+ * the same layout request (representation, tile size, feature bits of `schedule`; shared-memory
+ * limit) and may therefore stand in for a fresh pack.  tbk_forest_create_from_image uploads it;
+ * of `schedule` it takes the launch-shape fields, the layout is the image's. */
+typedef struct tbk_image tbk_image;
+TBK_EXPORT int tbk_image_create(const tbk_forest_arrays *forest, const tbk_schedule *schedule,
+                                int32_t smem_limit, tbk_image **out);
+TBK_EXPORT int tbk_image_free(tbk_image *image);
+/* buffer == NULL: only *size is set */
+TBK_EXPORT int tbk_image_serialize(const tbk_image *image, void *buffer, uint64_t capacity, uint64_t *size);
+TBK_EXPORT int tbk_image_deserialize(const void *buffer, uint64_t size, tbk_image **out);
+TBK_EXPORT int tbk_image_matches(const tbk_image *image, const tbk_schedule *schedule, int32_t smem_limit);
+TBK_EXPORT int tbk_forest_create_from_image(const tbk_image *image, const tbk_schedule *schedule,
+                                            int32_t device, int64_t batch_hint, tbk_forest **out);
+
 /* Frees the device buffers (Dealloc_Buffers, src/gpu/GPUModelSerializers.cpp:231-262). */
 TBK_EXPORT int tbk_forest_free(tbk_forest *forest);
 

@@ -185,6 +185,9 @@ TREEBEARD_RUNTIME_EXPORT void TB_FreeForest(intptr_t forest);
 /* Width in bits of the input element / result element types of a runner
  * (GetInputTypeBitWidth / GetReturnTypeBitWidth of the generated module,
  * src/json/forestcreator.h:307-313). */
+/* 1 if the runner was built from the packed image cached in a compiled-model file (the packer
+ * did not run), 0 if the forest was packed afresh. */
+TREEBEARD_RUNTIME_EXPORT int32_t TB_RunnerUsedPackedImage(intptr_t inferenceRunner);
 TREEBEARD_RUNTIME_EXPORT int32_t TB_GetInputTypeBitWidth(intptr_t inferenceRunner);
 TREEBEARD_RUNTIME_EXPORT int32_t TB_GetReturnTypeBitWidth(intptr_t inferenceRunner);
 

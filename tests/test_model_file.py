@@ -47,7 +47,7 @@ def test_model_file_rejects_damage(tmp_path):
     blob = open(out, "rb").read()
     cases = {
         "bad magic": b"NOTAFILE" + blob[8:],
-        "truncated": blob[: len(blob) // 2],
+        "truncated": blob[:1000],                         # inside the forest arrays
         "flipped byte": blob[:200] + bytes([blob[200] ^ 0x40]) + blob[201:],
         "trailing bytes": blob + b"\0" * 8,
         "empty": b"",
@@ -97,3 +97,74 @@ def test_runner_from_model_file_matches_direct_runner(name, tmp_path):
     assert runner2.batchSize == 128
     got2 = runner2.RunInference(X[:128], kind)
     assert_predictions_close(got2, want[:128], forest, sums[:128] if sums is not None else None)
+
+
+# ---- the packed image that a compiled-model file caches
+
+
+@pytest.mark.parametrize("name,layout", [("c2", dict(representation="sparse", tile_size=2)),
+                                         ("c4", dict(representation="array")),
+                                         ("c3", dict(representation="auto")),
+                                         ("c5", dict(representation="auto"))])
+def test_packed_image_survives_serialisation(name, layout):
+    """Host only: pack, serialise, read back, serialise again -- same bytes; a changed layout
+    request or shared-memory limit does not match; damaged bytes are refused."""
+    from treebeard_b200 import kernels
+    forest, _ = small_config(name)
+    image = kernels.PackedImage.pack(forest, **layout)
+    data = image.to_bytes()
+    again = kernels.PackedImage.from_bytes(data)
+    assert again.to_bytes() == data
+    assert again.matches(**layout)
+    assert not again.matches(**dict(layout, tile_size=3))
+    assert not again.matches(smem_limit=100 * 1024, **layout)
+    for bad in (data[:-9], data[:100] + bytes([data[100] ^ 1]) + data[101:], b"", data + b"\0"):
+        with pytest.raises(kernels.TbkError):
+            kernels.PackedImage.from_bytes(bad)
+
+
+def test_model_file_with_damaged_image_section_still_loads(tmp_path):
+    """The forest arrays have their own checksum: a packed-image section that is cut short or
+    altered costs only the shortcut (the loader packs again), never the model."""
+    forest, X, out, _ = _write(tmp_path)
+    blob = open(out, "rb").read()
+    bare = treebeard.LoadForest(out, "compiled_model")
+    marker = blob.index(b"TBB2SEC1")
+    assert marker > 0 and len(blob) - marker > 1000       # the file does carry an image
+    for what, data in {"cut short": blob[: marker + 500], "no section": blob[:marker],
+                       "altered": blob[: marker + 300] + bytes([blob[marker + 300] ^ 0x10]) + blob[marker + 301:]}.items():
+        path = str(tmp_path / "cut.tbmodel")
+        open(path, "wb").write(data)
+        back = treebeard.LoadForest(path, "compiled_model")
+        assert np.array_equal(back.thr, bare.thr) and np.array_equal(back.left, bare.left), what
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["c2", "c3", "c5"])
+def test_runner_from_model_file_uses_the_packed_image(name, tmp_path):
+    trees = {"c2": 52, "c3": 40, "c5": 12}[name]
+    forest, X, out, glob = _write(tmp_path, name=name, trees=trees, batch=256)
+    g = json.load(open(glob))
+    g["Representation"] = "gpu_auto"                      # wide rows / deep trees pick their key layouts
+    json.dump(g, open(glob, "w"))
+    want = oracle.predict(forest, X)
+    # written for the process default representation: the request differs, so the forest is packed again
+    runner = treebeard.TreebeardInferenceRunner.FromSOFile(out, glob)
+    assert not runner.used_packed_image()
+    assert_predictions_close(runner.RunInference(X), want)
+    # written for the same request: the image is uploaded as it is
+    model = str(tmp_path / "m.json")
+    ctx = treebeard.TreebeardContext(model, glob, treebeard.CompilerOptions(256, 1))
+    ctx.SetRepresentationType("gpu_auto")
+    out2 = str(tmp_path / "auto.tbmodel")
+    ctx.DumpLLVMIR(out2)
+    cached = treebeard.TreebeardInferenceRunner.FromSOFile(out2, "")
+    assert cached.used_packed_image()
+    assert_predictions_close(cached.RunInference(X), want)
+    # an altered image is dropped, the result stays right
+    blob = open(out2, "rb").read()
+    k = blob.index(b"TBB2SEC1") + 4000
+    open(out2, "wb").write(blob[:k] + bytes([blob[k] ^ 0x20]) + blob[k + 1:])
+    fallback = treebeard.TreebeardInferenceRunner.FromSOFile(out2, "")
+    assert not fallback.used_packed_image()
+    assert_predictions_close(fallback.RunInference(X), want)

@@ -12,6 +12,7 @@ namespace tb {
 namespace {
 
 const char kMagic[8] = {'T', 'B', 'B', '2', 'M', 'D', 'L', '\0'};
+const char kImageSection[8] = {'T', 'B', 'B', '2', 'S', 'E', 'C', '1'}; // opens the optional packed-image section
 
 // FNV-1a over the payload: catches truncated or edited files, not an integrity guarantee
 uint64_t fnv1a(uint64_t h, const void *data, size_t n) {
@@ -109,7 +110,8 @@ void ints_to_options(const int32_t *v, ModelFileOptions *o) {
 
 } // namespace
 
-std::string save_model_file(const std::string &path, const Forest &f, const ModelFileOptions &o) {
+std::string save_model_file(const std::string &path, const Forest &f, const ModelFileOptions &o,
+                            const std::vector<uint8_t> *image) {
   std::string err = validate(f);
   if (!err.empty()) return err;
   std::FILE *fp = std::fopen(path.c_str(), "wb");
@@ -134,6 +136,12 @@ std::string save_model_file(const std::string &path, const Forest &f, const Mode
   w.vec(f.class_id);
   const uint64_t sum = w.hash;
   if (std::fwrite(&sum, 1, sizeof(sum), fp) != sizeof(sum)) w.ok = false;
+  if (image && !image->empty()) { // after the checksum: a damaged image must not spoil the forest
+    const uint64_t n = image->size();
+    if (std::fwrite(kImageSection, 1, sizeof(kImageSection), fp) != sizeof(kImageSection) ||
+        std::fwrite(&n, 1, sizeof(n), fp) != sizeof(n) || std::fwrite(image->data(), 1, n, fp) != n)
+      w.ok = false;
+  }
   if (std::fclose(fp) != 0) w.ok = false;
   if (!w.ok) {
     std::remove(path.c_str());
@@ -142,7 +150,8 @@ std::string save_model_file(const std::string &path, const Forest &f, const Mode
   return "";
 }
 
-std::string load_model_file(const std::string &path, Forest *f, ModelFileOptions *o) {
+std::string load_model_file(const std::string &path, Forest *f, ModelFileOptions *o, std::vector<uint8_t> *image) {
+  if (image) image->clear();
   std::FILE *fp = std::fopen(path.c_str(), "rb");
   if (!fp) return "cannot open \"" + path + "\"";
   std::fseek(fp, 0, SEEK_END);
@@ -153,7 +162,7 @@ std::string load_model_file(const std::string &path, Forest *f, ModelFileOptions
     return "\"" + path + "\" is not a compiled-model file (too short)";
   }
   Reader r{fp};
-  r.remaining = (uint64_t)size - sizeof(uint64_t); // the checksum trails the payload
+  r.remaining = (uint64_t)size; // (the checksum trails the payload; an image section may follow it)
   char magic[sizeof(kMagic)];
   r.raw(magic, sizeof(magic));
   if (!r.ok || std::memcmp(magic, kMagic, sizeof(kMagic)) != 0) {
@@ -182,7 +191,26 @@ std::string load_model_file(const std::string &path, Forest *f, ModelFileOptions
   r.vec(&f->thr);
   r.vec(&f->class_id);
   uint64_t sum = 0;
-  const bool tail = r.ok && r.remaining == 0 && std::fread(&sum, 1, sizeof(sum), fp) == sizeof(sum);
+  bool tail = r.ok && r.remaining >= sizeof(sum) && std::fread(&sum, 1, sizeof(sum), fp) == sizeof(sum);
+  uint64_t rest = tail ? r.remaining - sizeof(sum) : 0;
+  if (tail && rest > 0) {
+    // only a packed-image section may follow; a section that is cut short is dropped (the
+    // forest arrays above are complete), anything else is a damaged file
+    char tag[sizeof(kImageSection)];
+    uint64_t n = 0;
+    if (rest < sizeof(tag) + sizeof(n) || std::fread(tag, 1, sizeof(tag), fp) != sizeof(tag) ||
+        std::memcmp(tag, kImageSection, sizeof(tag)) != 0 || std::fread(&n, 1, sizeof(n), fp) != sizeof(n)) {
+      tail = false;
+    } else {
+      rest -= sizeof(tag) + sizeof(n);
+      if (n == rest && image) {
+        image->resize(n);
+        if (std::fread(image->data(), 1, n, fp) != n) image->clear();
+      } else if (n < rest) {
+        tail = false; // bytes behind the section
+      }
+    }
+  }
   std::fclose(fp);
   if (!tail) return "\"" + path + "\" is truncated or has trailing bytes";
   if (sum != r.hash) return "\"" + path + "\": checksum mismatch";

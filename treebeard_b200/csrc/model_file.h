@@ -8,7 +8,11 @@
 // InitializeInferenceRunner(soPath, globalsJSONPath) (src/runtime/runtime.cpp:35-54).
 // Here the pair is
 //   * the MODEL FILE (binary, little endian): header, bound options, forest arrays in the
-//     model's own node numbering (so leaf ids stay those of the model file), checksum;
+//     model's own node numbering (so leaf ids stay those of the model file), checksum; then,
+//     optionally, the PACKED IMAGE of the forest (packed_image.h: the layout chosen for the
+//     bound options and its buffers, ready for upload, with a checksum of its own), so that
+//     loading skips the packer.  A loader that finds the image stale or damaged drops it and
+//     packs the forest arrays again;
 //   * the GLOBALS JSON (text): the bound options again, readable and editable; when it is
 //     given to the loader its values replace those of the model file, which is how a tuned
 //     launch shape or another batch size is applied without rewriting the binary.
@@ -17,6 +21,7 @@
 
 #include <cstdint>
 #include <string>
+#include <vector>
 
 namespace tb {
 
@@ -34,9 +39,13 @@ struct ModelFileOptions {
 
 constexpr uint32_t kModelFileVersion = 1;
 
-// Each returns an empty string on success, else the reason.
-std::string save_model_file(const std::string &path, const Forest &f, const ModelFileOptions &o);
-std::string load_model_file(const std::string &path, Forest *f, ModelFileOptions *o);
+// Each returns an empty string on success, else the reason.  `image`: the serialised packed
+// image to append (may be null or empty) / where to put the one found (may be null; left
+// empty when the file has none or its section is cut short).
+std::string save_model_file(const std::string &path, const Forest &f, const ModelFileOptions &o,
+                            const std::vector<uint8_t> *image = nullptr);
+std::string load_model_file(const std::string &path, Forest *f, ModelFileOptions *o,
+                            std::vector<uint8_t> *image = nullptr);
 
 std::string save_globals_json(const std::string &path, const Forest &f, const ModelFileOptions &o);
 // Overwrites the fields of *o that the JSON names.

@@ -125,6 +125,7 @@ struct InferenceRunner {
   bool returnFloat = true;
   int32_t numClasses = 0;
   int32_t device = 0;
+  bool fromPackedImage = false; // built from the packed image of a compiled-model file
   int64_t kernelMicros = 0;
 };
 
@@ -157,8 +158,13 @@ bool load_forest(const std::string &creator, const std::string &path, tb::Forest
   return true;
 }
 
+// cached_image: serialised packed image found in a compiled-model file (may be null).
+// save_image: when given, nothing is uploaded: the forest is packed for these options and the
+// serialised image is left there (the return value is null; failures are in the error state).
 InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &opt,
-                              const GPUAutoScheduleOptions *gpu, const std::string &repName) {
+                              const GPUAutoScheduleOptions *gpu, const std::string &repName,
+                              const std::vector<uint8_t> *cached_image = nullptr,
+                              std::vector<uint8_t> *save_image = nullptr) {
   if (opt.batchSize <= 0) {
     set_error(TBK_ERR_INVALID, "batch size must be positive");
     return nullptr;
@@ -208,7 +214,45 @@ InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &o
   fa.num_features = opt.numberOfFeatures > 0 ? std::max(opt.numberOfFeatures, forest.num_features)
                                               : forest.num_features;
   tbk_forest *kf = nullptr;
-  const int rc = tbk_forest_create(&fa, &sched, g_device, opt.batchSize, &kf);
+  int rc = TBK_OK;
+  if (save_image) {
+    // ahead-of-time use: pack only (no device is needed) and hand the bytes back
+    int smem_limit = 0;
+    if (cudaDeviceGetAttribute(&smem_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, g_device) != cudaSuccess) {
+      cudaGetLastError();
+      smem_limit = 0; // no device here: the B200 figure
+    }
+    tbk_image *img = nullptr;
+    rc = tbk_image_create(&fa, &sched, smem_limit, &img);
+    if (rc == TBK_OK) {
+      uint64_t n = 0;
+      rc = tbk_image_serialize(img, nullptr, 0, &n);
+      if (rc == TBK_OK) {
+        save_image->resize(n);
+        rc = tbk_image_serialize(img, save_image->data(), n, &n);
+      }
+      tbk_image_free(img);
+    }
+    if (rc != TBK_OK) set_error(rc, tbk_last_error());
+    return nullptr;
+  }
+  bool from_image = false;
+  if (cached_image && !cached_image->empty()) {
+    // a compiled-model file brought its packed image along: use it if it was packed for this
+    // very layout request on a device like this one, else fall back to packing the arrays
+    int smem_limit = 0;
+    tbk_image *img = nullptr;
+    if (cudaDeviceGetAttribute(&smem_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, g_device) == cudaSuccess &&
+        tbk_image_deserialize(cached_image->data(), cached_image->size(), &img) == TBK_OK) {
+      if (tbk_image_matches(img, &sched, smem_limit)) {
+        rc = tbk_forest_create_from_image(img, &sched, g_device, opt.batchSize, &kf);
+        from_image = rc == TBK_OK;
+      }
+      tbk_image_free(img);
+    }
+    cudaGetLastError();
+  }
+  if (!from_image) rc = tbk_forest_create(&fa, &sched, g_device, opt.batchSize, &kf);
   if (rc != TBK_OK) {
     set_error(rc, tbk_last_error());
     return nullptr;
@@ -222,6 +266,7 @@ InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &o
   r->returnFloat = opt.returnTypeFloatType;
   r->numClasses = forest.num_classes;
   r->device = g_device;
+  r->fromPackedImage = from_image;
   if (g_measure_kernel_time) tbk_set_timing(kf, 1);
   return r;
 }
@@ -289,7 +334,16 @@ bool write_compiled_model(const tb::Forest &forest, const CompilerOptions &opt, 
     return false;
   }
   const tb::ModelFileOptions m = to_file_options(opt, gpu, repName);
-  std::string err = tb::save_model_file(modelFilePath, forest, m);
+  // the packed image for the bound options travels with the forest, so that loading the file
+  // skips the packer; if packing fails here the file is written without it
+  std::vector<uint8_t> image;
+  clear_error();
+  build_runner(forest, opt, gpu, repName, nullptr, &image);
+  if (g_status != TBK_OK) {
+    image.clear();
+    clear_error();
+  }
+  std::string err = tb::save_model_file(modelFilePath, forest, m, &image);
   if (err.empty() && globalsPath && *globalsPath) err = tb::save_globals_json(globalsPath, forest, m);
   if (!err.empty()) {
     set_error(TBK_ERR_IO, err);
@@ -385,7 +439,8 @@ intptr_t InitializeInferenceRunner(const char *modelFilePath, const char *modelG
   }
   tb::Forest forest;
   tb::ModelFileOptions m;
-  std::string err = tb::load_model_file(modelFilePath, &forest, &m);
+  std::vector<uint8_t> image;
+  std::string err = tb::load_model_file(modelFilePath, &forest, &m, &image);
   if (err.empty() && modelGlobalsJSONPath && *modelGlobalsJSONPath) err = tb::load_globals_json(modelGlobalsJSONPath, &m);
   if (!err.empty()) {
     set_error(TBK_ERR_IO, err);
@@ -394,7 +449,7 @@ intptr_t InitializeInferenceRunner(const char *modelFilePath, const char *modelG
   CompilerOptions opt;
   GPUAutoScheduleOptions gpu;
   from_file_options(m, &opt, &gpu);
-  return reinterpret_cast<intptr_t>(build_runner(forest, opt, m.has_gpu_options ? &gpu : nullptr, m.representation));
+  return reinterpret_cast<intptr_t>(build_runner(forest, opt, m.has_gpu_options ? &gpu : nullptr, m.representation, &image));
 }
 
 void RunInference(intptr_t runner, void *inputs, void *results) {
@@ -435,6 +490,10 @@ void DeleteInferenceRunner(intptr_t runner) {
   if (!r) return;
   tbk_forest_free(r->forest);
   delete r;
+}
+int32_t TB_RunnerUsedPackedImage(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  return r && r->fromPackedImage ? 1 : 0;
 }
 void *TB_GetKernelForest(intptr_t runner) {
   auto *r = reinterpret_cast<InferenceRunner *>(runner);

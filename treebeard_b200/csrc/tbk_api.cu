@@ -8,11 +8,13 @@
 #include "walk_kernels.cuh"
 #include "walk_quant.cuh"
 #include "walk_deep.cuh"
+#include "packed_image.h"
 
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -40,6 +42,10 @@ int fail(int code, const char *fmt, ...) {
   } while (0)
 
 } // namespace
+
+struct tbk_image {
+  tb::PackedImage im;
+};
 
 struct tbk_forest {
   tb::PackedForest packed; // host copy (orig_node kept for lazy upload)
@@ -593,6 +599,20 @@ const char *tbk_last_error(void) { return g_last_error.c_str(); }
 
 int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, int32_t device,
                       int64_t batch_hint, tbk_forest **out) {
+  if (!out) return fail(TBK_ERR_INVALID, "null argument");
+  *out = nullptr;
+  int smem_limit = 0;
+  CUDA_TRY(cudaSetDevice(device));
+  CUDA_TRY(cudaDeviceGetAttribute(&smem_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  tbk_image *img = nullptr;
+  int rc = tbk_image_create(fa, schedule, smem_limit, &img);
+  if (rc != TBK_OK) return rc;
+  rc = tbk_forest_create_from_image(img, schedule, device, batch_hint, out);
+  tbk_image_free(img);
+  return rc;
+}
+
+int tbk_image_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, int32_t smem_limit, tbk_image **out) {
   if (!fa || !out) return fail(TBK_ERR_INVALID, "null argument");
   *out = nullptr;
   if (fa->num_trees <= 0 || !fa->tree_off || !fa->left || !fa->right || !fa->feat || !fa->thr)
@@ -614,9 +634,141 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
   host.initial_value = fa->initial_value;
   host.num_features = fa->num_features;
   if (fa->num_classes > 0 && fa->num_classes > 127) return fail(TBK_ERR_UNSUPPORTED, "more than 127 classes");
+  if (smem_limit <= 0) smem_limit = 227 * 1024;
 
+  std::unique_ptr<tbk_image> img(new tbk_image());
+  tb::PackedImage &im = img->im;
+  if (schedule) im.user = *schedule;
+  im.smem_limit = smem_limit;
+
+  // ---- choose the layout
+  const int bits = im.user.feature_bits;
+  if (bits != 0 && bits != 16 && bits != 32) return fail(TBK_ERR_INVALID, "feature_bits must be 0, 16 or 32");
+  int rep = im.user.representation;
+  const int ts = im.user.tile_size <= 0 ? 1 : im.user.tile_size;
+  im.requested_representation = rep;
+  im.requested_tile_size = ts;
+  im.requested_feature_bits = bits;
+  // an fp32 tile of 32 rows (plus the sentinel column) must fit beside a little metadata
+  const bool fp32_tile_fits = (int64_t)(host.num_features + 1) * 128 + 1024 <= smem_limit;
+  {
+    const std::string verr = tb::validate(host);
+    if (!verr.empty()) return fail(TBK_ERR_INVALID, "%s", verr.c_str());
+  }
+  int max_depth = 0;
+#pragma omp parallel for reduction(max : max_depth) schedule(dynamic, 64) num_threads(tb::pack_threads())
+  for (int64_t t = 0; t < T; ++t) max_depth = std::max(max_depth, (int)tb::tree_depth(host, t));
+  bool want_quant = (bits == 16 && max_depth <= tb::kQuantMaxDepth) ||
+                    (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits);
+  if (want_quant) {
+    std::string qerr = tb::pack_quant(host, &im.qf);
+    if (qerr.empty() && quant_smem_bytes(host.num_features) > smem_limit)
+      qerr = "rows are too wide for the 16-bit key tile";
+    if (qerr.empty() && im.qf.node_plane.size() >= (1ull << 32))
+      qerr = "forest too large for the 16-bit key layout (2^32 plane elements)";
+    if (!qerr.empty()) {
+      if (bits == 16) return fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str());
+      want_quant = false;
+      im.qf = tb::QuantForest();
+    }
+  }
+  // ---- deep trees: whole-tree stages over a key tile (deep_pack.h)
+  if (!want_quant && host.num_classes == 0 && ts == 1 && bits != 32 &&
+      (bits == 16 || im.user.representation == TBK_REP_AUTO)) {
+    int rw = 0, slots = 0;
+    const bool fits = max_depth > tb::kQuantMaxDepth && max_depth <= tb::kDeepMaxDepth &&
+                      deep_plan(host.num_features, max_depth, smem_limit, &rw, &slots);
+    if (fits) {
+      std::string derr = tb::pack_deep(host, &im.df);
+      if (derr.empty()) {
+        im.kind = tb::PackedImage::kDeep;
+        im.deep_row_warps = rw;
+        im.deep_slots = slots;
+        im.user.representation = TBK_REP_REORG;
+        *out = img.release();
+        return TBK_OK;
+      }
+      if (bits == 16) return fail(TBK_ERR_UNSUPPORTED, "%s", derr.c_str());
+      im.df = tb::DeepForest();
+    } else if (bits == 16) {
+      return fail(TBK_ERR_UNSUPPORTED, "16-bit feature keys: neither key layout fits this forest (depth %d, %d features)",
+                  max_depth, host.num_features);
+    }
+  }
+  if (bits == 16 && !want_quant)
+    return fail(TBK_ERR_UNSUPPORTED, "16-bit feature keys cover single-output forests of at most %d levels, tile size 1 "
+                                     "(this forest: %d levels, %d classes, tile size %d)",
+                tb::kDeepMaxDepth, max_depth, host.num_classes, ts);
+  if (rep == TBK_REP_AUTO) rep = TBK_REP_SPARSE;
+  if (want_quant) {
+    im.kind = tb::PackedImage::kQuant;
+    im.user.representation = TBK_REP_REORG;
+    *out = img.release();
+    return TBK_OK;
+  }
+  tb::PackOptions opt;
+  opt.representation = rep;
+  opt.tile_size = ts;
+  im.user.representation = rep;
+  std::string err = tb::pack_forest(host, opt, &im.packed);
+  if (!err.empty()) return fail(TBK_ERR_INVALID, "%s", err.c_str());
+  im.kind = tb::PackedImage::kGeneral;
+  *out = img.release();
+  return TBK_OK;
+}
+
+int tbk_image_free(tbk_image *img) {
+  delete img;
+  return TBK_OK;
+}
+
+int tbk_image_serialize(const tbk_image *img, void *buffer, uint64_t capacity, uint64_t *size) {
+  if (!img || !size) return fail(TBK_ERR_INVALID, "null argument");
+  std::vector<uint8_t> bytes;
+  tb::serialize_image(img->im, &bytes);
+  *size = bytes.size();
+  if (!buffer) return TBK_OK;
+  if (capacity < bytes.size()) return fail(TBK_ERR_INVALID, "buffer of %llu bytes, the image needs %llu",
+                                           (unsigned long long)capacity, (unsigned long long)bytes.size());
+  std::memcpy(buffer, bytes.data(), bytes.size());
+  return TBK_OK;
+}
+
+int tbk_image_deserialize(const void *buffer, uint64_t size, tbk_image **out) {
+  if (!buffer || !out) return fail(TBK_ERR_INVALID, "null argument");
+  *out = nullptr;
+  std::unique_ptr<tbk_image> img(new tbk_image());
+  const std::string err = tb::deserialize_image(static_cast<const uint8_t *>(buffer), size, &img->im);
+  if (!err.empty()) return fail(TBK_ERR_IO, "%s", err.c_str());
+  *out = img.release();
+  return TBK_OK;
+}
+
+int tbk_image_matches(const tbk_image *img, const tbk_schedule *schedule, int32_t smem_limit) {
+  if (!img) return 0;
+  tbk_schedule want{};
+  if (schedule) want = *schedule;
+  const tb::PackedImage &im = img->im;
+  const int ts = want.tile_size <= 0 ? 1 : want.tile_size;
+  if (smem_limit <= 0) smem_limit = 227 * 1024;
+  return im.requested_representation == want.representation && im.requested_tile_size == ts &&
+         im.requested_feature_bits == want.feature_bits && im.smem_limit == smem_limit;
+}
+
+int tbk_forest_create_from_image(const tbk_image *img, const tbk_schedule *schedule, int32_t device,
+                                 int64_t batch_hint, tbk_forest **out) {
+  if (!img || !out) return fail(TBK_ERR_INVALID, "null argument");
+  *out = nullptr;
+  const tb::PackedImage &im = img->im;
   auto *f = new tbk_forest();
-  if (schedule) f->user = *schedule;
+  f->user = im.user;
+  if (schedule) { // launch-shape requests of the caller; the layout is the image's
+    f->user.rows_per_block = schedule->rows_per_block;
+    f->user.rows_per_thread = schedule->rows_per_thread;
+    f->user.tree_threads = schedule->tree_threads;
+    f->user.tree_chunks = schedule->tree_chunks;
+    f->user.cache_trees = schedule->cache_trees;
+  }
   f->batch_hint = batch_hint;
   f->device = device;
   auto bail = [&](int rc) {
@@ -632,90 +784,45 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
   CUDA_TRY_F(cudaSetDevice(device));
   CUDA_TRY_F(cudaDeviceGetAttribute(&f->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
   CUDA_TRY_F(cudaDeviceGetAttribute(&f->num_sms, cudaDevAttrMultiProcessorCount, device));
+  if (im.smem_limit > f->max_smem_optin)
+    return bail(fail(TBK_ERR_UNSUPPORTED, "the packed image was laid out for %d bytes of shared memory per block, this device has %d",
+                     im.smem_limit, f->max_smem_optin));
   CUDA_TRY_F(cudaMalloc(&f->d_status, 4));
   CUDA_TRY_F(cudaMemset(f->d_status, 0, 4));
   CUDA_TRY_F(cudaEventCreate(&f->ev0));
   CUDA_TRY_F(cudaEventCreate(&f->ev1));
 
-  // ---- choose the layout
-  const int bits = f->user.feature_bits;
-  if (bits != 0 && bits != 16 && bits != 32) return bail(fail(TBK_ERR_INVALID, "feature_bits must be 0, 16 or 32"));
-  int rep = f->user.representation;
-  const int ts = f->user.tile_size <= 0 ? 1 : f->user.tile_size;
-  // an fp32 tile of 32 rows (plus the sentinel column) must fit beside a little metadata
-  const bool fp32_tile_fits = (int64_t)(host.num_features + 1) * 128 + 1024 <= f->max_smem_optin;
-  {
-    const std::string verr = tb::validate(host);
-    if (!verr.empty()) return bail(fail(TBK_ERR_INVALID, "%s", verr.c_str()));
+  if (im.kind == tb::PackedImage::kDeep) {
+    f->df = im.df; // (metadata and planes; the planes' host copies are dropped after the upload)
+    auto &q = f->df;
+    f->deep = true;
+    f->deep_row_warps = im.deep_row_warps;
+    f->deep_slots = im.deep_slots;
+    f->packed.representation = tb::kReorg;
+    f->packed.tile_size = 1;
+    f->packed.num_features = q.num_features;
+    f->packed.transform = q.transform;
+    f->packed.initial_value = q.initial_value;
+    f->packed.num_trees = q.num_trees;
+    f->packed.num_nodes = q.num_nodes;
+    f->packed.max_depth = q.max_depth;
+    int urc = upload_key_planes(f, q.node_plane, q.leaf_plane, q.exact_plane, q.orig_leaf, q.pairs, q.tree_index,
+                                q.lo, q.scale, q.num_features, false);
+    if (urc != TBK_OK) return bail(urc);
+    std::vector<uint32_t>().swap(q.node_plane);
+    std::vector<float>().swap(q.leaf_plane);
+    std::vector<float>().swap(q.exact_plane);
+    std::vector<int32_t>().swap(q.orig_leaf);
+    tb::LaunchPlan &pl = f->last_plan;
+    pl.row_warps = f->deep_row_warps; pl.tree_threads = 1; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
+    pl.stage_bytes = 4u << std::max(q.max_depth, tb::kDeepMinDepth); pl.smem_bytes = deep_smem_bytes(f); pl.threads = 32 * f->deep_row_warps;
+    *out = f;
+    return TBK_OK;
   }
-  int max_depth = 0;
-#pragma omp parallel for reduction(max : max_depth) schedule(dynamic, 64) num_threads(tb::pack_threads())
-  for (int64_t t = 0; t < T; ++t) max_depth = std::max(max_depth, (int)tb::tree_depth(host, t));
-  bool want_quant = (bits == 16 && max_depth <= tb::kQuantMaxDepth) ||
-                    (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits);
-  if (want_quant) {
-    std::string qerr = tb::pack_quant(host, &f->qf);
-    if (qerr.empty() && quant_smem_bytes(host.num_features) > f->max_smem_optin)
-      qerr = "rows are too wide for the 16-bit key tile";
-    if (qerr.empty() && f->qf.node_plane.size() >= (1ull << 32))
-      qerr = "forest too large for the 16-bit key layout (2^32 plane elements)";
-    if (!qerr.empty()) {
-      if (bits == 16) return bail(fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str()));
-      want_quant = false;
-      f->qf = tb::QuantForest();
-    }
-  }
-  // ---- deep trees: whole-tree stages over a key tile (deep_pack.h)
-  if (!want_quant && host.num_classes == 0 && ts == 1 && bits != 32 &&
-      (bits == 16 || f->user.representation == TBK_REP_AUTO)) {
-    int rw = 0, slots = 0;
-    const bool fits = max_depth > tb::kQuantMaxDepth && max_depth <= tb::kDeepMaxDepth &&
-                      deep_plan(host.num_features, max_depth, f->max_smem_optin, &rw, &slots);
-    if (fits) {
-      std::string derr = tb::pack_deep(host, &f->df);
-      if (derr.empty()) {
-        auto &q = f->df;
-        f->deep = true;
-        f->deep_row_warps = rw;
-        f->deep_slots = slots;
-        f->user.representation = TBK_REP_REORG;
-        f->packed.representation = tb::kReorg;
-        f->packed.tile_size = 1;
-        f->packed.num_features = q.num_features;
-        f->packed.transform = q.transform;
-        f->packed.initial_value = q.initial_value;
-        f->packed.num_trees = q.num_trees;
-        f->packed.num_nodes = q.num_nodes;
-        f->packed.max_depth = q.max_depth;
-        int urc = upload_key_planes(f, q.node_plane, q.leaf_plane, q.exact_plane, q.orig_leaf, q.pairs, q.tree_index,
-                                    q.lo, q.scale, q.num_features, false);
-        if (urc != TBK_OK) return bail(urc);
-        std::vector<uint32_t>().swap(q.node_plane);
-        std::vector<float>().swap(q.leaf_plane);
-        std::vector<float>().swap(q.exact_plane);
-        std::vector<int32_t>().swap(q.orig_leaf);
-        tb::LaunchPlan &pl = f->last_plan;
-        pl.row_warps = rw; pl.tree_threads = 1; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
-        pl.stage_bytes = 4u << std::max(q.max_depth, tb::kDeepMinDepth); pl.smem_bytes = deep_smem_bytes(f); pl.threads = 32 * rw;
-        *out = f;
-        return TBK_OK;
-      }
-      if (bits == 16) return bail(fail(TBK_ERR_UNSUPPORTED, "%s", derr.c_str()));
-      f->df = tb::DeepForest();
-    } else if (bits == 16) {
-      return bail(fail(TBK_ERR_UNSUPPORTED, "16-bit feature keys: neither key layout fits this forest (depth %d, %d features)",
-                       max_depth, host.num_features));
-    }
-  }
-  if (bits == 16 && !want_quant)
-    return bail(fail(TBK_ERR_UNSUPPORTED, "16-bit feature keys cover single-output forests of at most %d levels, tile size 1 "
-                                          "(this forest: %d levels, %d classes, tile size %d)",
-                     tb::kDeepMaxDepth, max_depth, host.num_classes, ts));
-  if (rep == TBK_REP_AUTO) rep = TBK_REP_SPARSE;
-  if (want_quant) {
+  if (im.kind == tb::PackedImage::kQuant) {
+    f->qf = im.qf;
     const auto &q = f->qf;
     f->quant = true;
-    f->user.representation = TBK_REP_REORG;
     // metadata shared with the generic entry points
     f->packed.representation = tb::kReorg;
     f->packed.tile_size = 1;
@@ -740,12 +847,7 @@ int tbk_forest_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule,
     return TBK_OK;
   }
 
-  tb::PackOptions opt;
-  opt.representation = rep;
-  opt.tile_size = ts;
-  f->user.representation = rep;
-  std::string err = tb::pack_forest(host, opt, &f->packed);
-  if (!err.empty()) return bail(fail(TBK_ERR_INVALID, "%s", err.c_str()));
+  f->packed = im.packed;
   const auto &p = f->packed;
   CUDA_TRY_F(cudaMalloc(&f->d_blob, std::max<size_t>(16, p.blob.size())));
   CUDA_TRY_F(cudaMemcpy(f->d_blob, p.blob.data(), p.blob.size(), cudaMemcpyHostToDevice));

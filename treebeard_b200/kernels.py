@@ -76,6 +76,13 @@ def lib():
         L.tbk_debug_expire_next_wait.argtypes = [vp]
         L.tbk_host_layout_check.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp]
         L.tbk_plan_launch.argtypes = [i32, i32, i64, i64, i32, vp, i64, i32, i32, i32, vp]
+        u64 = ctypes.c_uint64
+        L.tbk_image_create.argtypes = [vp, vp, i32, ctypes.POINTER(vp)]
+        L.tbk_image_free.argtypes = [vp]
+        L.tbk_image_serialize.argtypes = [vp, vp, u64, ctypes.POINTER(u64)]
+        L.tbk_image_deserialize.argtypes = [vp, u64, ctypes.POINTER(vp)]
+        L.tbk_image_matches.argtypes = [vp, vp, i32]
+        L.tbk_forest_create_from_image.argtypes = [vp, vp, i32, i64, ctypes.POINTER(vp)]
         _bound = True
     return L
 
@@ -221,6 +228,60 @@ class DeviceForest:
 
     def launch_count(self) -> int:
         return int(lib().tbk_launch_count(self._h))
+
+
+class PackedImage:
+    """A packed forest in host memory (tbk_image*): pack once, serialise, upload later."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    @classmethod
+    def pack(cls, forest, smem_limit: int = 0, **schedule):
+        c, keep = forest_arrays_c(forest)
+        sched = make_schedule(**schedule)
+        h = ctypes.c_void_p()
+        _check(lib().tbk_image_create(ctypes.byref(c), ctypes.byref(sched), smem_limit, ctypes.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def from_bytes(cls, data: bytes):
+        h = ctypes.c_void_p()
+        buf = (ctypes.c_char * len(data)).from_buffer_copy(data)
+        _check(lib().tbk_image_deserialize(buf, len(data), ctypes.byref(h)))
+        return cls(h)
+
+    def to_bytes(self) -> bytes:
+        n = ctypes.c_uint64()
+        _check(lib().tbk_image_serialize(self._h, None, 0, ctypes.byref(n)))
+        buf = (ctypes.c_char * n.value)()
+        _check(lib().tbk_image_serialize(self._h, buf, n.value, ctypes.byref(n)))
+        return bytes(buf)
+
+    def matches(self, smem_limit: int = 0, **schedule) -> bool:
+        sched = make_schedule(**schedule)
+        return bool(lib().tbk_image_matches(self._h, ctypes.byref(sched), smem_limit))
+
+    def upload(self, forest, device: int = 0, batch_hint: int = 0, **schedule) -> "DeviceForest":
+        """Uploads the image; `forest` only supplies the sizes the wrapper keeps."""
+        sched = make_schedule(**schedule)
+        h = ctypes.c_void_p()
+        _check(lib().tbk_forest_create_from_image(self._h, ctypes.byref(sched), device, batch_hint,
+                                                  ctypes.byref(h)))
+        df = DeviceForest.from_handle(h.value, device, forest.num_trees, int(forest.num_classes),
+                                      int(forest.num_features))
+        df._borrowed = False
+        return df
+
+    def close(self):
+        if getattr(self, "_h", None):
+            try:
+                lib().tbk_image_free(self._h)
+            except TypeError:
+                pass
+        self._h = None
+
+    __del__ = close
 
 
 def host_layout_check(forest, rows: Optional[np.ndarray], **schedule):

@@ -376,6 +376,10 @@ class TreebeardInferenceRunner:
                                                         results.ctypes.data, numRows)
         return results
 
+    def used_packed_image(self) -> bool:
+        """True if this runner was built from the packed image cached in a compiled-model file."""
+        return bool(_rt.TB_RunnerUsedPackedImage(self.inferenceRunner))
+
     def kernel_forest(self):
         """The kernel-level handle behind this runner (see kernels.DeviceForest)."""
         return int(_rt.TB_GetKernelForest(self.inferenceRunner) or 0)

@@ -85,6 +85,7 @@ _SIGNATURES = {
     "TB_LoadForest": ((_CP, _CP, _I32), _I64),
     "TB_ForestGetArrays": ((_I64, _VP), _I32),
     "TB_FreeForest": ((_I64,), None),
+    "TB_RunnerUsedPackedImage": ((_I64,), _I32),
     "TB_GetInputTypeBitWidth": ((_I64,), _I32),
     "TB_GetReturnTypeBitWidth": ((_I64,), _I32),
 }
