@@ -1,35 +1,44 @@
-// Walk kernel for the 16-bit-key layout (quant_pack.h): forests over rows too wide for
+// Walk kernel for the 15-bit-key layout (quant_pack.h): forests over rows too wide for
 // an fp32 row tile.
 //
-// One block = 32 warps = one tile of 32 rows, staged ONCE per block as 15-bit keys,
-// transposed and paired: line m of the key tile (128 bytes) holds, for row j in word j, the
-// keys of features 2m (low half) and 2m+1 (high half).  Lane = row, so a key load of a warp
-// touches 32 distinct banks whatever the features are.  The block works as TWO independent
-// halves of 16 warps: half h takes the groups h, h+2, ... of the chunk for all 32 rows; warp
-// w of a half walks, in every group of 32 trees, the columns (lane + w) mod 32 and
-// (lane + w + 16) mod 32 in lock-step, so the 32 lanes of a warp read 32 distinct columns
-// of the node plane (one shared-memory wavefront per load) and the half covers every
-// (row, tree) pair of the group exactly once.  While one half waits for a piece or sits in
-// its barrier, the other keeps the issue slots and the shared-memory pipe busy; the forest
-// is still streamed only once per 32-row tile.
+// A PERSISTENT block of 24 warps takes the 32-row tiles blockIdx.x, blockIdx.x + gridDim.x,
+// ... one after another and streams its tree chunk through shared memory once per tile.  A
+// tile is held as 15-bit keys, transposed and paired: line m of the key tile (128 bytes)
+// holds, for row j in word j, the keys of features 2m (low half) and 2m+1 (high half).
+// Lane = row, so a key load of a warp touches 32 distinct banks whatever the features are.
 //
-// Only the NODE planes stream through shared memory: two 16 KB pieces per group (upper
-// levels, bottom level) through a three-slot ring per half, filled by cp.async.bulk copies
-// that rotating warps issue; one named barrier per group frees the group's two slots.  The
-// leaf values are read straight from L2 (staging the leaf plane would move as many bytes
-// and take ring slots) and consumed one group later; the walkers first exchange their leaf
-// numbers through a small shared-memory table, so that a warp loads ONE tree's leaves for
-// all 32 rows (see fetch_leaves).  Per-row sums live in registers and are combined across
-// the 32 warps once, at the end.
+// The warps are specialised; they meet only at mbarriers, never at a block barrier:
+//  * 16 walkers in TWO independent sets of 8.  Set s takes the groups s, s+2, ... of the
+//    chunk for all 32 rows; warp w of a set walks, in every group of 32 trees, the four
+//    columns (lane + w + 8c) mod 32 in lock-step, so the 32 lanes of a warp read 32 distinct
+//    columns of the node plane (one shared-memory wavefront per load) and the set covers
+//    every (row, tree) pair of the group exactly once.  While one set waits for a piece, the
+//    other keeps the issue slots and the shared-memory pipe busy.
+//  * 2 ring producers, one per set.  Only the NODE planes stream through shared memory: two
+//    16 KB pieces per group (upper levels, bottom level) through the set's three-slot ring,
+//    filled by cp.async.bulk copies ("full" barriers); a walker warp releases a slot with one
+//    arrive on its "empty" barrier.
+//  * 2 leaf warps, one per set.  The walkers drop their leaf numbers into a small
+//    shared-memory table (two per set, alternating); the leaf warp turns a finished table
+//    into leaf-plane addresses, gathers the values straight from L2 one group ahead of their
+//    use, and keeps the per-row sums.  Leaf warp 1 hands its sums to leaf warp 0, which
+//    writes the tile's results.
+//  * 4 stagers, one per quarter of tensor memory.  While the walkers are busy with tile i
+//    they read the rows of tile i+1 (eight rows x 64 bytes per load instruction), turn
+//    them into paired keys and park them in tensor memory (tcgen05.st); at the end of a
+//    tile walkers and stagers together copy the parked keys into the key tile (tcgen05.ld,
+//    about a microsecond), so the walk never waits for row data.  The first tile of a block
+//    is staged by the walkers themselves; the rows of tile i+2 are prefetched into L2.
 //
-// The walk is fully unrolled per depth and written in PTX, both columns of a lane
+// The walk is fully unrolled per depth and written in PTX, the four columns of a lane
 // interleaved.  A level costs one key load, two half2 comparisons on the low halves of
 // (key, node word) -- "less than" picks the child, "equal" accumulates the tie flag -- one
 // shift-add, one predicated add and one node load; the key's address is the node word
 // shifted right by 15 plus the lane's base (bit 15 of a node word is 0, the feature code in
 // the upper half is the key's byte offset halved).  Key ties are only flagged on the fast
 // path; a flagged (row, tree) pair is then re-walked on the exact fp32 values from global
-// memory.  Every lane polls the stage barrier itself (mbarrier.try_wait, bounded).
+// memory.  Every lane polls its barrier itself (mbarrier.try_wait, bounded); a wait that
+// gives up ends the launch with status 4 after tensor memory has been released.
 //
 // Reference counterparts: the walk of src/mlir/CodeGenStateMachine.cpp:149-243 over the
 // reorg layout (src/gpu/ReorgForestRepresentation.cpp:495-571), the unrolled walk of
@@ -72,8 +81,8 @@ struct QuantParams {
   unsigned long long *tie_count; // optional statistics
 };
 
-constexpr int kQRingBytes = 6 * 16384; // two half-blocks x three 16 KB pieces
-constexpr int kQLeafTableBytes = 4096; // [2 halves][2 buffers][32 columns][32 rows] leaf numbers
+constexpr int kQRingBytes = 6 * 16384; // two walker sets x three 16 KB pieces
+constexpr int kQLeafTableBytes = 4096; // [2 sets][2 tables][32 columns][32 rows] leaf numbers
 constexpr uint32_t kQWaitTries = 1u << 20;
 
 // 16-bit keys of the deep-tree layout (walk_deep.cuh).
