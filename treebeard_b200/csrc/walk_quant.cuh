@@ -26,8 +26,8 @@
 //  * 4 stagers, one per quarter of tensor memory.  While the walkers are busy with tile i
 //    they read the rows of tile i+1 (eight rows x 64 bytes per load instruction), turn
 //    them into paired keys and park them in tensor memory (tcgen05.st); at the end of a
-//    tile walkers and stagers together copy the parked keys into the key tile (tcgen05.ld,
-//    about a microsecond), so the walk never waits for row data.  The first tile of a block
+//    tile the walkers copy the parked keys into the key tile (tcgen05.ld, about a
+//    microsecond), so the walk never waits for row data.  The first tile of a block
 //    is staged by the walkers themselves; the rows of tile i+2 are prefetched into L2.
 //
 // The walk is fully unrolled per depth and written in PTX, the four columns of a lane
@@ -123,10 +123,11 @@ __device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
 __device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t parity, uint32_t tries = kQWaitTries) {
   for (uint32_t it = 0; it < tries; ++it) {
     uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+    // (no suspend-time hint: the hardware's own limit per try measured a little faster)
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
                  " selp.u32 %0, 1, 0, p;\n}"
                  : "=r"(ok)
-                 : "r"(bar_addr), "r"(parity), "r"(200u)
+                 : "r"(bar_addr), "r"(parity)
                  : "memory");
     if (ok) return true;
   }
@@ -137,76 +138,83 @@ __device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar_addr, uint32_t 
 // The walk of four columns in lock-step, in PTX.  Operands of every block:
 //   %0..%3    byte addresses of the current nodes of columns 0..3 (updated)
 //   %4..%7    node words (updated)
-//   %8        tie flags, bit i = column i (updated)
+//   %8        tie flags of the block, bit i = column i (out)
 //   %9        the lane's base in the key tile
-//   %10..%13  address constants of the step per column, see quant_upper4
+//   %10..%13  address constants of the step per column, %14..%17 those of the crossing into
+//             the bottom-level piece, see quant_upper4
 // A node at address A has its children at 2A + c (left) and 2A + c + 128 (right).
-#define TBQ_FLAG_IN(i, bit) "and.b32 ka" #i ", %8, " #bit ";\n setp.ne.u32 t" #i ", ka" #i ", 0;\n"
 #define TBQ_DECL                                                                          \
   ".reg .b32 ka0, ka1, ka2, ka3, kx0, kx1, kx2, kx3;\n"                                   \
-  ".reg .pred p0, p1, p2, p3, t0, t1, t2, t3, q;\n"                                       \
-  TBQ_FLAG_IN(0, 1) TBQ_FLAG_IN(1, 2) TBQ_FLAG_IN(2, 4) TBQ_FLAG_IN(3, 8)
+  ".reg .pred p0, p1, p2, p3, t0, t1, t2, t3, q;\n"
 #define TBQ_KEY(i, n) "shr.u32 ka" #i ", " n ", 15;\n add.u32 ka" #i ", ka" #i ", %9;\n ld.shared.u16 kx" #i ", [ka" #i "];\n"
 #define TBQ_CMP(i, n) "setp.lt.f16x2 p" #i "|q, kx" #i ", " n ";\n setp.eq.or.f16x2 t" #i "|q, kx" #i ", " n ", t" #i ";\n"
+// the first comparison of a block starts the block's tie flags
+#define TBQ_CMP0(i, n) "setp.lt.f16x2 p" #i "|q, kx" #i ", " n ";\n setp.eq.f16x2 t" #i "|q, kx" #i ", " n ";\n"
 #define TBQ_ADV(i, a, c) "shl.b32 " a ", " a ", 1;\n add.u32 " a ", " a ", " c ";\n @p" #i " add.u32 " a ", " a ", 128;\n"
 #define TBQ_LD(a, n) "ld.shared.u32 " n ", [" a "];\n"
 #define TBQ_LEAF(i, a, c) "sub.u32 " a ", " a ", " c ";\n shr.u32 " a ", " a ", 6;\n @p" #i " add.u32 " a ", " a ", 1;\n"
 #define TBQ_COMPARE                                                                       \
   TBQ_KEY(0, "%4") TBQ_KEY(1, "%5") TBQ_KEY(2, "%6") TBQ_KEY(3, "%7")                     \
   TBQ_CMP(0, "%4") TBQ_CMP(1, "%5") TBQ_CMP(2, "%6") TBQ_CMP(3, "%7")
+#define TBQ_COMPARE0                                                                      \
+  TBQ_KEY(0, "%4") TBQ_KEY(1, "%5") TBQ_KEY(2, "%6") TBQ_KEY(3, "%7")                     \
+  TBQ_CMP0(0, "%4") TBQ_CMP0(1, "%5") TBQ_CMP0(2, "%6") TBQ_CMP0(3, "%7")
 #define TBQ_ADVANCE TBQ_ADV(0, "%0", "%10") TBQ_ADV(1, "%1", "%11") TBQ_ADV(2, "%2", "%12") TBQ_ADV(3, "%3", "%13")
 #define TBQ_LOAD TBQ_LD("%0", "%4") TBQ_LD("%1", "%5") TBQ_LD("%2", "%6") TBQ_LD("%3", "%7")
 #define TBQ_LEAVES TBQ_LEAF(0, "%0", "%10") TBQ_LEAF(1, "%1", "%11") TBQ_LEAF(2, "%2", "%12") TBQ_LEAF(3, "%3", "%13")
 #define TBQ_TIES "selp.u32 %8, 1, 0, t0;\n @t1 or.b32 %8, %8, 2;\n @t2 or.b32 %8, %8, 4;\n @t3 or.b32 %8, %8, 8;\n"
+#define TBQ_ADVANCE_X TBQ_ADV(0, "%0", "%14") TBQ_ADV(1, "%1", "%15") TBQ_ADV(2, "%2", "%16") TBQ_ADV(3, "%3", "%17")
 #define TBQ_STEP TBQ_COMPARE TBQ_ADVANCE TBQ_LOAD
-#define TBQ_OPERANDS                                                                      \
-  : "+r"(A[0]), "+r"(A[1]), "+r"(A[2]), "+r"(A[3]), "+r"(n[0]), "+r"(n[1]), "+r"(n[2]), "+r"(n[3]), "+r"(ties)      \
+#define TBQ_STEP0 TBQ_COMPARE0 TBQ_ADVANCE TBQ_LOAD
+// the last upper level: compare and compute the address in the bottom-level piece (the
+// constants %14..%17 carry the change of piece); nothing is loaded, the piece may not have arrived
+#define TBQ_CROSS TBQ_COMPARE TBQ_ADVANCE_X
+#define TBQ_CROSS0 TBQ_COMPARE0 TBQ_ADVANCE_X
+#define TBQ_OPERANDS_UP                                                                   \
+  : "+r"(A[0]), "+r"(A[1]), "+r"(A[2]), "+r"(A[3]), "=&r"(n[0]), "=&r"(n[1]), "=&r"(n[2]), "=&r"(n[3]), "=&r"(tb)   \
+  : "r"(keys_lane), "r"(cu[0]), "r"(cu[1]), "r"(cu[2]), "r"(cu[3]), "r"(cx[0]), "r"(cx[1]), "r"(cx[2]), "r"(cx[3])
+#define TBQ_OPERANDS_BOTTOM                                                               \
+  : "+r"(A[0]), "+r"(A[1]), "+r"(A[2]), "+r"(A[3]), "=&r"(n[0]), "=&r"(n[1]), "=&r"(n[2]), "=&r"(n[3]), "=&r"(tb)   \
   : "r"(keys_lane), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3])
 
-// STEPS levels inside the upper-level piece: compare, move to the child, load it.
-template <int STEPS>
-__device__ __forceinline__ void quant_steps4(uint32_t (&A)[4], uint32_t (&n)[4], uint32_t &ties, uint32_t keys_lane,
-                                             const uint32_t (&c)[4]) {
-  static_assert(STEPS >= 0 && STEPS <= 6, "at most six levels above the last upper level");
-  if constexpr (STEPS == 1)
-    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
-  else if constexpr (STEPS == 2)
-    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
-  else if constexpr (STEPS == 3)
-    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
-  else if constexpr (STEPS == 4)
-    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
-  else if constexpr (STEPS == 5)
-    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
-  else if constexpr (STEPS == 6)
-    asm volatile("{\n" TBQ_DECL TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_TIES "}" TBQ_OPERANDS);
-}
-// The last upper level: compare and compute the address in the bottom-level piece (the
-// constants carry the change of piece); nothing is loaded, the piece may not have arrived.
-__device__ __forceinline__ void quant_cross4(uint32_t (&A)[4], uint32_t (&n)[4], uint32_t &ties, uint32_t keys_lane,
-                                             const uint32_t (&c)[4]) {
-  asm volatile("{\n" TBQ_DECL TBQ_COMPARE TBQ_ADVANCE TBQ_TIES "}" TBQ_OPERANDS);
+// Upper levels 0 .. DEPTH-2 of four columns of a group of DEPTH levels (2 <= DEPTH <= 8), one
+// block of PTX: load the roots, DEPTH-2 steps inside the upper-level piece (compare, move to
+// the child, load it), then the crossing into the bottom-level piece.
+// In: A[i] = address of the root in the upper-level piece.  Out: the address of the
+// bottom-level node reached; bit i of `ties` is set if column i met a key tie.
+// cu = 128 - (root address), cx = cu + (first bottom-level node's address) - (root address)
+// - 128 * (2^(DEPTH-1) - 1), per column.
+template <int DEPTH>
+__device__ __forceinline__ void quant_upper4(uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane,
+                                             const uint32_t (&cu)[4], const uint32_t (&cx)[4]) {
+  static_assert(DEPTH >= 2 && DEPTH <= 8, "the upper-level piece holds at most seven levels");
+  [[maybe_unused]] uint32_t n[4];
+  uint32_t tb;
+  if constexpr (DEPTH == 2)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_CROSS0 TBQ_TIES "}" TBQ_OPERANDS_UP);
+  else if constexpr (DEPTH == 3)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_CROSS TBQ_TIES "}" TBQ_OPERANDS_UP);
+  else if constexpr (DEPTH == 4)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_CROSS TBQ_TIES "}" TBQ_OPERANDS_UP);
+  else if constexpr (DEPTH == 5)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_STEP TBQ_CROSS TBQ_TIES "}" TBQ_OPERANDS_UP);
+  else if constexpr (DEPTH == 6)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_STEP TBQ_STEP TBQ_CROSS TBQ_TIES "}" TBQ_OPERANDS_UP);
+  else if constexpr (DEPTH == 7)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_CROSS TBQ_TIES "}" TBQ_OPERANDS_UP);
+  else
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_CROSS TBQ_TIES "}"
+                 TBQ_OPERANDS_UP);
+  ties |= tb;
 }
 // The bottom level: load the node, compare; A[i] becomes the leaf number
 // ((A - c) >> 6) + went right, c = address of the column's first bottom-level node.
 __device__ __forceinline__ void quant_bottom4(uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane,
                                               const uint32_t (&c)[4]) {
-  uint32_t n[4] = {0, 0, 0, 0};
-  asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_COMPARE TBQ_LEAVES TBQ_TIES "}" TBQ_OPERANDS);
-}
-
-// Upper levels 0 .. DEPTH-2 of four columns of a group of DEPTH levels (DEPTH >= 2).
-// In: A[i] = address of the root in the upper-level piece.  Out: the address of the
-// bottom-level node reached.  cu = 128 - (root address), cx = cu + (first bottom-level
-// node's address) - (root address) - 128 * (2^(DEPTH-1) - 1), per column.
-template <int DEPTH>
-__device__ __forceinline__ void quant_upper4(uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane,
-                                             const uint32_t (&cu)[4], const uint32_t (&cx)[4]) {
-  uint32_t n[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) n[i] = lds_u32(A[i]);
-  quant_steps4<DEPTH - 2>(A, n, ties, keys_lane, cu);
-  quant_cross4(A, n, ties, keys_lane, cx);
+  [[maybe_unused]] uint32_t n[4];
+  uint32_t tb;
+  asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_COMPARE0 TBQ_LEAVES TBQ_TIES "}" TBQ_OPERANDS_BOTTOM);
+  ties |= tb;
 }
 __device__ __forceinline__ void quant_upper4_any(uint32_t depth, uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane,
                                                  const uint32_t (&cu)[4], const uint32_t (&cx)[4]) {
@@ -352,7 +360,7 @@ __host__ __device__ constexpr int quant_key_tile_bytes(int num_features) { retur
 //   warps 16..19  stagers: while a tile is walked they turn the NEXT tile's rows into keys and
 //                 park the finished key words in tensor memory -- the only on-chip space left
 //                 beside the 128 KB key tile -- stager s in lane quarter s (feature pairs
-//                 256 s ...).  At the end of the tile the twenty walker and stager warps copy
+//                 256 s ...).  At the end of the tile the sixteen walker warps copy
 //                 the words from tensor memory into the key tile with conflict-free stores.
 //   warps 20, 21  leaf warps, one per set: pick up each finished table, gather the leaf values
 //                 from the column-major leaf plane in L2 (lane = row; the leaves that the 32
@@ -419,7 +427,7 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
     for (int i = 6; i < 12; ++i) mbar_init(bars + i, kQSetWarps);  // empty: one arrival per walker warp of the set
     for (int i = 12; i < 16; ++i) mbar_init(bars + i, kQSetWarps); // table_full: every walker of the set has written
     mbar_init(bars + 16, kQWalkers + kQStagers);                   // tile_done: the tile is walked, the next one's keys are staged
-    mbar_init(bars + 18, kQWalkers + kQStagers);                   // keys_ready: every warp has copied its share of the keys
+    mbar_init(bars + 18, kQWalkers + kQStagers);                   // keys_ready: every walker has copied its share of the keys, the stagers know of it
     for (int i = 19; i < 23; ++i) mbar_init(bars + i, 1);          // table_free: the leaf warp has read the table
     mbar_init(bars + 23, 1);                                       // sum_ready: leaf warp 1 has written its row sums
     mbar_init(bars + 24, 1);                                       // sum_free: leaf warp 0 has read them
@@ -511,7 +519,8 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
     tmem_store8(taddr + (uint32_t)(kQUnitPairs * u), o);
   };
   // This warp's share of the copy from tensor memory into the key tile: the quarter's columns
-  // in chunks of 16 (two units), dealt to the quarter's five warps (rank = warp / 4).  Column
+  // in chunks of 16 (two units), dealt to the quarter's four walker warps (rank = warp / 4; a warp reaches only
+  // the lane quarter warp mod 4; the stagers stay out of it and finish their tile switch at once).  Column
   // 8u + 2s + e of lane 4a + j is the word of pair 256 q + 8u + 2j + e for row a + 8 ((s + j) mod 4).
   auto copy_keys_out = [&]() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -519,7 +528,7 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
 #pragma unroll
     for (int s4 = 0; s4 < 4; ++s4) rowoff[s4] = (uint32_t)(sa + 8 * ((s4 + sj) & 3)) * 4u;
 #pragma unroll 1
-    for (int c0 = 16 * (warp >> 2); c0 < kQStagerPairs && pair0 + c0 < NP; c0 += 16 * 5) {
+    for (int c0 = 16 * (warp >> 2); c0 < kQStagerPairs && pair0 + c0 < NP; c0 += 16 * 4) {
       uint32_t w[16];
       tmem_load16(taddr + (uint32_t)c0, w);
 #pragma unroll
@@ -568,7 +577,6 @@ __global__ void __launch_bounds__(kQThreads, 1) tb_walk_quant_kernel(const Quant
       if (lane == 0) mbar_arrive(tile_done_s);
       ok = mbar_wait_all_lanes(tile_done_s, (uint32_t)it & 1u);
       if (!ok) break;
-      if (has_next) copy_keys_out();
       __syncwarp();
       if (lane == 0) mbar_arrive(keys_ready_s);
       ok = mbar_wait_all_lanes(keys_ready_s, (uint32_t)it & 1u); // the copy is complete: tensor memory may be rewritten
