@@ -215,7 +215,8 @@ def test_sixteen_bit_key_kernel_is_exact(name):
     want, want_ids = oracle.predict(forest, X, leaf_ids=True)
     df = kernels.DeviceForest(forest, representation="reorg", feature_bits=16, batch_hint=len(X))
     info = df.info()
-    assert info.schedule.feature_bits == 16 and info.threads_per_block == 768
+    # wide rows: one key tile per block (24 warps); narrow rows: batches of tiles (20 warps)
+    assert info.schedule.feature_bits == 16 and info.threads_per_block == (768 if name == "c3" else 640)
     dX = _dev(X)
     ids = df.predict_leaf_ids(dX).cpu().numpy()
     df.check_status()
@@ -235,18 +236,60 @@ def test_sixteen_bit_key_kernel_is_exact(name):
     assert np.array_equal(got2[ok], got[ok])
 
 
-def test_auto_representation_picks_keys_for_wide_rows_only():
+def test_auto_representation_picks_keys_for_single_output_forests_of_up_to_eight_levels():
+    """"auto": keys for wide rows (one tile per block) and for narrow rows (batches of tiles)
+    of single-output forests; fp32 tiles for multiclass forests, on request, and for explicit
+    representations."""
     from treebeard_b200 import kernels
     wide, Xw = small_config("c3", rows=64)
     narrow, Xn = small_config("c2", rows=64)
+    multi, Xm = small_config("c4", rows=64)
     a = kernels.DeviceForest(wide, representation="auto")
     b = kernels.DeviceForest(narrow, representation="auto")
-    assert a.info().schedule.feature_bits == 16
-    assert b.info().schedule.feature_bits == 32
+    assert a.info().schedule.feature_bits == 16 and a.info().threads_per_block == 768
+    assert b.info().schedule.feature_bits == 16 and b.info().threads_per_block == 640
+    assert kernels.DeviceForest(narrow, representation="auto", feature_bits=32).info().schedule.feature_bits == 32
+    assert kernels.DeviceForest(narrow, representation="sparse").info().schedule.feature_bits == 32
+    assert kernels.DeviceForest(multi, representation="auto").info().schedule.feature_bits == 32
     assert_predictions_close(a.predict(_dev(Xw)).cpu().numpy(), oracle.predict(wide, Xw))
+    assert_predictions_close(b.predict(_dev(Xn)).cpu().numpy(), oracle.predict(narrow, Xn))
     with pytest.raises(kernels.TbkError):
         multi, _ = small_config("c4", rows=1)
         kernels.DeviceForest(multi, representation="reorg", feature_bits=16)
+
+
+@pytest.mark.parametrize("name,rows,chunks", [("c2", 100003, 0), ("c2", 100003, 3), ("c1", 77777, 0), ("c2", 5000, 0)])
+def test_batched_key_kernel_is_exact(name, rows, chunks):
+    """Narrow rows: the key tiles of up to 16 tiles are staged together and the forest streams
+    once per batch.  Full batches, persistent blocks with several batches, a ragged last
+    batch and tile, tree chunks, partial sums and leaf ids; ties, NaN and infinities included."""
+    from treebeard_b200 import kernels
+    forest, X = small_config(name, rows=rows)
+    X = X.copy()
+    split = np.nonzero(forest.left >= 0)[0]
+    for i in range(3000):
+        g = split[(i * 37) % len(split)]
+        X[(i * 31) % len(X), forest.feat[g]] = forest.thr[g]
+    X[3, :] = np.nan
+    X[rows - 1, 0] = np.inf
+    X[rows // 2, 1] = -np.inf
+    want, want_ids = oracle.predict(forest, X, leaf_ids=True)
+    df = kernels.DeviceForest(forest, representation="auto", batch_hint=rows, tree_chunks=chunks)
+    info = df.info()
+    assert info.schedule.feature_bits == 16 and info.threads_per_block == 640
+    dX = _dev(X)
+    got = df.predict(dX).cpu().numpy()
+    df.check_status()
+    ok = ~np.isnan(want)
+    assert_predictions_close(got[ok], want[ok])
+    assert df.info().reserved[0] > 0          # key ties were hit and resolved exactly
+    sub = slice(rows - 20001, rows) if rows > 20001 else slice(0, rows)
+    ids = df.predict_leaf_ids(dX[sub]).cpu().numpy()
+    df.check_status()
+    assert np.array_equal(ids, want_ids[sub]), f"{(ids != want_ids[sub]).sum()} leaf ids differ"
+    part = df.predict_partial(dX[:rows - 13])
+    again = df.finalize(part).cpu().numpy()
+    assert_predictions_close(again[ok[:rows - 13]], want[:rows - 13][ok[:rows - 13]])
 
 
 @pytest.mark.parametrize("trees,rows", [(1, 70), (24, 1500), (33, 20000)])
@@ -449,6 +492,7 @@ def test_sixteen_bit_keys_refuse_what_they_do_not_cover():
 
 
 @pytest.mark.parametrize("name,layout", [("c2", dict(representation="sparse")),
+                                         ("c2", dict(representation="auto", feature_bits=16)),
                                          ("c3", dict(representation="auto", feature_bits=16)),
                                          ("c5", dict(representation="auto", feature_bits=16))])
 def test_expired_device_wait_is_reported_and_survivable(name, layout):

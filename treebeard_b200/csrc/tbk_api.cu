@@ -7,6 +7,7 @@
 #include "schedule.h"
 #include "walk_kernels.cuh"
 #include "walk_quant.cuh"
+#include "walk_quant_batch.cuh"
 #include "walk_deep.cuh"
 #include "packed_image.h"
 
@@ -170,26 +171,46 @@ int quant_smem_bytes(int num_features) {
   return tb::kQBarBytes + tb::kQRingBytes + tb::kQLeafTableBytes + tb::quant_key_tile_bytes(num_features);
 }
 
-// One prediction with the 16-bit-key kernel (persistent blocks of 16 warps over tiles of 32 rows).
+// Tiles of 32 rows that the narrow-row kernel can stage together (0: the rows are too wide for it).
+int quant_batch_tiles(const tbk_forest *f, int num_features) {
+  const int room = f->max_smem_optin - tb::kQBBarBytes - tb::kQRingBytes;
+  const int fit = room / tb::quant_batch_tile_bytes(num_features);
+  return fit >= 4 ? std::min(fit, tb::kQBMaxTiles) : 0;
+}
+
+// One prediction with a 15-bit-key kernel: rows whose key tiles fit shared memory several at a
+// time go to the batch kernel (persistent blocks of 20 warps over batches of up to 16 tiles),
+// wide rows to the kernel that holds one tile (persistent blocks of 24 warps over tiles of 32 rows).
 int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
               float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot) {
   const auto &q = f->qf;
   const int64_t G = (int64_t)q.groups.size();
   const int64_t tiles = (n_rows + 31) / 32;
+  const int max_batch = quant_batch_tiles(f, q.num_features);
+  const bool batched = max_batch > 0;
+  // batch kernel: as many tiles per batch as still give every SM a batch
+  int R = 1;
+  if (batched) {
+    R = max_batch;
+    while (R > 1 && (tiles + R - 1) / R < (int64_t)f->num_sms) R = (R + 1) / 2;
+  }
+  const int64_t units = batched ? (tiles + R - 1) / R : tiles; // blocks' units of work along x
   int64_t chunks = 1;
   if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
-  else if (tiles < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + tiles - 1) / tiles;
-  chunks = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(chunks, G), 65535));
+  else if (batched) {
+    if (units < (int64_t)f->num_sms) chunks = ((int64_t)f->num_sms + units - 1) / units;
+  } else if (tiles < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + tiles - 1) / tiles;
+  chunks = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(chunks, batched ? std::max<int64_t>(1, G / 2) : G), 65535));
   const int gpc = (int)((G + chunks - 1) / chunks);
   chunks = (G + gpc - 1) / gpc;
   const bool vec4 = q.num_features % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(d_rows) & 15) == 0;
-  // One block per SM (shared memory allows no more).  With more tiles than blocks a block is
-  // persistent and stages its next tile in tensor memory while it walks the current one; that
-  // path reads rows with 16-byte loads.
+  // One block per SM (shared memory allows no more).  With more units than blocks a block is
+  // persistent; the one-tile kernel then stages its next tile in tensor memory while it walks
+  // the current one, a path that reads rows with 16-byte loads.
   const int64_t blocks_x = std::max<int64_t>(1, (int64_t)f->num_sms / chunks);
-  const int64_t grid_x = (vec4 && tiles > blocks_x) ? blocks_x : tiles;
+  const int64_t grid_x = batched ? std::min(units, blocks_x) : (vec4 && tiles > blocks_x) ? blocks_x : tiles;
   tb::LaunchPlan plan;
-  plan.row_warps = 1;
+  plan.row_warps = batched ? R : 1;
   plan.tree_threads = tb::kQWalkers;
   plan.rows_per_lane = 1;
   plan.chunks = (int32_t)chunks;
@@ -197,8 +218,8 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   plan.staged = 1;
   plan.cache_rows = 1;
   plan.stage_bytes = tb::kQPiece;
-  plan.smem_bytes = quant_smem_bytes(q.num_features);
-  plan.threads = tb::kQThreads;
+  plan.smem_bytes = batched ? tb::quant_batch_smem_bytes(q.num_features, R) : quant_smem_bytes(q.num_features);
+  plan.threads = batched ? tb::kQBThreads : tb::kQThreads;
   plan.grid_x = grid_x;
   f->last_plan = plan;
 
@@ -241,6 +262,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   p.transform = q.transform;
   p.initial_value = (float)q.initial_value;
   p.vec4_ok = vec4 ? 1 : 0;
+  p.tiles_per_batch = R;
   p.status = f->d_status;
   p.tie_count = f->d_ties;
   p.skip_first_copy = f->expire_next_wait ? 1 : 0;
@@ -251,13 +273,16 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   const bool ids = mode == kLeafIds;
   const int ud = (f->uniform_depth == 8 || f->uniform_depth == 6) ? f->uniform_depth : 0;
   const QuantKernel qkernel =
-      ud == 8 ? (ids ? tb::tb_walk_quant_kernel<8, true> : tb::tb_walk_quant_kernel<8, false>)
+      batched ? (ud == 8   ? (ids ? tb::tb_walk_quant_batch_kernel<8, true> : tb::tb_walk_quant_batch_kernel<8, false>)
+                 : ud == 6 ? (ids ? tb::tb_walk_quant_batch_kernel<6, true> : tb::tb_walk_quant_batch_kernel<6, false>)
+                           : (ids ? tb::tb_walk_quant_batch_kernel<0, true> : tb::tb_walk_quant_batch_kernel<0, false>))
+      : ud == 8 ? (ids ? tb::tb_walk_quant_kernel<8, true> : tb::tb_walk_quant_kernel<8, false>)
       : ud == 6 ? (ids ? tb::tb_walk_quant_kernel<6, true> : tb::tb_walk_quant_kernel<6, false>)
                 : (ids ? tb::tb_walk_quant_kernel<0, true> : tb::tb_walk_quant_kernel<0, false>);
   CUDA_TRY(cudaFuncSetAttribute((const void *)qkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
   if (f->timing) CUDA_TRY(cudaEventRecord(f->ev0, stream));
   dim3 grid((unsigned)grid_x, (unsigned)chunks);
-  qkernel<<<grid, tb::kQThreads, plan.smem_bytes, stream>>>(p);
+  qkernel<<<grid, plan.threads, plan.smem_bytes, stream>>>(p);
   CUDA_TRY(cudaGetLastError());
   ++f->launches;
   const int tpb = 256;
@@ -658,8 +683,14 @@ int tbk_image_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, 
   int max_depth = 0;
 #pragma omp parallel for reduction(max : max_depth) schedule(dynamic, 64) num_threads(tb::pack_threads())
   for (int64_t t = 0; t < T; ++t) max_depth = std::max(max_depth, (int)tb::tree_depth(host, t));
+  // narrow rows: the key tiles of at least four 32-row tiles fit beside the ring, so the batch
+  // kernel applies; measured faster than the fp32 walk on single-output forests of up to 8 levels
+  const bool batch_fits =
+      (smem_limit - tb::kQBBarBytes - tb::kQRingBytes) / tb::quant_batch_tile_bytes(host.num_features) >= 4;
   bool want_quant = (bits == 16 && max_depth <= tb::kQuantMaxDepth) ||
-                    (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits);
+                    (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits) ||
+                    (bits == 0 && rep == TBK_REP_AUTO && ts == 1 && host.num_classes == 0 && batch_fits &&
+                     max_depth <= tb::kQuantMaxDepth);
   if (want_quant) {
     std::string qerr = tb::pack_quant(host, &im.qf);
     if (qerr.empty() && quant_smem_bytes(host.num_features) > smem_limit)
@@ -843,6 +874,11 @@ int tbk_forest_create_from_image(const tbk_image *img, const tbk_schedule *sched
     tb::LaunchPlan &pl = f->last_plan;
     pl.row_warps = 1; pl.tree_threads = tb::kQWalkers; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
     pl.stage_bytes = tb::kQPiece; pl.smem_bytes = quant_smem_bytes(q.num_features); pl.threads = tb::kQThreads;
+    if (const int batch = quant_batch_tiles(f, q.num_features)) { // narrow rows: the batch kernel
+      pl.row_warps = batch;
+      pl.smem_bytes = tb::quant_batch_smem_bytes(q.num_features, batch);
+      pl.threads = tb::kQBThreads;
+    }
     *out = f;
     return TBK_OK;
   }

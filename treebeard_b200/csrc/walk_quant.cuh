@@ -75,6 +75,7 @@ struct QuantParams {
   int32_t num_groups, groups_per_chunk, num_features, transform;
   float initial_value;
   int32_t vec4_ok;
+  int32_t tiles_per_batch;       // narrow-row kernel (walk_quant_batch.cuh): 32-row tiles staged together
   int32_t skip_first_copy;       // failure drill: the first piece's copy is never issued, so its wait expires
   uint32_t wait_tries;           // polls before a wait gives up (0 = kQWaitTries)
   int32_t *status;
