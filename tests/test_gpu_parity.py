@@ -253,9 +253,11 @@ def test_auto_representation_picks_keys_for_single_output_forests_of_up_to_eight
     assert kernels.DeviceForest(multi, representation="auto").info().schedule.feature_bits == 32
     assert_predictions_close(a.predict(_dev(Xw)).cpu().numpy(), oracle.predict(wide, Xw))
     assert_predictions_close(b.predict(_dev(Xn)).cpu().numpy(), oracle.predict(narrow, Xn))
-    with pytest.raises(kernels.TbkError):
-        multi, _ = small_config("c4", rows=1)
-        kernels.DeviceForest(multi, representation="reorg", feature_bits=16)
+    # integral thresholds (integer-valued features: rows tie with thresholds all the time) keep fp32 tiles
+    import copy
+    rounded = copy.copy(narrow)
+    rounded.thr = np.where(narrow.left >= 0, np.round(narrow.thr * 4), narrow.thr).astype(np.float32)
+    assert kernels.DeviceForest(rounded, representation="auto").info().schedule.feature_bits == 32
 
 
 @pytest.mark.parametrize("name,rows,chunks", [("c2", 100003, 0), ("c2", 100003, 3), ("c1", 77777, 0), ("c2", 5000, 0)])
@@ -485,10 +487,44 @@ def test_runner_rejects_buffers_on_different_sides(tmp_path):
 
 
 def test_sixteen_bit_keys_refuse_what_they_do_not_cover():
-    from treebeard_b200 import kernels
-    forest, _ = small_config("c4")
+    """Multiclass forests need rows narrow enough for the batch kernel, and their key layout
+    keeps no per-class partial sums."""
+    from treebeard_b200 import kernels, synth
+    wide = synth.generate_forest(40, 60, 6, 1800, 0.1, 0.1, synth.Marginal("normal", 1800), num_classes=3)
     with pytest.raises(kernels.TbkError):
-        kernels.DeviceForest(forest, representation="auto", feature_bits=16)
+        kernels.DeviceForest(wide, representation="auto", feature_bits=16)
+    forest, X = small_config("c4", rows=64)
+    df = kernels.DeviceForest(forest, representation="auto", feature_bits=16)
+    with pytest.raises(kernels.TbkError, match="partial"):
+        df.predict_partial(_dev(X))
+
+
+@pytest.mark.parametrize("rows", [100003, 5000, 77])
+def test_batched_key_kernel_multiclass(rows):
+    """Multiclass forests on the batch kernel: classes laid out group by group, one walker set
+    per class, arg-max on the fly with the reference's tie rule; int8 and fp32 class ids."""
+    from treebeard_b200 import kernels
+    forest, X = small_config("c4", rows=rows)
+    X = X.copy()
+    split = np.nonzero(forest.left >= 0)[0]
+    for i in range(2000):
+        g = split[(i * 37) % len(split)]
+        X[(i * 31) % len(X), forest.feat[g]] = forest.thr[g]
+    want, sums = oracle.predict(forest, X, class_sums=True)
+    _, want_ids = oracle.predict(forest, X, leaf_ids=True)
+    df = kernels.DeviceForest(forest, representation="auto", feature_bits=16, batch_hint=rows)
+    info = df.info()
+    assert info.schedule.feature_bits == 16 and info.threads_per_block == 640
+    dX = _dev(X)
+    got = df.predict(dX).cpu().numpy()
+    df.check_status()
+    assert_predictions_close(got, want, forest, sums)
+    got8 = df.predict(dX, int8=True).cpu().numpy()
+    assert got8.dtype == np.int8 and np.array_equal(got8, got.astype(np.int8))
+    sub = slice(max(0, rows - 9001), rows)
+    ids = df.predict_leaf_ids(dX[sub]).cpu().numpy()
+    df.check_status()
+    assert np.array_equal(ids, want_ids[sub])
 
 
 @pytest.mark.parametrize("name,layout", [("c2", dict(representation="sparse")),

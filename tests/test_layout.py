@@ -157,9 +157,20 @@ def test_sixteen_bit_keys_refuse_what_they_cannot_hold():
     chain = synth.generate_forest(5, 2, 13, 4, 0.3, 0.1, synth.Marginal("uniform01", 4))
     with pytest.raises(kernels.TbkError, match="deeper"):
         kernels.host_layout_check(chain, None, representation="reorg", feature_bits=16)
-    multi, _ = small_config("c4", rows=1)
-    with pytest.raises(kernels.TbkError, match="single-output"):
-        kernels.host_layout_check(multi, None, representation="reorg", feature_bits=16)
+
+
+def test_sixteen_bit_keys_lay_multiclass_forests_out_class_by_class():
+    """Every class fills whole groups of 32 columns; the host interpreter of the packed planes
+    must find the oracle's leaves and per-class sums."""
+    forest, X = small_config("c4", rows=300)
+    want, want_ids = oracle.predict(forest, X, leaf_ids=True)
+    _, sums_want = oracle.predict(forest, X, class_sums=True)
+    ids, sums, info = kernels.host_layout_check(forest, X, representation="reorg", feature_bits=16)
+    assert np.array_equal(ids, want_ids)
+    assert np.allclose(sums, sums_want - forest.initial_value, rtol=1e-5, atol=1e-5) or \
+        np.allclose(sums, sums_want, rtol=1e-5, atol=1e-5)
+    per_class = np.bincount(forest.class_id, minlength=forest.num_classes)
+    assert info.num_groups == sum(max(1, -(-int(n) // 32)) for n in per_class)
 
 
 def test_multiclass_class_without_trees_keeps_its_place():

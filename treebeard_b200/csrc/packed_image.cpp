@@ -120,6 +120,8 @@ void serialize_image(const PackedImage &im, std::vector<uint8_t> *out) {
     o.vec(q.tree_index);
     o.vec(q.lo);
     o.vec(q.scale);
+    o.pod(q.num_classes);
+    o.vec(q.group_class);
   } else {
     const DeepForest &q = im.df;
     put_key_forest_head(o, q.num_features, q.transform, q.initial_value, q.num_trees, q.num_nodes, q.max_depth);
@@ -202,11 +204,16 @@ std::string deserialize_image(const uint8_t *data, uint64_t size, PackedImage *i
     in.vec(&q.tree_index);
     in.vec(&q.lo);
     in.vec(&q.scale);
+    q.num_classes = in.pod<int32_t>();
+    in.vec(&q.group_class);
     const size_t n = q.node_plane.size();
     if (in.ok && (q.leaf_plane.size() != n || q.exact_plane.size() != n || q.orig_leaf.size() != n ||
                   q.tree_index.size() != q.groups.size() * kQuantCols || q.lo.size() != (size_t)q.num_features + 1 ||
-                  q.scale.size() != q.lo.size()))
+                  q.scale.size() != q.lo.size() || q.num_classes < 0 ||
+                  q.group_class.size() != (q.num_classes > 0 ? q.groups.size() : 0)))
       in.ok = false;
+    for (const int32_t cls : q.group_class)
+      if (cls < 0 || cls >= q.num_classes) in.ok = false;
     for (const QuantGroup &g : q.groups)
       if (in.ok && (g.depth < 1 || g.depth > (uint32_t)kQuantMaxDepth || g.slots != (1u << g.depth) ||
                     g.elem_off + (uint64_t)g.slots * kQuantCols > n))

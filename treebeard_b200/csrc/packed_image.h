@@ -30,7 +30,7 @@ struct PackedImage {
   DeepForest df;       // kDeep
 };
 
-constexpr uint32_t kPackedImageVersion = 2; // changes whenever a packer's output does
+constexpr uint32_t kPackedImageVersion = 3; // changes whenever a packer's output does
 
 void serialize_image(const PackedImage &im, std::vector<uint8_t> *out);
 // Empty string on success.  Checks the version, sizes and a checksum; a stale or damaged

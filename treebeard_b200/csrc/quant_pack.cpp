@@ -34,7 +34,6 @@ std::string quant_feature_ranges(const Forest &f, float span, std::vector<float>
 std::string pack_quant(const Forest &f, QuantForest *out) {
   std::string err = validate(f);
   if (!err.empty()) return err;
-  if (f.num_classes > 0) return "16-bit feature keys are implemented for single-output forests only";
   if (f.num_features > kQuantMaxFeatures) return "more than " + std::to_string(kQuantMaxFeatures) + " features";
   const int64_t T = f.num_trees();
   const int F = f.num_features;
@@ -43,6 +42,7 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
   q = QuantForest();
   q.num_features = F;
   q.transform = f.transform;
+  q.num_classes = f.num_classes;
   q.initial_value = f.initial_value;
   q.num_trees = T;
   q.num_nodes = f.num_nodes();
@@ -57,18 +57,38 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
   }
   if (q.max_depth > kQuantMaxDepth)
     return "trees deeper than " + std::to_string(kQuantMaxDepth) + " levels do not fit the key layout's stages";
+  // columns in walking order: trees by depth -- within their class for a multiclass forest,
+  // whose classes each fill whole groups -- and -1 for the filler columns
   std::vector<int64_t> order(T);
   std::iota(order.begin(), order.end(), 0);
-  std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return depth[a] < depth[b]; });
+  const bool multi = f.num_classes > 0;
+  std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) {
+    if (multi && f.class_id[a] != f.class_id[b]) return f.class_id[a] < f.class_id[b];
+    return depth[a] < depth[b];
+  });
+  std::vector<int64_t> cols;
+  if (multi) {
+    size_t at = 0;
+    for (int32_t cls = 0; cls < f.num_classes; ++cls) {
+      const size_t begin = cols.size();
+      while (at < order.size() && f.class_id[order[at]] == cls) cols.push_back(order[at++]);
+      if (cols.size() == begin) cols.push_back(-1); // a class without trees still gets its group
+      while (cols.size() % kQuantCols) cols.push_back(-1);
+      q.group_class.insert(q.group_class.end(), (cols.size() - begin) / kQuantCols, cls);
+    }
+  } else {
+    cols.assign(order.begin(), order.end());
+    while (cols.size() % kQuantCols) cols.push_back(-1);
+  }
 
-  const int64_t G = (T + kQuantCols - 1) / kQuantCols;
+  const int64_t G = (int64_t)cols.size() / kQuantCols;
   q.groups.resize(G);
   q.tree_index.assign(G * kQuantCols, -1);
   uint64_t elems = 0;
   for (int64_t g = 0; g < G; ++g) {
     uint32_t d = 1; // at least one level, so that every group has both halves of its planes
-    for (int c = 0; c < kQuantCols && g * kQuantCols + c < T; ++c)
-      d = std::max<uint32_t>(d, depth[order[g * kQuantCols + c]]);
+    for (int c = 0; c < kQuantCols; ++c)
+      if (cols[g * kQuantCols + c] >= 0) d = std::max<uint32_t>(d, depth[cols[g * kQuantCols + c]]);
     q.groups[g] = QuantGroup{elems, d, 1u << d};
     elems += (uint64_t)(1u << d) * kQuantCols;
   }
@@ -82,8 +102,8 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
     const QuantGroup &gm = q.groups[g];
     for (int c = 0; c < kQuantCols; ++c) {
       const int64_t k = g * kQuantCols + c;
-      if (k >= T) break;
-      const int64_t t = order[k], a = f.tree_off[t];
+      if (cols[k] < 0) continue;
+      const int64_t t = cols[k], a = f.tree_off[t];
       q.tree_index[k] = (int32_t)t;
       struct Item { int32_t node; uint32_t slot, level; };
       std::vector<Item> stack{{0, 0, 0}};
@@ -121,6 +141,8 @@ void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows,
     for (int i = 0; i < F; ++i) keys[i] = quant_key15(row[i], q.lo[i], q.scale[i]);
     keys[F] = (uint16_t)kKey15Max;
     float acc = 0.f;
+    const int C = q.num_classes;
+    if (sums && C > 0) std::fill(sums + r * C, sums + (r + 1) * C, 0.f);
     for (size_t g = 0; g < q.groups.size(); ++g) {
       const QuantGroup &gm = q.groups[g];
       for (int c = 0; c < kQuantCols; ++c) {
@@ -140,10 +162,11 @@ void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows,
         }
         const uint64_t e = quant_leaf_elem(gm, n - (gm.slots - 1), c);
         acc += q.leaf_plane[e];
+        if (sums && C > 0) sums[r * C + q.group_class[g]] += q.leaf_plane[e];
         if (leaf_ids) leaf_ids[r * q.num_trees + t] = q.orig_leaf[e];
       }
     }
-    if (sums) sums[r] = acc;
+    if (sums && C == 0) sums[r] = acc;
   }
   if (ties) *ties = tie_count;
 }

@@ -52,7 +52,7 @@ struct QuantGroup {
 };
 
 struct QuantForest {
-  int32_t num_features = 0, transform = 0;
+  int32_t num_features = 0, transform = 0, num_classes = 0;
   double initial_value = 0.0;
   int64_t num_trees = 0, num_nodes = 0;
   int32_t max_depth = 0;
@@ -62,6 +62,7 @@ struct QuantForest {
   std::vector<float> exact_plane;
   std::vector<int32_t> orig_leaf;   // original node id per leaf-plane element
   std::vector<int32_t> tree_index;  // [groups*32] original tree index, -1 = filler
+  std::vector<int32_t> group_class; // multiclass: the class every tree of the group votes for
   std::vector<float> lo, scale;     // per feature (+ sentinel entry)
 };
 
@@ -110,10 +111,14 @@ inline uint32_t quant_feature_of_code(uint32_t code) { return (code >> 6) * 2u +
 std::string quant_feature_ranges(const Forest &f, float span, std::vector<float> *lo, std::vector<float> *scale);
 
 // Empty string on success.  Fails (so that the caller can fall back to another layout)
-// for multiclass forests, trees deeper than kQuantMaxDepth, or non-finite thresholds.
+// for trees deeper than kQuantMaxDepth or non-finite thresholds.  Multiclass forests are
+// laid out class by class: every class is padded to whole groups (filler columns hold one
+// pass-through tree with value 0), classes in increasing order, every class present, so a
+// group belongs to one class (group_class).
 std::string pack_quant(const Forest &f, QuantForest *out);
 
-// Host interpreter of the packed planes (layout verification only).
+// Host interpreter of the packed planes (layout verification only).  sums: one value per
+// row, or num_classes values per row for a multiclass forest.
 void walk_quant_on_host(const QuantForest &q, const float *rows, int64_t n_rows, int64_t ld,
                         int32_t *leaf_ids, float *sums, int64_t *ties);
 

@@ -78,6 +78,8 @@ struct tbk_forest {
   float *d_qleaf = nullptr, *d_qexact = nullptr, *d_qlo = nullptr, *d_qscale = nullptr;
   tb::DevQuantGroup *d_qgroups = nullptr;
   int32_t *d_qtree_index = nullptr, *d_qorig = nullptr;
+  int32_t *d_qset_groups = nullptr, *d_qgroup_class = nullptr; // multiclass key layout
+  int32_t qset_count[2] = {0, 0};
   unsigned long long *d_ties = nullptr;
   // one-tree-per-stage layout (deep trees); shares the device buffers of the key layout
   bool deep = false;
@@ -181,13 +183,19 @@ int quant_batch_tiles(const tbk_forest *f, int num_features) {
 // One prediction with a 15-bit-key kernel: rows whose key tiles fit shared memory several at a
 // time go to the batch kernel (persistent blocks of 20 warps over batches of up to 16 tiles),
 // wide rows to the kernel that holds one tile (persistent blocks of 24 warps over tiles of 32 rows).
-int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out,
+int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out, int32_t out_kind,
               float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot) {
   const auto &q = f->qf;
   const int64_t G = (int64_t)q.groups.size();
   const int64_t tiles = (n_rows + 31) / 32;
   const int max_batch = quant_batch_tiles(f, q.num_features);
   const bool batched = max_batch > 0;
+  const bool multi = q.num_classes > 0;
+  if (multi && !batched) return fail(TBK_ERR_UNSUPPORTED, "multiclass forests in the key layout need rows narrow enough for the batch kernel");
+  if (multi && mode == kPartial)
+    return fail(TBK_ERR_UNSUPPORTED, "the key layout keeps no per-class partial sums: create the forest with feature_bits = 32");
+  if (multi && f->user.tree_chunks > 1)
+    return fail(TBK_ERR_UNSUPPORTED, "multiclass forests in the key layout are walked in one tree chunk");
   // batch kernel: as many tiles per batch as still give every SM a batch
   int R = 1;
   if (batched) {
@@ -197,6 +205,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   const int64_t units = batched ? (tiles + R - 1) / R : tiles; // blocks' units of work along x
   int64_t chunks = 1;
   if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
+  else if (multi) chunks = 1; // a class must stay within one leaf warp's sequence of groups
   else if (batched) {
     if (units < (int64_t)f->num_sms) chunks = ((int64_t)f->num_sms + units - 1) / units;
   } else if (tiles < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + tiles - 1) / tiles;
@@ -263,6 +272,12 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   p.initial_value = (float)q.initial_value;
   p.vec4_ok = vec4 ? 1 : 0;
   p.tiles_per_batch = R;
+  p.set_groups = f->d_qset_groups;
+  p.set_count[0] = f->qset_count[0];
+  p.set_count[1] = f->qset_count[1];
+  p.group_class = f->d_qgroup_class;
+  p.num_classes = q.num_classes;
+  p.out_kind = out_kind == TBK_OUT_I8 ? 1 : 0;
   p.status = f->d_status;
   p.tie_count = f->d_ties;
   p.skip_first_copy = f->expire_next_wait ? 1 : 0;
@@ -273,9 +288,12 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   const bool ids = mode == kLeafIds;
   const int ud = (f->uniform_depth == 8 || f->uniform_depth == 6) ? f->uniform_depth : 0;
   const QuantKernel qkernel =
-      batched ? (ud == 8   ? (ids ? tb::tb_walk_quant_batch_kernel<8, true> : tb::tb_walk_quant_batch_kernel<8, false>)
-                 : ud == 6 ? (ids ? tb::tb_walk_quant_batch_kernel<6, true> : tb::tb_walk_quant_batch_kernel<6, false>)
-                           : (ids ? tb::tb_walk_quant_batch_kernel<0, true> : tb::tb_walk_quant_batch_kernel<0, false>))
+      multi ? (ud == 8 ? (ids ? tb::tb_walk_quant_batch_kernel<8, true, true> : tb::tb_walk_quant_batch_kernel<8, false, true>)
+                       : (ids ? tb::tb_walk_quant_batch_kernel<0, true, true> : tb::tb_walk_quant_batch_kernel<0, false, true>))
+      : batched
+          ? (ud == 8   ? (ids ? tb::tb_walk_quant_batch_kernel<8, true, false> : tb::tb_walk_quant_batch_kernel<8, false, false>)
+             : ud == 6 ? (ids ? tb::tb_walk_quant_batch_kernel<6, true, false> : tb::tb_walk_quant_batch_kernel<6, false, false>)
+                       : (ids ? tb::tb_walk_quant_batch_kernel<0, true, false> : tb::tb_walk_quant_batch_kernel<0, false, false>))
       : ud == 8 ? (ids ? tb::tb_walk_quant_kernel<8, true> : tb::tb_walk_quant_kernel<8, false>)
       : ud == 6 ? (ids ? tb::tb_walk_quant_kernel<6, true> : tb::tb_walk_quant_kernel<6, false>)
                 : (ids ? tb::tb_walk_quant_kernel<0, true> : tb::tb_walk_quant_kernel<0, false>);
@@ -450,7 +468,7 @@ int run(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t l
     if (out_kind != TBK_OUT_F32 && out_kind != TBK_OUT_I8) return fail(TBK_ERR_INVALID, "unknown output kind %d", out_kind);
   }
   CUDA_TRY(cudaSetDevice(f->device));
-  if (f->quant) return run_quant(f, mode, d_rows, n_rows, ld, d_out, d_partial, d_leaf_ids, stream, slot);
+  if (f->quant) return run_quant(f, mode, d_rows, n_rows, ld, d_out, out_kind, d_partial, d_leaf_ids, stream, slot);
   if (f->deep) return run_deep(f, mode, d_rows, n_rows, ld, d_out, d_partial, d_leaf_ids, stream, slot);
 
   tb::ForestShape shape{pk.num_features, pk.num_classes, (int64_t)pk.groups.size(), pk.max_group_bytes,
@@ -687,10 +705,24 @@ int tbk_image_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, 
   // kernel applies; measured faster than the fp32 walk on single-output forests of up to 8 levels
   const bool batch_fits =
       (smem_limit - tb::kQBBarBytes - tb::kQRingBytes) / tb::quant_batch_tile_bytes(host.num_features) >= 4;
-  bool want_quant = (bits == 16 && max_depth <= tb::kQuantMaxDepth) ||
-                    (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits) ||
+  // (multiclass forests only on request: the key layout walks them in one tree chunk and
+  // keeps no per-class partial sums, which small batches and tree shards need).  Forests whose
+  // thresholds are mostly whole numbers were trained on integer-valued features: their rows
+  // tie with thresholds all the time (measured: one comparison in 16 on 4-bit features, the
+  // key walk then runs at a quarter of the fp32 walk's rate), so they keep fp32 tiles too.
+  int64_t splits = 0, whole = 0;
+#pragma omp parallel for reduction(+ : splits, whole) schedule(static) num_threads(tb::pack_threads())
+  for (int64_t g = 0; g < host.num_nodes(); ++g)
+    if (!host.is_leaf(g)) {
+      ++splits;
+      whole += host.thr[g] == std::floor(host.thr[g]) ? 1 : 0;
+    }
+  const bool integer_features = splits > 0 && 2 * whole > splits;
+  bool want_quant = (bits == 16 && max_depth <= tb::kQuantMaxDepth && (host.num_classes == 0 || batch_fits)) ||
+                    (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits &&
+                     host.num_classes == 0) ||
                     (bits == 0 && rep == TBK_REP_AUTO && ts == 1 && host.num_classes == 0 && batch_fits &&
-                     max_depth <= tb::kQuantMaxDepth);
+                     max_depth <= tb::kQuantMaxDepth && !integer_features);
   if (want_quant) {
     std::string qerr = tb::pack_quant(host, &im.qf);
     if (qerr.empty() && quant_smem_bytes(host.num_features) > smem_limit)
@@ -727,9 +759,10 @@ int tbk_image_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, 
     }
   }
   if (bits == 16 && !want_quant)
-    return fail(TBK_ERR_UNSUPPORTED, "16-bit feature keys cover single-output forests of at most %d levels, tile size 1 "
-                                     "(this forest: %d levels, %d classes, tile size %d)",
-                tb::kDeepMaxDepth, max_depth, host.num_classes, ts);
+    return fail(TBK_ERR_UNSUPPORTED, "16-bit feature keys cover single-output forests of at most %d levels and multiclass "
+                                     "forests of at most %d levels over narrow rows, tile size 1 "
+                                     "(this forest: %d levels, %d classes, %d features, tile size %d)",
+                tb::kDeepMaxDepth, tb::kQuantMaxDepth, max_depth, host.num_classes, host.num_features, ts);
   if (rep == TBK_REP_AUTO) rep = TBK_REP_SPARSE;
   if (want_quant) {
     im.kind = tb::PackedImage::kQuant;
@@ -858,6 +891,7 @@ int tbk_forest_create_from_image(const tbk_image *img, const tbk_schedule *sched
     f->packed.representation = tb::kReorg;
     f->packed.tile_size = 1;
     f->packed.num_features = q.num_features;
+    f->packed.num_classes = q.num_classes;
     f->packed.transform = q.transform;
     f->packed.initial_value = q.initial_value;
     f->packed.num_trees = q.num_trees;
@@ -866,6 +900,25 @@ int tbk_forest_create_from_image(const tbk_image *img, const tbk_schedule *sched
     int urc = upload_key_planes(f, q.node_plane, q.leaf_plane, q.exact_plane, q.orig_leaf, q.groups, q.tree_index,
                                 q.lo, q.scale, q.num_features, true);
     if (urc != TBK_OK) return bail(urc);
+    if (q.num_classes > 0) {
+      // every class goes to one of the two walker sets, whichever has fewer groups so far;
+      // within a set the groups keep their order, so its classes come in increasing order
+      const size_t G = q.groups.size();
+      std::vector<int32_t> lists(2 * G, 0);
+      int32_t count[2] = {0, 0};
+      for (size_t g = 0; g < G;) {
+        size_t e = g;
+        while (e < G && q.group_class[e] == q.group_class[g]) ++e;
+        const int s = count[1] < count[0] ? 1 : 0;
+        for (; g < e; ++g) lists[(size_t)s * G + count[s]++] = (int32_t)g;
+      }
+      f->qset_count[0] = count[0];
+      f->qset_count[1] = count[1];
+      CUDA_TRY_F(cudaMalloc(&f->d_qset_groups, lists.size() * 4));
+      CUDA_TRY_F(cudaMemcpy(f->d_qset_groups, lists.data(), lists.size() * 4, cudaMemcpyHostToDevice));
+      CUDA_TRY_F(cudaMalloc(&f->d_qgroup_class, G * 4));
+      CUDA_TRY_F(cudaMemcpy(f->d_qgroup_class, q.group_class.data(), G * 4, cudaMemcpyHostToDevice));
+    }
     // host copies of the big planes are no longer needed
     std::vector<uint32_t>().swap(f->qf.node_plane);
     std::vector<float>().swap(f->qf.leaf_plane);
@@ -931,6 +984,8 @@ int tbk_forest_free(tbk_forest *f) {
   cudaFree(f->d_qorig);
   cudaFree(f->d_qgroups);
   cudaFree(f->d_qtree_index);
+  cudaFree(f->d_qset_groups);
+  cudaFree(f->d_qgroup_class);
   cudaFree(f->d_qlo);
   cudaFree(f->d_qscale);
   cudaFree(f->d_ties);

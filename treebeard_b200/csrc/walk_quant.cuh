@@ -76,6 +76,13 @@ struct QuantParams {
   float initial_value;
   int32_t vec4_ok;
   int32_t tiles_per_batch;       // narrow-row kernel (walk_quant_batch.cuh): 32-row tiles staged together
+  // multiclass forests (narrow-row kernel only): the groups each walker set takes, in walking
+  // order ([2][num_groups], set_count of them used; null = groups set, set + 2, ...), the class
+  // of every group, and the output type (0 = fp32 class id, 1 = int8 class id)
+  const int32_t *set_groups;
+  int32_t set_count[2];
+  const int32_t *group_class;
+  int32_t num_classes, out_kind;
   int32_t skip_first_copy;       // failure drill: the first piece's copy is never issued, so its wait expires
   uint32_t wait_tries;           // polls before a wait gives up (0 = kQWaitTries)
   int32_t *status;

@@ -15,7 +15,12 @@
 //  * 2 leaf warps, one per set: the walkers drop their leaf numbers into [tile][column][row]
 //    byte tables (two per set, alternating by group); the leaf warp gathers the leaf values
 //    from L2, sums a group pairwise and keeps one running sum per tile.  Leaf warp 1 hands its
-//    sums to leaf warp 0, which writes the batch's results.
+//    sums to leaf warp 0, which writes the batch's results.  Multiclass forests: a group
+//    belongs to one class and every class to one set, whose leaf warp meets the classes in
+//    increasing order; it keeps the running sum of the current class and, when the class
+//    changes, updates the best class so far (ties go to the higher class index, the rule of
+//    the reference's generated arg-max, src/reduction/LowerReduceOps.cpp:148-189); leaf warp 0
+//    merges the two sets' winners and writes the class id.
 //  * 2 ring producers, one per set: three 16 KB slots per set, cp.async.bulk + mbarrier.
 // Ties between 15-bit keys are flagged by the walk and re-walked on the exact fp32 values, as
 // in walk_quant.cuh.  Every wait is bounded; a wait that gives up ends the launch with status 4.
@@ -32,15 +37,16 @@ constexpr int kQBThreads = 32 * (kQBWalkers + kQBLeafWarps + kQBProducers);
 constexpr int kQBMaxTiles = 16;   // tiles per batch: one per walker warp when the batch is staged
 constexpr int kQBBarBytes = 512;
 // shared memory: barriers, the ring, then per tile of the batch its leaf-number tables
-// (2 sets x 2 tables x 1 KB), the row sums leaf warp 1 hands over (128 B) and its key tile
+// (2 sets x 2 tables x 1 KB), what leaf warp 1 hands over (row sums, or best class sums and
+// their classes: 256 B) and its key tile
 __host__ __device__ constexpr int quant_batch_tile_bytes(int num_features) {
-  return 4 * 1024 + 128 + quant_key_tile_bytes(num_features);
+  return 4 * 1024 + 256 + quant_key_tile_bytes(num_features);
 }
 __host__ __device__ constexpr int quant_batch_smem_bytes(int num_features, int tiles) {
   return kQBBarBytes + kQRingBytes + tiles * quant_batch_tile_bytes(num_features);
 }
 
-template <int UD, bool LEAF_IDS>
+template <int UD, bool LEAF_IDS, bool MULTI>
 __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31;
@@ -63,7 +69,7 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
   const uint32_t ltab0_s = bars_s + kQBBarBytes + 6 * kQPiece;   // [set][table][tile][column][row] bytes
   const uint32_t ltab_s = ltab0_s + (uint32_t)set * 2u * (uint32_t)R * 1024u;
   const uint32_t sums1_s = ltab0_s + 4u * (uint32_t)R * 1024u;   // [tile][row] floats
-  const uint32_t keys_s = sums1_s + (uint32_t)R * 128u;          // [tile] key tiles
+  const uint32_t keys_s = sums1_s + (uint32_t)R * 256u;          // [tile] key tiles
 
   const long long num_tiles = (p.n_rows + 31) / 32;
   const long long num_batches = (num_tiles + R - 1) / R;
@@ -71,7 +77,9 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
   const int g0 = blockIdx.y * p.groups_per_chunk;
   const int g1 = min(p.num_groups, g0 + p.groups_per_chunk);
   const int NG = g1 - g0;
-  const int NGs = (NG - set + 1) / 2; // groups set, set + 2, ... of the chunk
+  // the set's groups: set, set + 2, ... of the chunk; whole classes of a multiclass forest
+  const int NGs = MULTI ? p.set_count[set] : (NG - set + 1) / 2;
+  auto group_index = [&](int k) { return MULTI ? p.set_groups[set * p.num_groups + k] : 2 * k + set; };
   const int P = 2 * NGs;              // pieces of this set per batch
   const int NP = (F + 2) / 2;         // feature pairs = lines of a key tile
 
@@ -110,7 +118,7 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
       for (int piece = 0; piece < P && ok; ++piece) {
         if (round > 0) ok = wait(empty_s + 8u * (uint32_t)slot, (round - 1u) & 1u);
         if (ok && lane == 0 && !(p.skip_first_copy && it == 0 && piece == 0)) {
-          const uint2 gm = group_of(2 * (piece >> 1) + set);
+          const uint2 gm = group_of(group_index(piece >> 1));
           const uint32_t hs = 1u << (gm.y - 1); // slots per piece
           const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
           uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw) + set * 3 + slot;
@@ -131,11 +139,38 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
       const long long batch = blockIdx.x + (long long)it * gridDim.x;
       const long long row0 = batch * R * 32 + lane;
       float sums[kQBMaxTiles];
+      [[maybe_unused]] float best[kQBMaxTiles];  // multiclass: the largest class sum so far and its class
+      [[maybe_unused]] int best_class[kQBMaxTiles];
+      [[maybe_unused]] int cur_class = -1;
 #pragma unroll
-      for (int r = 0; r < kQBMaxTiles; ++r) sums[r] = 0.f;
+      for (int r = 0; r < kQBMaxTiles; ++r) {
+        sums[r] = 0.f;
+        if constexpr (MULTI) {
+          best[r] = -INFINITY;
+          best_class[r] = 0;
+        }
+      }
+      // the class whose sum has been running is complete: it wins against a smaller or equal best
+      auto fold = [&]() {
+#pragma unroll
+        for (int r = 0; r < kQBMaxTiles; ++r) {
+          if (sums[r] >= best[r]) {
+            best[r] = sums[r];
+            best_class[r] = cur_class;
+          }
+          sums[r] = 0.f;
+        }
+      };
       for (int k = 0; k < NGs && ok; ++k, ++kk) {
-        const int gi = 2 * k + set;
+        const int gi = group_index(k);
         const uint2 gm = group_of(gi);
+        if constexpr (MULTI && !LEAF_IDS) {
+          const int cls = p.group_class[g0 + gi];
+          if (cls != cur_class) {
+            if (cur_class >= 0) fold();
+            cur_class = cls;
+          }
+        }
         const uint32_t slots = 2u << (gm.y - 1);
         ok = wait(table_s + 8u * (kk & 1u), (kk >> 1) & 1u);
         if (!ok) break;
@@ -177,7 +212,44 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
         if (lane == 0) mbar_arrive(table_free_s + 8u * (kk & 1u)); // every tile's table has been read
       }
       if (!ok) break;
-      if constexpr (!LEAF_IDS) {
+      if constexpr (MULTI && !LEAF_IDS) {
+        if (cur_class >= 0) fold();
+        // the batch's results: leaf warp 1 hands its best class to leaf warp 0
+        if (set == 1) {
+          if (it > 0) ok = wait(sum_free_s, (uint32_t)(it - 1) & 1u);
+          if (!ok) break;
+#pragma unroll
+          for (int r = 0; r < kQBMaxTiles; ++r)
+            if (r < R) {
+              asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums1_s + (uint32_t)(r * 64 + lane) * 4u), "f"(best[r]) : "memory");
+              asm volatile("st.shared.u32 [%0], %1;" ::"r"(sums1_s + (uint32_t)(r * 64 + 32 + lane) * 4u), "r"(best_class[r]) : "memory");
+            }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sum_ready_s);
+        } else {
+          ok = wait(sum_ready_s, (uint32_t)it & 1u);
+          if (!ok) break;
+#pragma unroll
+          for (int r = 0; r < kQBMaxTiles; ++r)
+            if (r < R) {
+              const float b1 = lds_f32(sums1_s + (uint32_t)(r * 64 + lane) * 4u);
+              const int c1 = (int)lds_u32(sums1_s + (uint32_t)(r * 64 + 32 + lane) * 4u);
+              if (b1 > best[r] || (b1 == best[r] && c1 > best_class[r])) best_class[r] = c1;
+            }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sum_free_s);
+#pragma unroll
+          for (int r = 0; r < kQBMaxTiles; ++r) {
+            const long long row = row0 + r * 32;
+            if (r < R && row < p.n_rows) {
+              if (p.out_kind == 1)
+                reinterpret_cast<int8_t *>(p.out)[row] = (int8_t)best_class[r];
+              else
+                reinterpret_cast<float *>(p.out)[row] = (float)best_class[r];
+            }
+          }
+        }
+      } else if constexpr (!LEAF_IDS) {
         // the batch's results: leaf warp 1 hands its sums to leaf warp 0
         if (set == 1) {
           if (it > 0) ok = wait(sum_free_s, (uint32_t)(it - 1) & 1u);
@@ -252,7 +324,7 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
       if (!ok) break;
 
       for (int k = 0; k < NGs && ok; ++k, ++kk) {
-        const int gi = 2 * k + set;
+        const int gi = group_index(k);
         const uint2 gm = group_of(gi);
         const uint32_t depth = UD ? (uint32_t)UD : gm.y, hs = 1u << (depth - 1);
         // the two pieces of this group
