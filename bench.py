@@ -36,16 +36,22 @@ HBM_FALLBACK_GBS = 6650.0
 # proportion to the rows, so a launch's traffic is this figure times its rows.  Each figure
 # belongs to the kernel sources it was captured on: it is reported only while their hash
 # (kernel_source_hash) still matches.
-NCU_DRAM_BYTES_PER_ROW = {"c3": (8189.0, ""), "c2": (118.2, ""), "c4": (76.3, "")}
-KERNEL_SOURCES = ("walk_kernels.cuh", "walk_quant.cuh", "walk_deep.cuh", "tbk_api.cu")
+NCU_DRAM_BYTES_PER_ROW = {"c3": (8820.1, "1135f8192e2af30d"), "c2": (131.8, "1135f8192e2af30d")}
+KERNEL_SOURCES = ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh", "walk_deep.cuh")
 
 
 def kernel_source_hash():
+    """Hash of the kernel sources' CODE: comments and blank space do not count, so that an edit
+    of a comment does not disown an ncu figure."""
     import hashlib
+    import re
     h = hashlib.sha256()
     for name in KERNEL_SOURCES:
-        with open(os.path.join(ROOT, "treebeard_b200", "csrc", name), "rb") as fh:
-            h.update(fh.read())
+        with open(os.path.join(ROOT, "treebeard_b200", "csrc", name), "r", encoding="utf-8") as fh:
+            for line in fh:
+                code = re.sub(r"\s+", " ", line.split("//", 1)[0]).strip()
+                if code:
+                    h.update(code.encode() + b"\n")
     return h.hexdigest()[:16]
 
 

@@ -1,4 +1,5 @@
 #include "model_file.h"
+#include "checksum.h"
 #include "json.h"
 
 #include <cstdio>
@@ -14,15 +15,8 @@ namespace {
 const char kMagic[8] = {'T', 'B', 'B', '2', 'M', 'D', 'L', '\0'};
 const char kImageSection[8] = {'T', 'B', 'B', '2', 'S', 'E', 'C', '1'}; // opens the optional packed-image section
 
-// FNV-1a over the payload: catches truncated or edited files, not an integrity guarantee
-uint64_t fnv1a(uint64_t h, const void *data, size_t n) {
-  const unsigned char *p = static_cast<const unsigned char *>(data);
-  for (size_t i = 0; i < n; ++i) {
-    h ^= p[i];
-    h *= 1099511628211ull;
-  }
-  return h;
-}
+// checksum over the payload, chunk by chunk as it is written (checksum.h)
+uint64_t checksum(uint64_t h, const void *data, size_t n) { return hash_bytes(h, data, n); }
 
 struct Writer {
   std::FILE *fp;
@@ -31,7 +25,7 @@ struct Writer {
   void raw(const void *p, size_t n) {
     if (n == 0) return;
     if (std::fwrite(p, 1, n, fp) != n) ok = false;
-    hash = fnv1a(hash, p, n);
+    hash = checksum(hash, p, n);
   }
   template <typename T> void pod(const T &v) { raw(&v, sizeof(T)); }
   template <typename T> void vec(const std::vector<T> &v) {
@@ -56,7 +50,7 @@ struct Reader {
       return;
     }
     remaining -= n;
-    hash = fnv1a(hash, p, n);
+    hash = checksum(hash, p, n);
   }
   template <typename T> T pod() {
     T v{};

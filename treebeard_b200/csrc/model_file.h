@@ -37,7 +37,7 @@ struct ModelFileOptions {
   std::string representation; // "gpu_sparse" | "gpu_array" | "gpu_reorg" | "" (process default)
 };
 
-constexpr uint32_t kModelFileVersion = 1;
+constexpr uint32_t kModelFileVersion = 2;
 
 // Each returns an empty string on success, else the reason.  `image`: the serialised packed
 // image to append (may be null or empty) / where to put the one found (may be null; left

@@ -1,4 +1,5 @@
 #include "packed_image.h"
+#include "checksum.h"
 
 #include <cstring>
 #include <type_traits>
@@ -9,18 +10,14 @@ namespace {
 
 const char kImageMagic[8] = {'T', 'B', 'B', '2', 'I', 'M', 'G', '\0'};
 
-uint64_t fnv1a(const uint8_t *p, size_t n) {
-  uint64_t h = 14695981039346656037ull;
-  for (size_t i = 0; i < n; ++i) {
-    h ^= p[i];
-    h *= 1099511628211ull;
-  }
-  return h;
-}
+uint64_t checksum(const uint8_t *p, size_t n) { return hash_bytes(kHashSeed, p, n); }
 
 struct Out {
-  std::vector<uint8_t> *b;
+  std::vector<uint8_t> *b; // null: only count the bytes
+  uint64_t count = 0;
   void raw(const void *p, size_t n) {
+    count += n;
+    if (!b) return;
     const uint8_t *c = static_cast<const uint8_t *>(p);
     b->insert(b->end(), c, c + n);
   }
@@ -75,9 +72,8 @@ void put_key_forest_head(Out &o, int32_t num_features, int32_t transform, double
 
 } // namespace
 
-void serialize_image(const PackedImage &im, std::vector<uint8_t> *out) {
-  out->clear();
-  Out o{out};
+namespace {
+void put_image(const PackedImage &im, Out &o) {
   o.raw(kImageMagic, sizeof(kImageMagic));
   o.pod<uint32_t>(kPackedImageVersion);
   o.pod(im.kind);
@@ -134,7 +130,21 @@ void serialize_image(const PackedImage &im, std::vector<uint8_t> *out) {
     o.vec(q.lo);
     o.vec(q.scale);
   }
-  const uint64_t sum = fnv1a(out->data(), out->size());
+}
+} // namespace
+
+uint64_t serialized_image_size(const PackedImage &im) {
+  Out o{nullptr};
+  put_image(im, o);
+  return o.count + 8;
+}
+
+void serialize_image(const PackedImage &im, std::vector<uint8_t> *out) {
+  out->clear();
+  out->reserve(serialized_image_size(im));
+  Out o{out};
+  put_image(im, o);
+  const uint64_t sum = checksum(out->data(), out->size());
   o.pod(sum);
 }
 
@@ -142,7 +152,7 @@ std::string deserialize_image(const uint8_t *data, uint64_t size, PackedImage *i
   if (size < sizeof(kImageMagic) + 4 + 8) return "packed image: too short";
   uint64_t sum = 0;
   std::memcpy(&sum, data + size - 8, 8);
-  if (sum != fnv1a(data, size - 8)) return "packed image: checksum mismatch";
+  if (sum != checksum(data, size - 8)) return "packed image: checksum mismatch";
   In in{data, size - 8};
   char magic[sizeof(kImageMagic)];
   in.raw(magic, sizeof(magic));

@@ -33,6 +33,7 @@ struct PackedImage {
 constexpr uint32_t kPackedImageVersion = 3; // changes whenever a packer's output does
 
 void serialize_image(const PackedImage &im, std::vector<uint8_t> *out);
+uint64_t serialized_image_size(const PackedImage &im); // without serialising
 // Empty string on success.  Checks the version, sizes and a checksum; a stale or damaged
 // image is an error, never a partially filled structure.
 std::string deserialize_image(const uint8_t *data, uint64_t size, PackedImage *im);

@@ -788,12 +788,12 @@ int tbk_image_free(tbk_image *img) {
 
 int tbk_image_serialize(const tbk_image *img, void *buffer, uint64_t capacity, uint64_t *size) {
   if (!img || !size) return fail(TBK_ERR_INVALID, "null argument");
+  *size = tb::serialized_image_size(img->im);
+  if (!buffer) return TBK_OK;
+  if (capacity < *size) return fail(TBK_ERR_INVALID, "buffer of %llu bytes, the image needs %llu",
+                                    (unsigned long long)capacity, (unsigned long long)*size);
   std::vector<uint8_t> bytes;
   tb::serialize_image(img->im, &bytes);
-  *size = bytes.size();
-  if (!buffer) return TBK_OK;
-  if (capacity < bytes.size()) return fail(TBK_ERR_INVALID, "buffer of %llu bytes, the image needs %llu",
-                                           (unsigned long long)capacity, (unsigned long long)bytes.size());
   std::memcpy(buffer, bytes.data(), bytes.size());
   return TBK_OK;
 }

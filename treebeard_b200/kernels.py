@@ -247,16 +247,19 @@ class PackedImage:
     @classmethod
     def from_bytes(cls, data: bytes):
         h = ctypes.c_void_p()
-        buf = (ctypes.c_char * len(data)).from_buffer_copy(data)
-        _check(lib().tbk_image_deserialize(buf, len(data), ctypes.byref(h)))
+        view = ctypes.c_char_p(data) if isinstance(data, bytes) else (ctypes.c_char * len(data)).from_buffer(data)
+        _check(lib().tbk_image_deserialize(ctypes.cast(view, ctypes.c_void_p), len(data), ctypes.byref(h)))
         return cls(h)
 
-    def to_bytes(self) -> bytes:
+    def to_bytes(self):
+        """The serialised image (bytes; a bytearray above 64 MiB, to spare a copy)."""
         n = ctypes.c_uint64()
         _check(lib().tbk_image_serialize(self._h, None, 0, ctypes.byref(n)))
-        buf = (ctypes.c_char * n.value)()
-        _check(lib().tbk_image_serialize(self._h, buf, n.value, ctypes.byref(n)))
-        return bytes(buf)
+        buf = bytearray(n.value)
+        view = (ctypes.c_char * n.value).from_buffer(buf)
+        _check(lib().tbk_image_serialize(self._h, view, n.value, ctypes.byref(n)))
+        del view
+        return bytes(buf) if n.value < (1 << 26) else buf
 
     def matches(self, smem_limit: int = 0, **schedule) -> bool:
         sched = make_schedule(**schedule)
