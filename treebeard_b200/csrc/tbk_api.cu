@@ -175,7 +175,7 @@ int quant_smem_bytes(int num_features) {
 
 // Tiles of 32 rows that the narrow-row kernel can stage together (0: the rows are too wide for it).
 int quant_batch_tiles(const tbk_forest *f, int num_features) {
-  const int room = f->max_smem_optin - tb::kQBBarBytes - tb::kQRingBytes;
+  const int room = f->max_smem_optin - tb::kQBBarBytes - tb::kQBRingBytes;
   const int fit = room / tb::quant_batch_tile_bytes(num_features);
   return fit >= 4 ? std::min(fit, tb::kQBMaxTiles) : 0;
 }
@@ -704,7 +704,7 @@ int tbk_image_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, 
   // narrow rows: the key tiles of at least four 32-row tiles fit beside the ring, so the batch
   // kernel applies; measured faster than the fp32 walk on single-output forests of up to 8 levels
   const bool batch_fits =
-      (smem_limit - tb::kQBBarBytes - tb::kQRingBytes) / tb::quant_batch_tile_bytes(host.num_features) >= 4;
+      (smem_limit - tb::kQBBarBytes - tb::kQBRingBytes) / tb::quant_batch_tile_bytes(host.num_features) >= 4;
   // (multiclass forests only on request: the key layout walks them in one tree chunk and
   // keeps no per-class partial sums, which small batches and tree shards need).  Forests whose
   // thresholds are mostly whole numbers were trained on integer-valued features: their rows

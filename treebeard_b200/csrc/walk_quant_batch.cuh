@@ -21,7 +21,8 @@
 //    changes, updates the best class so far (ties go to the higher class index, the rule of
 //    the reference's generated arg-max, src/reduction/LowerReduceOps.cpp:148-189); leaf warp 0
 //    merges the two sets' winners and writes the class id.
-//  * 2 ring producers, one per set: three 16 KB slots per set, cp.async.bulk + mbarrier.
+//  * 2 ring producers, one per set: four 16 KB slots per set (the two pieces of the group
+//    being walked and both pieces of the next one), cp.async.bulk + mbarrier.
 // Ties between 15-bit keys are flagged by the walk and re-walked on the exact fp32 values, as
 // in walk_quant.cuh.  Every wait is bounded; a wait that gives up ends the launch with status 4.
 //
@@ -36,6 +37,8 @@ constexpr int kQBWalkers = 16, kQBLeafWarps = 2, kQBProducers = 2;
 constexpr int kQBThreads = 32 * (kQBWalkers + kQBLeafWarps + kQBProducers);
 constexpr int kQBMaxTiles = 16;   // tiles per batch: one per walker warp when the batch is staged
 constexpr int kQBBarBytes = 512;
+constexpr int kQBSlots = 4;       // ring slots per set
+constexpr int kQBRingBytes = 2 * kQBSlots * 16384;
 // shared memory: barriers, the ring, then per tile of the batch its leaf-number tables
 // (2 sets x 2 tables x 1 KB), what leaf warp 1 hands over (row sums, or best class sums and
 // their classes: 256 B) and its key tile
@@ -43,7 +46,7 @@ __host__ __device__ constexpr int quant_batch_tile_bytes(int num_features) {
   return 4 * 1024 + 256 + quant_key_tile_bytes(num_features);
 }
 __host__ __device__ constexpr int quant_batch_smem_bytes(int num_features, int tiles) {
-  return kQBBarBytes + kQRingBytes + tiles * quant_batch_tile_bytes(num_features);
+  return kQBBarBytes + kQBRingBytes + tiles * quant_batch_tile_bytes(num_features);
 }
 
 template <int UD, bool LEAF_IDS, bool MULTI>
@@ -58,15 +61,15 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
   const int F = p.num_features, R = p.tiles_per_batch;
   const int KT = quant_key_tile_bytes(F);
   const uint32_t bars_s = smem_u32(smem_raw);
-  // barriers: full[set][3] @0, empty[set][3] @48, table_full[set][2] @96, table_free[set][2] @128,
-  // keys_free @160, keys_ready @168, sum_ready @176, sum_free @184
-  const uint32_t full_s = bars_s + (uint32_t)set * 24u, empty_s = bars_s + 48u + (uint32_t)set * 24u;
-  const uint32_t table_s = bars_s + 96u + (uint32_t)set * 16u, table_free_s = bars_s + 128u + (uint32_t)set * 16u;
-  const uint32_t keys_free_s = bars_s + 160u, keys_ready_s = bars_s + 168u;
-  const uint32_t sum_ready_s = bars_s + 176u, sum_free_s = bars_s + 184u;
-  unsigned char *ring = smem_raw + kQBBarBytes + (size_t)set * 3 * kQPiece;
+  // barriers: full[set][4] @0, empty[set][4] @64, table_full[set][2] @128, table_free[set][2] @160,
+  // keys_free @192, keys_ready @200, sum_ready @208, sum_free @216
+  const uint32_t full_s = bars_s + (uint32_t)set * 32u, empty_s = bars_s + 64u + (uint32_t)set * 32u;
+  const uint32_t table_s = bars_s + 128u + (uint32_t)set * 16u, table_free_s = bars_s + 160u + (uint32_t)set * 16u;
+  const uint32_t keys_free_s = bars_s + 192u, keys_ready_s = bars_s + 200u;
+  const uint32_t sum_ready_s = bars_s + 208u, sum_free_s = bars_s + 216u;
+  unsigned char *ring = smem_raw + kQBBarBytes + (size_t)set * kQBSlots * kQPiece;
   const uint32_t ring_s = smem_u32(ring);
-  const uint32_t ltab0_s = bars_s + kQBBarBytes + 6 * kQPiece;   // [set][table][tile][column][row] bytes
+  const uint32_t ltab0_s = bars_s + kQBBarBytes + (uint32_t)kQBRingBytes;   // [set][table][tile][column][row] bytes
   const uint32_t ltab_s = ltab0_s + (uint32_t)set * 2u * (uint32_t)R * 1024u;
   const uint32_t sums1_s = ltab0_s + 4u * (uint32_t)R * 1024u;   // [tile][row] floats
   const uint32_t keys_s = sums1_s + (uint32_t)R * 256u;          // [tile] key tiles
@@ -85,14 +88,14 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
 
   if (tid == 0) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
-    for (int i = 0; i < 6; ++i) mbar_init(bars + i, 1);             // full: the copy's bytes
-    for (int i = 6; i < 12; ++i) mbar_init(bars + i, kQSetWarps);   // empty: one arrival per walker warp of the set
-    for (int i = 12; i < 16; ++i) mbar_init(bars + i, kQSetWarps);  // table_full: every walker of the set has written
-    for (int i = 16; i < 20; ++i) mbar_init(bars + i, 1);           // table_free: the leaf warp has read the table
-    mbar_init(bars + 20, kQBWalkers);                               // keys_free: the previous batch is walked
-    mbar_init(bars + 21, kQBWalkers);                               // keys_ready: the batch's keys are staged
-    mbar_init(bars + 22, 1);                                        // sum_ready: leaf warp 1 has written its sums
-    mbar_init(bars + 23, 1);                                        // sum_free: leaf warp 0 has read them
+    for (int i = 0; i < 8; ++i) mbar_init(bars + i, 1);             // full: the copy's bytes
+    for (int i = 8; i < 16; ++i) mbar_init(bars + i, kQSetWarps);   // empty: one arrival per walker warp of the set
+    for (int i = 16; i < 20; ++i) mbar_init(bars + i, kQSetWarps);  // table_full: every walker of the set has written
+    for (int i = 20; i < 24; ++i) mbar_init(bars + i, 1);           // table_free: the leaf warp has read the table
+    mbar_init(bars + 24, kQBWalkers);                               // keys_free: the previous batch is walked
+    mbar_init(bars + 25, kQBWalkers);                               // keys_ready: the batch's keys are staged
+    mbar_init(bars + 26, 1);                                        // sum_ready: leaf warp 1 has written its sums
+    mbar_init(bars + 27, 1);                                        // sum_free: leaf warp 0 has read them
     fence_barrier_init();
   }
   __syncthreads();
@@ -111,7 +114,7 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
 
   if (producer) {
     // ---- the set's ring producer: piece q (upper levels of a group for even q, its bottom
-    // level for odd q) goes to slot q mod 3 once every walker of the set has released the slot
+    // level for odd q) goes to slot q mod 4 once every walker of the set has released the slot
     int slot = 0;
     uint32_t round = 0;
     for (int it = 0; it < my_batches && ok; ++it) {
@@ -121,11 +124,11 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
           const uint2 gm = group_of(group_index(piece >> 1));
           const uint32_t hs = 1u << (gm.y - 1); // slots per piece
           const size_t off = ((size_t)gm.x + ((piece & 1) ? hs : 0u)) * 32;
-          uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw) + set * 3 + slot;
+          uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw) + set * kQBSlots + slot;
           mbar_expect_tx(bar, hs * 128u);
           bulk_g2s_hint(ring + (size_t)slot * kQPiece, p.node_plane + off, hs * 128u, bar, keep);
         }
-        if (++slot == 3) {
+        if (++slot == kQBSlots) {
           slot = 0;
           ++round;
         }
@@ -329,9 +332,9 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
         const uint32_t depth = UD ? (uint32_t)UD : gm.y, hs = 1u << (depth - 1);
         // the two pieces of this group
         const uint32_t su = (uint32_t)slot, pu = parity;
-        if (++slot == 3) { slot = 0; parity ^= 1u; }
+        if (++slot == kQBSlots) { slot = 0; parity ^= 1u; }
         const uint32_t sb = (uint32_t)slot, pb = parity;
-        if (++slot == 3) { slot = 0; parity ^= 1u; }
+        if (++slot == kQBSlots) { slot = 0; parity ^= 1u; }
         uint32_t root[4], bot[4], cu[4], cx[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
