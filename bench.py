@@ -34,19 +34,20 @@ HBM_FALLBACK_GBS = 6650.0
 # DRAM bytes per row (dram__bytes_read.sum + dram__bytes_write.sum) of the walk kernel, from
 # one ncu capture per workload on a reduced batch (see profiles/); traffic grows in
 # proportion to the rows, so a launch's traffic is this figure times its rows.  Each figure
-# belongs to the kernel sources it was captured on: it is reported only while their hash
-# (kernel_source_hash) still matches.
-NCU_DRAM_BYTES_PER_ROW = {"c3": (8820.1, "1135f8192e2af30d"), "c2": (131.8, "1135f8192e2af30d")}
-KERNEL_SOURCES = ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh", "walk_deep.cuh")
+# belongs to the kernel sources it was captured on: it is reported only while the hash of the
+# code of the headers that make up the workload's kernel (kernel_source_hash) still matches.
+KERNEL_SOURCES = {"c3": ("walk_kernels.cuh", "walk_quant.cuh"),
+                  "c2": ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh")}
+NCU_DRAM_BYTES_PER_ROW = {"c3": (8820.1, "600f2104e11475ec"), "c2": (131.8, "ac6e56db88274caf")}
 
 
-def kernel_source_hash():
-    """Hash of the kernel sources' CODE: comments and blank space do not count, so that an edit
-    of a comment does not disown an ncu figure."""
+def kernel_source_hash(workload):
+    """Hash of the CODE of the workload's kernel headers: comments and blank space do not
+    count, so that an edit of a comment does not disown an ncu figure."""
     import hashlib
     import re
     h = hashlib.sha256()
-    for name in KERNEL_SOURCES:
+    for name in KERNEL_SOURCES.get(workload, ()):
         with open(os.path.join(ROOT, "treebeard_b200", "csrc", name), "r", encoding="utf-8") as fh:
             for line in fh:
                 code = re.sub(r"\s+", " ", line.split("//", 1)[0]).strip()
@@ -60,7 +61,7 @@ def ncu_traffic(workload, n_rows, custom):
     if custom or workload not in NCU_DRAM_BYTES_PER_ROW:
         return None, "no ncu capture for this workload"
     per_row, captured_on = NCU_DRAM_BYTES_PER_ROW[workload]
-    now = kernel_source_hash()
+    now = kernel_source_hash(workload)
     if captured_on != now:
         return None, f"kernel sources changed since the ncu capture (captured on {captured_on or 'an earlier build'}, now {now})"
     return per_row * n_rows, "ncu dram bytes per row on a reduced batch x rows (profiles/)"
