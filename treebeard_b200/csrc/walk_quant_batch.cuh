@@ -352,44 +352,40 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
           ok = wait(table_free_s + 8u * (kk & 1u), ((kk >> 1) - 1u) & 1u);
           if (!ok) break;
         }
-        const uint32_t buf = (kk & 1u) * (uint32_t)R * 1024u;
+        uint32_t keys_lane = keys_s + (uint32_t)lane * 4u, drop[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) drop[c] = drop0[c] + (kk & 1u) * (uint32_t)R * 1024u;
 #pragma unroll 1
         for (int r = 0; r < R; ++r) {
-          const uint32_t keys_lane = keys_s + (uint32_t)r * (uint32_t)KT + (uint32_t)lane * 4u;
-          const long long row = row0 + r * 32 + lane;
-          const float *rowp = p.rows + (row < p.n_rows ? row : 0) * p.ld;
           uint32_t A[4], ties = 0;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) A[c] = bot[c];
           if (depth >= 2) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) A[c] = root[c];
             if constexpr (UD >= 2)
-              quant_upper4<UD>(A, ties, keys_lane, cu, cx);
+              quant_full4<UD>(A, ties, keys_lane, cu, cx, bot);
             else
-              quant_upper4_any(depth, A, ties, keys_lane, cu, cx);
-            if (ties) { // rare: the tied column is walked again on exact values
+              quant_full4_any(depth, A, ties, keys_lane, cu, cx, bot);
+          } else {
 #pragma unroll
-              for (int c = 0; c < 4; ++c)
-                if (ties & (1u << c)) {
-                  A[c] = bot[c] + 128u * quant_upper_exact(root[c], keys_lane, p.exact_plane, gm.x, depth, col[c], rowp);
-                  ++tie_count;
-                }
-              ties = 0;
-            }
+            for (int c = 0; c < 4; ++c) A[c] = bot[c];
+            quant_bottom4(A, ties, keys_lane, bot);
           }
-          quant_bottom4(A, ties, keys_lane, bot);
-          if (ties) {
+          if (ties) { // rare: a tied column is walked again, exact values deciding the tied comparisons
+            const long long row = row0 + r * 32 + lane;
+            const float *rowp = p.rows + (row < p.n_rows ? row : 0) * p.ld;
 #pragma unroll
             for (int c = 0; c < 4; ++c)
               if (ties & (1u << c)) {
-                A[c] = quant_bottom_exact(bot[c], A[c] >> 1, keys_lane, p.exact_plane, gm.x, depth, col[c], rowp);
+                const uint32_t j = depth >= 2 ? quant_upper_exact(root[c], keys_lane, p.exact_plane, gm.x, depth, col[c], rowp) : 0u;
+                A[c] = quant_bottom_exact(bot[c], j, keys_lane, p.exact_plane, gm.x, depth, col[c], rowp);
                 ++tie_count;
               }
           }
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop0[c] + buf + (uint32_t)r * 1024u), "r"(A[c]) : "memory");
+          for (int c = 0; c < 4; ++c) asm volatile("st.shared.u8 [%0], %1;" ::"r"(drop[c]), "r"(A[c]) : "memory");
+          keys_lane += (uint32_t)KT;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) drop[c] += 1024u;
         }
         __syncwarp();
         if (elected) {
