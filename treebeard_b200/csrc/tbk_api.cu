@@ -328,7 +328,7 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
 bool deep_plan(int num_features, int max_depth, int smem_limit, int *row_warps, int *slots) {
   const int64_t slot = 4ll << std::max(max_depth, tb::kDeepMinDepth);
   // four slots hold the node planes of the pair being walked and of the next one
-  for (int rw = 32; rw >= 4; rw -= 2) {
+  for (int rw = 30; rw >= 4; rw -= 2) { // (the block has one more warp, the ring producer)
     const int64_t keys = (int64_t)(num_features + 1) * 64 * rw;
     const int64_t room = (int64_t)smem_limit - 128 - keys;
     const int64_t s = std::min<int64_t>(tb::kDeepMaxSlots, room / slot);
@@ -371,7 +371,7 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
   plan.cache_rows = 1;
   plan.stage_bytes = 4u << std::max(q.max_depth, tb::kDeepMinDepth);
   plan.smem_bytes = deep_smem_bytes(f);
-  plan.threads = 32 * rw;
+  plan.threads = 32 * (rw + 1); // row warps + the ring producer
   plan.grid_x = grid_x;
   f->last_plan = plan;
 
@@ -421,13 +421,13 @@ int run_deep(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int6
   p.skip_first_copy = f->expire_next_wait ? 1 : 0;
   p.wait_tries = f->expire_next_wait ? 2000u : 0u;
   f->expire_next_wait = false;
-  // up to 20 warps the compiler may use 96 registers per thread, beyond that 64
+  // up to 24 warps (row warps + producer) the compiler may use 80 registers per thread, beyond that 64
   // specialised for forests whose pairs all have 12 levels; generic otherwise
   using DeepKernel = void (*)(const tb::DeepParams);
-  const bool d12 = f->uniform_depth == 12, ids = mode == kLeafIds, small = plan.threads <= 640;
+  const bool d12 = f->uniform_depth == 12, ids = mode == kLeafIds, small = plan.threads <= 768;
   const DeepKernel kernel =
-      small ? (d12 ? (ids ? tb::tb_walk_deep_kernel<640, 12, true> : tb::tb_walk_deep_kernel<640, 12, false>)
-                   : (ids ? tb::tb_walk_deep_kernel<640, 0, true> : tb::tb_walk_deep_kernel<640, 0, false>))
+      small ? (d12 ? (ids ? tb::tb_walk_deep_kernel<768, 12, true> : tb::tb_walk_deep_kernel<768, 12, false>)
+                   : (ids ? tb::tb_walk_deep_kernel<768, 0, true> : tb::tb_walk_deep_kernel<768, 0, false>))
             : (d12 ? (ids ? tb::tb_walk_deep_kernel<1024, 12, true> : tb::tb_walk_deep_kernel<1024, 12, false>)
                    : (ids ? tb::tb_walk_deep_kernel<1024, 0, true> : tb::tb_walk_deep_kernel<1024, 0, false>));
   CUDA_TRY(cudaFuncSetAttribute((const void *)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_bytes));
@@ -879,7 +879,7 @@ int tbk_forest_create_from_image(const tbk_image *img, const tbk_schedule *sched
     std::vector<int32_t>().swap(q.orig_leaf);
     tb::LaunchPlan &pl = f->last_plan;
     pl.row_warps = f->deep_row_warps; pl.tree_threads = 1; pl.rows_per_lane = 1; pl.chunks = 1; pl.staged = 1; pl.cache_rows = 1;
-    pl.stage_bytes = 4u << std::max(q.max_depth, tb::kDeepMinDepth); pl.smem_bytes = deep_smem_bytes(f); pl.threads = 32 * f->deep_row_warps;
+    pl.stage_bytes = 4u << std::max(q.max_depth, tb::kDeepMinDepth); pl.smem_bytes = deep_smem_bytes(f); pl.threads = 32 * (f->deep_row_warps + 1);
     *out = f;
     return TBK_OK;
   }

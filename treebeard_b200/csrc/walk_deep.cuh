@@ -4,9 +4,11 @@
 // the whole forest.  Lane = row: every thread walks its own row through BOTH trees of a
 // pair in lock-step (two independent dependence chains per thread), so all threads of the
 // block read the same two node planes.  The node planes stream through a ring of whole-tree
-// pieces (16 KB each at 12 levels) filled by cp.async.bulk copies that different warps
-// issue, the next pair's always in flight while a pair is walked; one block-wide barrier
-// per pair frees its two slots.  Leaf values are read straight from L2 (32 scattered
+// pieces (16 KB each at 12 levels) filled by cp.async.bulk copies that one extra PRODUCER warp
+// issues, the next pair's always in flight while a pair is walked; a row warp frees a slot
+// with one arrival on the slot's "empty" mbarrier and the producer refills it when all row
+// warps have arrived, so the row warps never meet at a block barrier and may drift apart by a
+// pair.  Leaf values are read straight from L2 (32 scattered
 // sectors per warp whatever the layout) and consumed one pair later.  Sums stay in the
 // owning thread's register: there is no cross-thread reduction.
 //
@@ -122,10 +124,10 @@ template <int MAX_THREADS, int UD, bool LEAF_IDS>
 __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const DeepParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int RW = blockDim.x >> 5;
+  const int RW = (blockDim.x >> 5) - 1; // row warps; the last warp is the ring producer
   const int F = p.num_features;
   const int S = p.ring_slots;
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw); // [S]
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw); // [S], then empty[S]
   unsigned char *ring = smem_raw + 128;
   const uint32_t ring_s = smem_u32(ring);
   const uint32_t keys_s = ring_s + (uint32_t)S * p.slot_bytes;
@@ -141,9 +143,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
 
   if (tid == 0) {
     for (int i = 0; i < S; ++i) mbar_init(&full[i], 1);
+    for (int i = 0; i < S; ++i) mbar_init(&full[S + i], RW); // empty: one arrival per row warp
     fence_barrier_init();
   }
   __syncthreads();
+  const uint32_t full_s = smem_u32(full), empty_s = full_s + 8u * (uint32_t)S;
+  const uint32_t tries = p.wait_tries ? p.wait_tries : kQWaitTries;
 
   // piece 2k + j of the block: node plane of tree j of pair k.  Pieces are consumed in order,
   // so slots and barrier phases advance by counters (S and RW are run-time values: no
@@ -155,9 +160,23 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
     mbar_expect_tx(bar, gm.slots * 4u);
     bulk_g2s(ring + (size_t)slot * p.slot_bytes, p.node_plane + off, gm.slots * 4u, bar);
   };
-  if (lane == 0 && warp < S && warp < P && !(p.skip_first_copy && warp == 0)) issue(warp, warp);
-  if (RW < S && tid == 0)
-    for (int i = RW; i < S && i < P; ++i) issue(i, i);
+  if (warp == RW) {
+    // ---- the producer: piece q goes to slot q mod S, once every row warp has released
+    // the piece that was there
+    bool ok = true;
+    int slot = 0;
+    uint32_t round = 0;
+    for (int piece = 0; piece < P && ok; ++piece) {
+      if (round > 0) ok = mbar_wait_all_lanes(empty_s + 8u * (uint32_t)slot, (round - 1u) & 1u, tries);
+      if (ok && lane == 0 && !(p.skip_first_copy && piece == 0)) issue(piece, slot);
+      if (++slot == S) {
+        slot = 0;
+        ++round;
+      }
+    }
+    if (__syncthreads_or(!ok) && lane == 0) atomicExch(p.status, 4);
+    return;
+  }
 
   // ---- stage this thread's row as keys
   {
@@ -184,18 +203,15 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
   // fp32 rounding of the exact result (one conversion and one add per tree)
   double acc = 0.0;
   float pend0 = 0.f, pend1 = 0.f; // leaf values of the previous pair, on their way from L2
-  bool ok = true, failed = false;
+  bool ok = true;
   unsigned ties = 0;
   int slot = 0;          // ring slot of the next piece to consume
   uint32_t parity = 0;   // phase of that slot's barrier
-  int issuer = 0;        // warp that issues the next refill
-  int next_piece = S;    // next piece to issue
 
   // Takes the next piece: waits for it and returns its shared-memory address.
-  const uint32_t full_s = smem_u32(full);
   auto take = [&](int *slot_out) -> uint32_t {
     const int s = slot;
-    if (ok) ok = mbar_wait_all_lanes(full_s + 8u * (uint32_t)s, parity, p.wait_tries ? p.wait_tries : kQWaitTries);
+    if (ok) ok = mbar_wait_all_lanes(full_s + 8u * (uint32_t)s, parity, tries);
     *slot_out = s;
     if (++slot == S) {
       slot = 0;
@@ -204,7 +220,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
     return ring_s + (uint32_t)s * p.slot_bytes;
   };
 
-  for (int k = 0; k < g1 - g0; ++k) {
+  for (int k = 0; k < g1 - g0 && ok; ++k) {
     const DevQuantGroup gm = p.pairs[g0 + k];
     const uint32_t depth = UD ? (uint32_t)UD : gm.depth;
     uint32_t i0 = gm.slots, i1 = gm.slots;
@@ -242,18 +258,15 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
         if (t1 >= 0) p.leaf_ids[row * p.num_trees + t1] = p.orig_leaf[gm.elem_off + gm.slots + j1];
       }
     }
-    // One block-wide barrier per pair (it also carries a wait failure to every thread, so
-    // that the exit is uniform) frees the pair's two slots; two rotating warps refill them
-    // with the next pieces in order.
-    failed = __syncthreads_or(!ok) != 0;
-    if (failed) break;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (next_piece < P && lane == 0 && warp == issuer) issue(next_piece, sl[i]);
-      ++next_piece;
-      if (++issuer == RW) issuer = 0;
+    // this warp is done with the pair's two node planes
+    __syncwarp();
+    if (ok && lane == 0) {
+      mbar_arrive(empty_s + 8u * (uint32_t)sl[0]);
+      mbar_arrive(empty_s + 8u * (uint32_t)sl[1]);
     }
   }
+  // every wait above is bounded: a wait that gave up ends the launch with a status word
+  const bool failed = __syncthreads_or(!ok) != 0;
   if (failed) {
     if (tid == 0) atomicExch(p.status, 4);
     return;
