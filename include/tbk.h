@@ -84,10 +84,15 @@ typedef struct tbk_schedule {
                               async copies, 2 = read nodes from global memory,
                               0 = auto */
   int32_t feature_bits;    /* how rows are staged in shared memory: 32 = fp32 values,
-                              16 = order-preserving 16-bit keys with exact fp32 tie
-                              resolution (reorg layout, single-output forests, at most 8
-                              levels; meant for rows too wide for an fp32 tile),
-                              0 = auto */
+                              16 = order-preserving 15/16-bit keys with exact fp32 tie
+                              resolution (leaf selection stays bit-exact): single-output
+                              forests of at most 12 levels; multiclass forests of at most
+                              8 levels over narrow rows (one tree chunk, no per-class
+                              partial sums: tbk_predict_partial is refused),
+                              0 = auto: with representation TBK_REP_AUTO keys for
+                              single-output forests of at most 12 levels unless most
+                              thresholds are whole numbers (integer-valued features tie
+                              all the time), fp32 otherwise */
   int32_t reserved[4];
 } tbk_schedule;
 
