@@ -161,6 +161,36 @@ def test_runner_api_on_golden_json(stem, rep, golden_dir):
     assert np.array_equal(on_dev, got)
 
 
+def test_runner_with_64_bit_types(golden_dir):
+    """The reference's other tested type combination (f64 thresholds and values, i32 indices,
+    src/test/GPUTests.cpp:682-840): host buffers hold doubles, the walk computes in fp32."""
+    from treebeard_b200 import treebeard
+    z = np.load(os.path.join(golden_dir, "TestModel_Size2_13.npz"))
+    rows, expected = z["rows"], z["expected"]
+    batch = 64
+    options = treebeard.CompilerOptions(batch, 1)
+    options.SetThresholdTypeWidth(64)
+    options.SetInputElementTypeWidth(64)
+    options.SetReturnTypeWidth(64)
+    options.SetFeatureIndexTypeWidth(32)
+    options.SetNodeIndexTypeWidth(32)
+    ctx = treebeard.TreebeardContext(os.path.join(golden_dir, "TestModel_Size2_13.json"), "", options)
+    ctx.SetInputFiletype("xgboost_json")
+    ctx.SetRepresentationType("gpu_sparse")
+    runner = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx)
+    wide = np.ascontiguousarray(rows[:4 * batch], np.float64)
+    got = runner.RunInference(wide[:batch], np.float64)
+    assert got.dtype == np.float64 and oracle.fp_equal(got, expected[:batch]).all()
+    many = runner.RunInferenceOnMultipleBatches(wide, np.float64)
+    assert oracle.fp_equal(many, expected[:4 * batch]).all()
+    with pytest.raises(treebeard.TreebeardRuntimeError):
+        runner.RunInference(wide[:batch])                    # the runner returns float64
+    with pytest.raises(treebeard.TreebeardRuntimeError, match="host"):
+        dev = torch.zeros((batch, rows.shape[1]), device="cuda")
+        out = torch.zeros(batch, device="cuda")
+        runner.treebeardAPI.RunInference(runner.inferenceRunner, dev.data_ptr(), out.data_ptr())
+
+
 def test_runner_multiclass_int8(tmp_path):
     from treebeard_b200 import synth, treebeard
     forest, X = small_config("c4", rows=256)

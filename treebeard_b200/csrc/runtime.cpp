@@ -169,8 +169,13 @@ InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &o
     set_error(TBK_ERR_INVALID, "batch size must be positive");
     return nullptr;
   }
-  if (opt.thresholdTypeWidth != 32 || opt.inputElementTypeWidth != 32) {
-    set_error(TBK_ERR_UNSUPPORTED, "only fp32 thresholds and fp32 inputs are supported");
+  // 64-bit types (the reference's other tested combination, f64 thresholds / i32 indices): the
+  // walk computes in fp32 either way -- thresholds of the supported model formats are fp32
+  // values --; a 64-bit input or return width means that the HOST buffers of RunInference hold
+  // doubles, converted on the way in and out.  Index widths do not matter to this library.
+  if ((opt.thresholdTypeWidth != 32 && opt.thresholdTypeWidth != 64) ||
+      (opt.inputElementTypeWidth != 32 && opt.inputElementTypeWidth != 64)) {
+    set_error(TBK_ERR_UNSUPPORTED, "thresholds and inputs must be 32 or 64 bits wide");
     return nullptr;
   }
   if (opt.tilingType != 0) {
@@ -178,8 +183,8 @@ InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &o
     return nullptr;
   }
   const bool int8_out = !opt.returnTypeFloatType && opt.returnTypeWidth == 8;
-  if (!int8_out && !(opt.returnTypeFloatType && opt.returnTypeWidth == 32)) {
-    set_error(TBK_ERR_UNSUPPORTED, "return type must be fp32 or (multiclass) int8");
+  if (!int8_out && !(opt.returnTypeFloatType && (opt.returnTypeWidth == 32 || opt.returnTypeWidth == 64))) {
+    set_error(TBK_ERR_UNSUPPORTED, "return type must be fp32, fp64 or (multiclass) int8");
     return nullptr;
   }
   if (int8_out && forest.num_classes == 0) {
@@ -375,6 +380,29 @@ void run_batch(InferenceRunner *r, void *inputs, void *results, int64_t rows) {
     set_error(TBK_ERR_INVALID, "device buffers are not on the runner's GPU");
     return;
   }
+  // 64-bit host buffers: convert into fp32 staging vectors around the fp32 path
+  const bool wide_in = r->inputWidth == 64, wide_out = r->returnFloat && r->returnWidth == 64;
+  std::vector<float> narrow_in, narrow_out;
+  void *wide_results = nullptr;
+  if (wide_in || wide_out) {
+    if (on_device) {
+      set_error(TBK_ERR_UNSUPPORTED, "64-bit inputs or results are converted on the host: pass host buffers");
+      return;
+    }
+    if (wide_in) {
+      const double *src = static_cast<const double *>(inputs);
+      const int64_t n = rows * r->rowSize;
+      narrow_in.resize((size_t)n);
+#pragma omp parallel for schedule(static)
+      for (int64_t i = 0; i < n; ++i) narrow_in[i] = (float)src[i];
+      inputs = narrow_in.data();
+    }
+    if (wide_out) {
+      narrow_out.resize((size_t)rows);
+      wide_results = results;
+      results = narrow_out.data();
+    }
+  }
   int rc = TBK_OK;
   const int runs = g_measure_kernel_time ? std::max(1, g_kernel_runs) : 1;
   if (on_device) {
@@ -418,7 +446,15 @@ void run_batch(InferenceRunner *r, void *inputs, void *results, int64_t rows) {
   } else {
     rc = tbk_predict_host(r->forest, static_cast<const float *>(inputs), rows, r->rowSize, results, kind);
   }
-  if (rc != TBK_OK) set_error(rc, tbk_last_error());
+  if (rc != TBK_OK) {
+    set_error(rc, tbk_last_error());
+    return;
+  }
+  if (wide_results) {
+    double *dst = static_cast<double *>(wide_results);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < rows; ++i) dst[i] = (double)narrow_out[i];
+  }
 }
 
 } // namespace

@@ -351,9 +351,20 @@ class TreebeardInferenceRunner:
             want = f"({rows if rows is not None else 'n'}, {self.rowSize})"
             raise TreebeardRuntimeError(f"inputs have shape {shape}, the runner expects {want}")
 
+    def _host_types(self, resultType):
+        """numpy types of the host buffers: what the runner was compiled for (32- or 64-bit
+        inputs; fp32, fp64 or int8 results)."""
+        in_type = numpy.float64 if _rt.TB_GetInputTypeBitWidth(self.inferenceRunner) == 64 else numpy.float32
+        width = _rt.TB_GetReturnTypeBitWidth(self.inferenceRunner)
+        out_type = numpy.int8 if width == 8 else numpy.float64 if width == 64 else numpy.float32
+        if numpy.dtype(resultType) != numpy.dtype(out_type):
+            raise TreebeardRuntimeError(f"the runner returns {numpy.dtype(out_type)}, not {numpy.dtype(resultType)}")
+        return in_type, out_type
+
     def RunInference(self, inputs, resultType=numpy.float32):
         if isinstance(inputs, numpy.ndarray):
-            assert inputs.dtype == numpy.float32 and inputs.flags.c_contiguous
+            in_type, resultType = self._host_types(resultType)
+            assert inputs.dtype == in_type and inputs.flags.c_contiguous
             self._check_shape(inputs, self.batchSize)
             results = numpy.zeros((self.batchSize), resultType)
             self.treebeardAPI.RunInference(self.inferenceRunner, inputs.ctypes.data, results.ctypes.data)
@@ -368,7 +379,8 @@ class TreebeardInferenceRunner:
 
     def RunInferenceOnMultipleBatches(self, inputs, resultType=numpy.float32):
         assert type(inputs) is numpy.ndarray
-        assert inputs.dtype == numpy.float32 and inputs.flags.c_contiguous
+        in_type, resultType = self._host_types(resultType)
+        assert inputs.dtype == in_type and inputs.flags.c_contiguous
         self._check_shape(inputs, None)
         numRows = inputs.shape[0]
         results = numpy.zeros((numRows), resultType)
