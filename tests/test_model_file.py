@@ -105,6 +105,8 @@ def test_runner_from_model_file_matches_direct_runner(name, tmp_path):
 @pytest.mark.parametrize("name,layout", [("c2", dict(representation="sparse", tile_size=2)),
                                          ("c4", dict(representation="array")),
                                          ("c3", dict(representation="auto")),
+                                         ("c2", dict(representation="auto")),
+                                         ("c4", dict(representation="auto", feature_bits=16)),
                                          ("c5", dict(representation="auto"))])
 def test_packed_image_survives_serialisation(name, layout):
     """Host only: pack, serialise, read back, serialise again -- same bytes; a changed layout
