@@ -49,6 +49,49 @@ __host__ __device__ constexpr int quant_batch_smem_bytes(int num_features, int t
   return kQBBarBytes + kQBRingBytes + tiles * quant_batch_tile_bytes(num_features);
 }
 
+// All DEPTH levels of four columns in ONE block of PTX, for callers that hold both pieces of
+// the group (walk_quant_batch.cuh): the upper levels as in quant_upper4, then the bottom level
+// as in quant_bottom4 (cb = address of the column's first bottom-level node).  In: A[i] =
+// address of the root.  Out: A[i] = leaf number; bit i of `ties` is set if column i met a key
+// tie on any level.
+#define TBQ_LEAVES_B TBQ_LEAF(0, "%0", "%18") TBQ_LEAF(1, "%1", "%19") TBQ_LEAF(2, "%2", "%20") TBQ_LEAF(3, "%3", "%21")
+#define TBQ_BOTTOM TBQ_LOAD TBQ_COMPARE TBQ_LEAVES_B TBQ_TIES
+#define TBQ_OPERANDS_FULL TBQ_OPERANDS_UP, "r"(cb[0]), "r"(cb[1]), "r"(cb[2]), "r"(cb[3])
+template <int DEPTH>
+__device__ __forceinline__ void quant_full4(uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane, const uint32_t (&cu)[4],
+                                            const uint32_t (&cx)[4], const uint32_t (&cb)[4]) {
+  static_assert(DEPTH >= 2 && DEPTH <= 8, "two to eight levels");
+  [[maybe_unused]] uint32_t n[4];
+  uint32_t tb;
+  if constexpr (DEPTH == 2)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_CROSS0 TBQ_BOTTOM "}" TBQ_OPERANDS_FULL);
+  else if constexpr (DEPTH == 3)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_CROSS TBQ_BOTTOM "}" TBQ_OPERANDS_FULL);
+  else if constexpr (DEPTH == 4)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_CROSS TBQ_BOTTOM "}" TBQ_OPERANDS_FULL);
+  else if constexpr (DEPTH == 5)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_STEP TBQ_CROSS TBQ_BOTTOM "}" TBQ_OPERANDS_FULL);
+  else if constexpr (DEPTH == 6)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_STEP TBQ_STEP TBQ_CROSS TBQ_BOTTOM "}" TBQ_OPERANDS_FULL);
+  else if constexpr (DEPTH == 7)
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_CROSS TBQ_BOTTOM "}" TBQ_OPERANDS_FULL);
+  else
+    asm volatile("{\n" TBQ_DECL TBQ_LOAD TBQ_STEP0 TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_STEP TBQ_CROSS TBQ_BOTTOM "}"
+                 TBQ_OPERANDS_FULL);
+  ties |= tb;
+}
+__device__ __forceinline__ void quant_full4_any(uint32_t depth, uint32_t (&A)[4], uint32_t &ties, uint32_t keys_lane,
+                                                const uint32_t (&cu)[4], const uint32_t (&cx)[4], const uint32_t (&cb)[4]) {
+  switch (depth) {
+  case 2: return quant_full4<2>(A, ties, keys_lane, cu, cx, cb);
+  case 3: return quant_full4<3>(A, ties, keys_lane, cu, cx, cb);
+  case 4: return quant_full4<4>(A, ties, keys_lane, cu, cx, cb);
+  case 5: return quant_full4<5>(A, ties, keys_lane, cu, cx, cb);
+  case 6: return quant_full4<6>(A, ties, keys_lane, cu, cx, cb);
+  case 7: return quant_full4<7>(A, ties, keys_lane, cu, cx, cb);
+  default: return quant_full4<8>(A, ties, keys_lane, cu, cx, cb);
+  }
+}
 template <int UD, bool LEAF_IDS, bool MULTI>
 __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
