@@ -267,9 +267,8 @@ def test_sixteen_bit_key_kernel_is_exact(name):
 
 
 def test_auto_representation_picks_keys_for_single_output_forests_of_up_to_eight_levels():
-    """"auto": keys for wide rows (one tile per block) and for narrow rows (batches of tiles)
-    of single-output forests; fp32 tiles for multiclass forests, on request, and for explicit
-    representations."""
+    """"auto": keys for wide rows (one tile per block) and for narrow rows (batches of tiles,
+    multiclass forests included); fp32 tiles on request and for explicit representations."""
     from treebeard_b200 import kernels
     wide, Xw = small_config("c3", rows=64)
     narrow, Xn = small_config("c2", rows=64)
@@ -280,14 +279,25 @@ def test_auto_representation_picks_keys_for_single_output_forests_of_up_to_eight
     assert b.info().schedule.feature_bits == 16 and b.info().threads_per_block == 640
     assert kernels.DeviceForest(narrow, representation="auto", feature_bits=32).info().schedule.feature_bits == 32
     assert kernels.DeviceForest(narrow, representation="sparse").info().schedule.feature_bits == 32
-    assert kernels.DeviceForest(multi, representation="auto").info().schedule.feature_bits == 32
+    m = kernels.DeviceForest(multi, representation="auto")
+    assert m.info().schedule.feature_bits == 16 and m.info().threads_per_block == 640
+    assert kernels.DeviceForest(multi, representation="sparse").info().schedule.feature_bits == 32
+    want_m, sums_m = oracle.predict(multi, Xm, class_sums=True)
+    assert_predictions_close(m.predict(_dev(Xm)).cpu().numpy(), want_m, multi, sums_m)
     assert_predictions_close(a.predict(_dev(Xw)).cpu().numpy(), oracle.predict(wide, Xw))
     assert_predictions_close(b.predict(_dev(Xn)).cpu().numpy(), oracle.predict(narrow, Xn))
-    # integral thresholds (integer-valued features: rows tie with thresholds all the time) keep fp32 tiles
+    # whole-number thresholds (integer-valued features: rows EQUAL thresholds all the time) become
+    # lattice features of the key layout: exact without a single tie on whole-number rows
     import copy
     rounded = copy.copy(narrow)
     rounded.thr = np.where(narrow.left >= 0, np.round(narrow.thr * 4), narrow.thr).astype(np.float32)
-    assert kernels.DeviceForest(rounded, representation="auto").info().schedule.feature_bits == 32
+    Xr = np.round(Xn * 4).astype(np.float32)
+    c = kernels.DeviceForest(rounded, representation="auto")
+    assert c.info().schedule.feature_bits == 16
+    want, want_ids = oracle.predict(rounded, Xr, leaf_ids=True)
+    assert np.array_equal(c.predict_leaf_ids(_dev(Xr)).cpu().numpy(), want_ids)
+    assert_predictions_close(c.predict(_dev(Xr)).cpu().numpy(), want)
+    assert c.info().reserved[0] == 0
 
 
 @pytest.mark.parametrize("name,rows,chunks", [("c2", 100003, 0), ("c2", 100003, 3), ("c1", 77777, 0), ("c2", 5000, 0)])
@@ -517,16 +527,12 @@ def test_runner_rejects_buffers_on_different_sides(tmp_path):
 
 
 def test_sixteen_bit_keys_refuse_what_they_do_not_cover():
-    """Multiclass forests need rows narrow enough for the batch kernel, and their key layout
-    keeps no per-class partial sums."""
+    """Multiclass forests need rows narrow enough for the batch kernel."""
     from treebeard_b200 import kernels, synth
     wide = synth.generate_forest(40, 60, 6, 1800, 0.1, 0.1, synth.Marginal("normal", 1800), num_classes=3)
     with pytest.raises(kernels.TbkError):
         kernels.DeviceForest(wide, representation="auto", feature_bits=16)
-    forest, X = small_config("c4", rows=64)
-    df = kernels.DeviceForest(forest, representation="auto", feature_bits=16)
-    with pytest.raises(kernels.TbkError, match="partial"):
-        df.predict_partial(_dev(X))
+    assert kernels.DeviceForest(wide, representation="auto").info().schedule.feature_bits == 32
 
 
 @pytest.mark.parametrize("rows", [100003, 5000, 77])
@@ -540,6 +546,9 @@ def test_batched_key_kernel_multiclass(rows):
     for i in range(2000):
         g = split[(i * 37) % len(split)]
         X[(i * 31) % len(X), forest.feat[g]] = forest.thr[g]
+    for i in range(0, 2000, 3):                      # ... and values that are not whole numbers next to them
+        g = split[(i * 37) % len(split)]
+        X[(i * 31) % len(X), forest.feat[g]] += ((-1) ** i) * [1e-6, 1e-3, 0.5][i % 3]
     want, sums = oracle.predict(forest, X, class_sums=True)
     _, want_ids = oracle.predict(forest, X, leaf_ids=True)
     df = kernels.DeviceForest(forest, representation="auto", feature_bits=16, batch_hint=rows)
@@ -555,6 +564,12 @@ def test_batched_key_kernel_multiclass(rows):
     ids = df.predict_leaf_ids(dX[sub]).cpu().numpy()
     df.check_status()
     assert np.array_equal(ids, want_ids[sub])
+    # per-class partial sums (what tree shards exchange) and the second pass over them
+    part = df.predict_partial(dX)
+    assert part.shape == (rows, forest.num_classes)
+    assert np.allclose(part.cpu().numpy() + forest.initial_value, sums, rtol=1e-5, atol=1e-5) or \
+        np.allclose(part.cpu().numpy(), sums, rtol=1e-5, atol=1e-5)
+    assert_predictions_close(df.finalize(part).cpu().numpy(), want, forest, sums)
 
 
 @pytest.mark.parametrize("name,layout", [("c2", dict(representation="sparse")),

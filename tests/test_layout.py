@@ -171,6 +171,22 @@ def test_sixteen_bit_keys_lay_multiclass_forests_out_class_by_class():
         np.allclose(sums, sums_want, rtol=1e-5, atol=1e-5)
     per_class = np.bincount(forest.class_id, minlength=forest.num_classes)
     assert info.num_groups == sum(max(1, -(-int(n) // 32)) for n in per_class)
+    # C4's features and thresholds are whole numbers: lattice features, whose whole-number rows
+    # never tie although one comparison in 16 is an exact equality
+    assert info.reserved[0] == 0
+    # rows that are not whole numbers, hugging thresholds from both sides, infinities and NaN:
+    # decided by the keys where they can, by the exact comparison otherwise -- always the oracle's leaf
+    Y = X.copy()
+    split = np.nonzero(forest.left >= 0)[0]
+    for i in range(4000):
+        g = split[(i * 37) % len(split)]
+        Y[i % len(Y), forest.feat[g]] = forest.thr[g] + ((-1) ** i) * [1e-6, 1e-4, 0.25, 0.5][i % 4]
+    Y[7, :] = np.nan
+    Y[8, 0], Y[9, 1] = np.inf, -np.inf
+    _, want_ids = oracle.predict(forest, Y, leaf_ids=True)
+    ids, _, info = kernels.host_layout_check(forest, Y, representation="reorg", feature_bits=16)
+    assert np.array_equal(ids, want_ids)
+    assert info.reserved[0] > 0
 
 
 def test_multiclass_class_without_trees_keeps_its_place():

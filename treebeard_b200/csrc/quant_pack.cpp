@@ -6,15 +6,18 @@
 
 namespace tb {
 
-std::string quant_feature_ranges(const Forest &f, float span, std::vector<float> *lo_out, std::vector<float> *scale_out) {
+std::string quant_feature_ranges(const Forest &f, float span, std::vector<float> *lo_out, std::vector<float> *scale_out,
+                                 bool lattice) {
   const int F = f.num_features;
   std::vector<float> lo(F + 1, std::numeric_limits<float>::infinity());
   std::vector<float> hi(F + 1, -std::numeric_limits<float>::infinity());
+  std::vector<char> whole(F + 1, 1); // every threshold of the feature is a whole number
   for (int64_t g = 0; g < f.num_nodes(); ++g) {
     if (!std::isfinite(f.thr[g])) return "non-finite threshold or leaf value";
     if (f.is_leaf(g)) continue;
     lo[f.feat[g]] = std::min(lo[f.feat[g]], f.thr[g]);
     hi[f.feat[g]] = std::max(hi[f.feat[g]], f.thr[g]);
+    if (f.thr[g] != std::floor(f.thr[g]) || std::fabs(f.thr[g]) > 0x1p22f) whole[f.feat[g]] = 0;
   }
   lo_out->assign(F + 1, 0.f);
   scale_out->assign(F + 1, 0.f);
@@ -26,12 +29,17 @@ std::string quant_feature_ranges(const Forest &f, float span, std::vector<float>
     // the largest threshold off the two saturated keys under rounding
     float s = hi[i] > lo[i] ? span / (hi[i] - lo[i]) : 0x1p40f;
     if (!std::isfinite(s) || s <= 0.f) s = 0x1p40f;
+    if (lattice && whole[i] && hi[i] - lo[i] <= span) {
+      // whole-number thresholds: a whole-number slope puts each of them exactly on a key
+      // (threshold - lo, the product and the sum are all exact in fp32)
+      s = -(hi[i] > lo[i] ? std::floor(span / (hi[i] - lo[i])) : 1024.f);
+    }
     (*scale_out)[i] = s;
   }
   return "";
 }
 
-std::string pack_quant(const Forest &f, QuantForest *out) {
+std::string pack_quant(const Forest &f, QuantForest *out, bool lattice) {
   std::string err = validate(f);
   if (!err.empty()) return err;
   if (f.num_features > kQuantMaxFeatures) return "more than " + std::to_string(kQuantMaxFeatures) + " features";
@@ -47,7 +55,7 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
   q.num_trees = T;
   q.num_nodes = f.num_nodes();
 
-  err = quant_feature_ranges(f, kKey15Span, &q.lo, &q.scale);
+  err = quant_feature_ranges(f, kKey15Span, &q.lo, &q.scale, lattice);
   if (!err.empty()) return err;
 
   std::vector<int32_t> depth(T);
@@ -121,7 +129,9 @@ std::string pack_quant(const Forest &f, QuantForest *out) {
         const int32_t ft = f.feat[a + it.node];
         const float thr = f.thr[a + it.node];
         const uint64_t e = gm.elem_off + (uint64_t)quant_plane_slot(it.slot, it.level, gm.depth) * kQuantCols + c;
-        q.node_plane[e] = (quant_feature_code((uint32_t)ft) << 16) | quant_key15(thr, q.lo[ft], q.scale[ft]);
+        q.node_plane[e] = (quant_feature_code((uint32_t)ft) << 16) | quant_threshold_key15(thr, q.lo[ft], q.scale[ft]);
+        ++q.num_splits;
+        if (thr == std::floor(thr) && !(q.scale[ft] < 0.f)) ++q.whole_number_splits;
         q.exact_plane[e] = thr;
         stack.push_back({f.left[a + it.node], 2 * it.slot + 1, it.level + 1});
         stack.push_back({f.right[a + it.node], 2 * it.slot + 2, it.level + 1});

@@ -63,6 +63,9 @@ struct QuantForest {
   std::vector<int32_t> orig_leaf;   // original node id per leaf-plane element
   std::vector<int32_t> tree_index;  // [groups*32] original tree index, -1 = filler
   std::vector<int32_t> group_class; // multiclass: the class every tree of the group votes for
+  // split nodes in all, and those with a whole-number threshold on a feature that is not a
+  // lattice feature (rows of integer-valued features tie with such thresholds all the time)
+  int64_t num_splits = 0, whole_number_splits = 0;
   std::vector<float> lo, scale;     // per feature (+ sentinel entry)
 };
 
@@ -96,10 +99,29 @@ inline uint16_t quant_key(float v, float lo, float scale) {
 constexpr float kKey15Top = 31741.0f, kKey15Min = 1024.0f, kKey15Max = 31743.0f;
 constexpr float kKey15Span = 30715.0f; // keys between the smallest and the largest threshold
 constexpr float kKey16Span = 65531.0f;
+// A NEGATIVE scale marks a lattice feature (see quant_feature_ranges): every threshold is a
+// whole number and the slope |scale| is one too, so thresholds and whole-number row values
+// land EXACTLY on keys (value - lo, the product and the sum are exact in fp32).  A whole-number
+// row value x then has key(x) <= key(t) exactly when x >= t; any other row value gets
+// floor + 1, which either decides like its neighbours or equals the node key (below).
 inline uint16_t quant_key15(float v, float lo, float scale) {
+  if (scale < 0.f) {
+    float y = std::fmaf(v - lo, scale, kKey15Top);
+    y = std::fmin(std::fmax(y, kKey15Min), kKey15Max - 1.0f);
+    return v == std::floor(v) ? (uint16_t)y : (uint16_t)(std::floor(y) + 1.0f);
+  }
   float y = std::fmaf(v - lo, -scale, kKey15Top);
   y = std::fmin(std::fmax(y, kKey15Min), kKey15Max); // fmax first: NaN becomes the smallest key
   return (uint16_t)std::floor(y);
+}
+// Key stored in a split node.  Ordinary features: the key of the threshold itself (equal keys
+// decide nothing and go through the exact comparison).  Lattice features: one above it --
+// whole-number rows at or above the threshold have keys up to the threshold's and go right by
+// "row key < node key", whole-number rows below it have larger keys and go left, and only a
+// row value that is not a whole number can meet the node key exactly (it lies within
+// 1/|scale| of the threshold): the exact comparison then decides, as for any key tie.
+inline uint16_t quant_threshold_key15(float t, float lo, float scale) {
+  return scale < 0.f ? (uint16_t)(quant_key15(t, lo, scale) + 1) : quant_key15(t, lo, scale);
 }
 inline uint32_t quant_feature_code(uint32_t f) { return (f >> 1) * 64u + (f & 1u); }
 inline uint32_t quant_feature_of_code(uint32_t code) { return (code >> 6) * 2u + (code & 1u); }
@@ -108,14 +130,19 @@ inline uint32_t quant_feature_of_code(uint32_t code) { return (code >> 6) * 2u +
 // feature): lo = smallest threshold of the feature, scale = span / (hi - lo), span being
 // the number of key steps between the smallest and the largest threshold (kKey15Span here,
 // kKey16Span in the deep-tree layout).  Fails on a non-finite threshold or leaf value.
-std::string quant_feature_ranges(const Forest &f, float span, std::vector<float> *lo, std::vector<float> *scale);
+// lattice: features whose thresholds are all whole numbers no more than `span` apart get a
+// whole-number slope, stored NEGATED (see quant_key15): rows of integer-valued features, which
+// equal thresholds all the time, then never need the exact comparison.
+std::string quant_feature_ranges(const Forest &f, float span, std::vector<float> *lo, std::vector<float> *scale,
+                                 bool lattice = false);
 
+// lattice: allow lattice features (the kernel for narrow rows handles them).
 // Empty string on success.  Fails (so that the caller can fall back to another layout)
 // for trees deeper than kQuantMaxDepth or non-finite thresholds.  Multiclass forests are
 // laid out class by class: every class is padded to whole groups (filler columns hold one
 // pass-through tree with value 0), classes in increasing order, every class present, so a
 // group belongs to one class (group_class).
-std::string pack_quant(const Forest &f, QuantForest *out);
+std::string pack_quant(const Forest &f, QuantForest *out, bool lattice = false);
 
 // Host interpreter of the packed planes (layout verification only).  sums: one value per
 // row, or num_classes values per row for a multiclass forest.

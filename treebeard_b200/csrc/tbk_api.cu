@@ -192,10 +192,6 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   const bool batched = max_batch > 0;
   const bool multi = q.num_classes > 0;
   if (multi && !batched) return fail(TBK_ERR_UNSUPPORTED, "multiclass forests in the key layout need rows narrow enough for the batch kernel");
-  if (multi && mode == kPartial)
-    return fail(TBK_ERR_UNSUPPORTED, "the key layout keeps no per-class partial sums: create the forest with feature_bits = 32");
-  if (multi && f->user.tree_chunks > 1)
-    return fail(TBK_ERR_UNSUPPORTED, "multiclass forests in the key layout are walked in one tree chunk");
   // batch kernel: as many tiles per batch as still give every SM a batch
   int R = 1;
   if (batched) {
@@ -204,8 +200,8 @@ int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int
   }
   const int64_t units = batched ? (tiles + R - 1) / R : tiles; // blocks' units of work along x
   int64_t chunks = 1;
-  if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
-  else if (multi) chunks = 1; // a class must stay within one leaf warp's sequence of groups
+  if (multi) chunks = 1; // a class must stay within one leaf warp's sequence of groups
+  else if (f->user.tree_chunks > 0) chunks = f->user.tree_chunks;
   else if (batched) {
     if (units < (int64_t)f->num_sms) chunks = ((int64_t)f->num_sms + units - 1) / units;
   } else if (tiles < 2 * (int64_t)f->num_sms) chunks = (2 * (int64_t)f->num_sms + tiles - 1) / tiles;
@@ -705,27 +701,21 @@ int tbk_image_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, 
   // kernel applies; measured faster than the fp32 walk on single-output forests of up to 8 levels
   const bool batch_fits =
       (smem_limit - tb::kQBBarBytes - tb::kQBRingBytes) / tb::quant_batch_tile_bytes(host.num_features) >= 4;
-  // (multiclass forests only on request: the key layout walks them in one tree chunk and
-  // keeps no per-class partial sums, which small batches and tree shards need).  Forests whose
-  // thresholds are mostly whole numbers were trained on integer-valued features: their rows
-  // tie with thresholds all the time (measured: one comparison in 16 on 4-bit features, the
-  // key walk then runs at a quarter of the fp32 walk's rate), so they keep fp32 tiles too.
-  int64_t splits = 0, whole = 0;
-#pragma omp parallel for reduction(+ : splits, whole) schedule(static) num_threads(tb::pack_threads())
-  for (int64_t g = 0; g < host.num_nodes(); ++g)
-    if (!host.is_leaf(g)) {
-      ++splits;
-      whole += host.thr[g] == std::floor(host.thr[g]) ? 1 : 0;
-    }
-  const bool integer_features = splits > 0 && 2 * whole > splits;
+  // (multiclass forests too: one walker set per class, arg-max or per-class sums in the leaf warps)
   bool want_quant = (bits == 16 && max_depth <= tb::kQuantMaxDepth && (host.num_classes == 0 || batch_fits)) ||
                     (bits == 0 && (rep == TBK_REP_AUTO || rep == TBK_REP_REORG) && ts == 1 && !fp32_tile_fits &&
                      host.num_classes == 0) ||
-                    (bits == 0 && rep == TBK_REP_AUTO && ts == 1 && host.num_classes == 0 && batch_fits &&
-                     max_depth <= tb::kQuantMaxDepth && !integer_features);
+                    (bits == 0 && rep == TBK_REP_AUTO && ts == 1 && batch_fits && max_depth <= tb::kQuantMaxDepth);
   if (want_quant) {
-    std::string qerr = tb::pack_quant(host, &im.qf);
-    if (qerr.empty() && quant_smem_bytes(host.num_features) > smem_limit)
+    // narrow rows (batch kernel): features with whole-number thresholds become lattice features
+    std::string qerr = tb::pack_quant(host, &im.qf, batch_fits);
+    // Whole-number thresholds that could not be put on a lattice (a feature with other
+    // thresholds too, or wide rows) mean integer-valued features whose rows tie with thresholds
+    // all the time (measured: one comparison in 16 on 4-bit features, the key walk then runs at
+    // a quarter of the fp32 walk's rate): such forests keep fp32 tiles unless keys were asked for.
+    if (qerr.empty() && bits == 0 && fp32_tile_fits && 2 * im.qf.whole_number_splits > im.qf.num_splits)
+      qerr = "integer-valued features";
+    if (qerr.empty() && !batch_fits && quant_smem_bytes(host.num_features) > smem_limit)
       qerr = "rows are too wide for the 16-bit key tile";
     if (qerr.empty() && im.qf.node_plane.size() >= (1ull << 32))
       qerr = "forest too large for the 16-bit key layout (2^32 plane elements)";
@@ -1333,7 +1323,9 @@ int tbk_host_layout_check(const tbk_forest_arrays *fa, const tbk_schedule *sched
     int64_t ties = 0, groups = 0, elems = 0;
     if (max_depth <= tb::kQuantMaxDepth) {
       tb::QuantForest q;
-      std::string qerr = tb::pack_quant(host, &q);
+      // (lattice features where the rows are narrow enough for the batch kernel, as at upload)
+      const bool narrow = (227 * 1024 - tb::kQBBarBytes - tb::kQBRingBytes) / tb::quant_batch_tile_bytes(host.num_features) >= 4;
+      std::string qerr = tb::pack_quant(host, &q, narrow);
       if (!qerr.empty()) return fail(TBK_ERR_UNSUPPORTED, "%s", qerr.c_str());
       if (rows && n_rows > 0) tb::walk_quant_on_host(q, rows, n_rows, ld, leaf_ids, sums, &ties);
       groups = (int64_t)q.groups.size();

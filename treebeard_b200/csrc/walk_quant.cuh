@@ -109,6 +109,22 @@ __device__ __forceinline__ uint32_t quant_key15_dev(float v, float lo, float sc)
   return h;
 }
 
+// The same with lattice features (negative scale, quant_pack.h): whole-number values land
+// exactly on their key, other values get floor + 1.  Used where staging is cheap (the kernel
+// for narrow rows) and for the node keys.
+__device__ __forceinline__ uint32_t quant_key15_lattice_dev(float v, float lo, float sc) {
+  if (sc < 0.f) {
+    float y = __fmaf_rn(__fsub_rn(v, lo), sc, 31741.0f);
+    y = fminf(fmaxf(y, 1024.0f), 31742.0f);
+    const float fl = floorf(y);
+    return (uint32_t)(v == floorf(v) ? y : fl + 1.0f);
+  }
+  return quant_key15_dev(v, lo, sc);
+}
+__device__ __forceinline__ uint32_t quant_threshold_key15_dev(float t, float lo, float sc) {
+  return quant_key15_lattice_dev(t, lo, sc) + (sc < 0.f ? 1u : 0u);
+}
+
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -286,7 +302,7 @@ __global__ void tb_quant_fill_keys(uint32_t *node_plane, const float *exact_plan
   const uint32_t node = node_plane[i];
   if (wide) {
     const uint32_t code = node >> 16, f = (code >> 6) * 2u + (code & 1u);
-    if (f < (uint32_t)num_features) node_plane[i] = (code << 16) | quant_key15_dev(exact_plane[i], lo[f], scale[f]);
+    if (f < (uint32_t)num_features) node_plane[i] = (code << 16) | quant_threshold_key15_dev(exact_plane[i], lo[f], scale[f]);
   } else {
     const uint32_t f = node >> 16;
     if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_key_dev(exact_plane[i], lo[f], scale[f]);

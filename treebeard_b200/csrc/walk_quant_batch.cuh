@@ -20,7 +20,8 @@
 //    increasing order; it keeps the running sum of the current class and, when the class
 //    changes, updates the best class so far (ties go to the higher class index, the rule of
 //    the reference's generated arg-max, src/reduction/LowerReduceOps.cpp:148-189); leaf warp 0
-//    merges the two sets' winners and writes the class id.
+//    merges the two sets' winners and writes the class id (or each leaf warp writes its
+//    classes' sums, where per-class partial sums are asked for).
 //  * 2 ring producers, one per set: four 16 KB slots per set (the two pieces of the group
 //    being walked and both pieces of the next one), cp.async.bulk + mbarrier.
 // Ties between 15-bit keys are flagged by the walk and re-walked on the exact fp32 values, as
@@ -196,10 +197,16 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
           best_class[r] = 0;
         }
       }
-      // the class whose sum has been running is complete: it wins against a smaller or equal best
+      // the class whose sum has been running is complete: it is written out where per-class
+      // partial sums are wanted ([rows][classes]; every class belongs to one set, so every
+      // element is written once), and it wins against a smaller or equal best
       auto fold = [&]() {
 #pragma unroll
         for (int r = 0; r < kQBMaxTiles; ++r) {
+          if (p.write_partial) {
+            const long long row = row0 + r * 32;
+            if (r < R && row < p.n_rows) p.partial[row * p.num_classes + cur_class] = sums[r];
+          }
           if (sums[r] >= best[r]) {
             best[r] = sums[r];
             best_class[r] = cur_class;
@@ -260,6 +267,7 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
       if (!ok) break;
       if constexpr (MULTI && !LEAF_IDS) {
         if (cur_class >= 0) fold();
+        if (p.write_partial) continue; // the per-class sums are the result
         // the batch's results: leaf warp 1 hands its best class to leaf warp 0
         if (set == 1) {
           if (it > 0) ok = wait(sum_free_s, (uint32_t)(it - 1) & 1u);
@@ -359,7 +367,7 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int f = 2 * m + h;
-            k2[h] = f < F ? quant_key15_dev(live ? __ldg(src + f) : 0.f, __ldg(p.lo + f), __ldg(p.scale + f)) : 0x7bffu;
+            k2[h] = f < F ? quant_key15_lattice_dev(live ? __ldg(src + f) : 0.f, __ldg(p.lo + f), __ldg(p.scale + f)) : 0x7bffu;
           }
           asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst + (uint32_t)m * 128u), "r"(k2[0] | (k2[1] << 16)) : "memory");
         }
