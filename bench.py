@@ -37,8 +37,9 @@ HBM_FALLBACK_GBS = 6650.0
 # belongs to the kernel sources it was captured on: it is reported only while the hash of the
 # code of the headers that make up the workload's kernel (kernel_source_hash) still matches.
 KERNEL_SOURCES = {"c3": ("walk_kernels.cuh", "walk_quant.cuh"),
-                  "c2": ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh")}
-NCU_DRAM_BYTES_PER_ROW = {"c3": (8820.1, "600f2104e11475ec"), "c2": (131.8, "b2f2e1f981e0b8e8")}
+                  "c2": ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh"),
+                  "c4": ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh")}
+NCU_DRAM_BYTES_PER_ROW = {"c3": (8750.9, "a272d16cce04051e"), "c2": (131.8, "2ed7ffa4fd85a9ba"), "c4": (107.1, "2ed7ffa4fd85a9ba")}
 
 
 def kernel_source_hash(workload):

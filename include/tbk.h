@@ -87,11 +87,10 @@ typedef struct tbk_schedule {
                               16 = order-preserving 15/16-bit keys with exact fp32 tie
                               resolution (leaf selection stays bit-exact): single-output
                               forests of at most 12 levels; multiclass forests of at most
-                              8 levels over narrow rows (one tree chunk, no per-class
-                              partial sums: tbk_predict_partial is refused),
-                              0 = auto: with representation TBK_REP_AUTO keys for
-                              single-output forests of at most 12 levels unless most
-                              thresholds are whole numbers (integer-valued features tie
+                              8 levels over narrow rows (walked in one tree chunk),
+                              0 = auto: with representation TBK_REP_AUTO keys for these
+                              forests unless most thresholds are whole numbers that cannot
+                              become lattice features (integer-valued features then tie
                               all the time), fp32 otherwise */
   int32_t reserved[4];
 } tbk_schedule;
