@@ -284,6 +284,9 @@ def tree_sharded_c5(args, torch, dist, kernels, rank, world, dev):
         del df
         full = kernels.DeviceForest(forest, device=dev.index, batch_hint=n_rows // world, representation="auto")
         lo, hi = rank * n_rows // world, (rank + 1) * n_rows // world
+        # rank 0 holds the tree-sharded predictions (the sum of every rank's partial sums): its
+        # own row range, recomputed below with the whole forest on one GPU, must agree
+        tree_pred = out[lo:hi].clone() if rank == 0 else None
         Xs, outs = X[lo:hi], out[lo:hi]
 
         def row_step(ev):
@@ -293,6 +296,11 @@ def tree_sharded_c5(args, torch, dist, kernels, rank, world, dev):
 
         res["row_sharded_ms"] = timed(row_step, 2)[-1]
         full.check_status()
+        if rank == 0:
+            diff = (outs - tree_pred).abs()
+            tol = 1e-6 + 1e-5 * outs.abs()
+            res["tree_vs_row_sharded"] = {"rows_compared": int(hi - lo), "max_abs_diff": float(diff.max()),
+                                          "within_tolerance": bool((diff <= tol).all())}
     return res
 
 
