@@ -246,7 +246,7 @@ def test_sixteen_bit_key_kernel_is_exact(name):
     df = kernels.DeviceForest(forest, representation="reorg", feature_bits=16, batch_hint=len(X))
     info = df.info()
     # wide rows: one key tile per block (24 warps); narrow rows: batches of tiles (20 warps)
-    assert info.schedule.feature_bits == 16 and info.threads_per_block == (768 if name == "c3" else 640)
+    assert info.schedule.feature_bits == 16 and info.threads_per_block == (768 if name == "c3" else 704)
     dX = _dev(X)
     ids = df.predict_leaf_ids(dX).cpu().numpy()
     df.check_status()
@@ -276,11 +276,11 @@ def test_auto_representation_picks_keys_for_single_output_forests_of_up_to_eight
     a = kernels.DeviceForest(wide, representation="auto")
     b = kernels.DeviceForest(narrow, representation="auto")
     assert a.info().schedule.feature_bits == 16 and a.info().threads_per_block == 768
-    assert b.info().schedule.feature_bits == 16 and b.info().threads_per_block == 640
+    assert b.info().schedule.feature_bits == 16 and b.info().threads_per_block == 704
     assert kernels.DeviceForest(narrow, representation="auto", feature_bits=32).info().schedule.feature_bits == 32
     assert kernels.DeviceForest(narrow, representation="sparse").info().schedule.feature_bits == 32
     m = kernels.DeviceForest(multi, representation="auto")
-    assert m.info().schedule.feature_bits == 16 and m.info().threads_per_block == 640
+    assert m.info().schedule.feature_bits == 16 and m.info().threads_per_block == 704
     assert kernels.DeviceForest(multi, representation="sparse").info().schedule.feature_bits == 32
     want_m, sums_m = oracle.predict(multi, Xm, class_sums=True)
     assert_predictions_close(m.predict(_dev(Xm)).cpu().numpy(), want_m, multi, sums_m)
@@ -318,7 +318,7 @@ def test_batched_key_kernel_is_exact(name, rows, chunks):
     want, want_ids = oracle.predict(forest, X, leaf_ids=True)
     df = kernels.DeviceForest(forest, representation="auto", batch_hint=rows, tree_chunks=chunks)
     info = df.info()
-    assert info.schedule.feature_bits == 16 and info.threads_per_block == 640
+    assert info.schedule.feature_bits == 16 and info.threads_per_block == 704
     dX = _dev(X)
     got = df.predict(dX).cpu().numpy()
     df.check_status()
@@ -553,7 +553,7 @@ def test_batched_key_kernel_multiclass(rows):
     _, want_ids = oracle.predict(forest, X, leaf_ids=True)
     df = kernels.DeviceForest(forest, representation="auto", feature_bits=16, batch_hint=rows)
     info = df.info()
-    assert info.schedule.feature_bits == 16 and info.threads_per_block == 640
+    assert info.schedule.feature_bits == 16 and info.threads_per_block == 704
     dX = _dev(X)
     got = df.predict(dX).cpu().numpy()
     df.check_status()

@@ -12,10 +12,11 @@
 //    (three barrier waits, three arrivals, the address set-up) are paid once per batch.  The
 //    walkers also stage the batch: thread = row, keys written as paired lines
 //    (word j of line m = keys of features 2m | 2m+1 << 16 for row j).
-//  * 2 leaf warps, one per set: the walkers drop their leaf numbers into [tile][column][row]
-//    byte tables (two per set, alternating by group); the leaf warp gathers the leaf values
-//    from L2, sums a group pairwise and keeps one running sum per tile.  Leaf warp 1 hands its
-//    sums to leaf warp 0, which writes the batch's results.  Multiclass forests: a group
+//  * 4 leaf warps, two per set (one takes the even tiles of the batch, one the odd tiles; one
+//    leaf warp per scheduler): the walkers drop their leaf numbers into [tile][column][row]
+//    byte tables (two per set, alternating by group); a leaf warp gathers the leaf values
+//    from L2, sums a group pairwise and keeps one running sum per tile.  The leaf warps of set 1
+//    hand their sums to those of set 0, which write the batch's results.  Multiclass forests: a group
 //    belongs to one class and every class to one set, whose leaf warp meets the classes in
 //    increasing order; it keeps the running sum of the current class and, when the class
 //    changes, updates the best class so far (ties go to the higher class index, the rule of
@@ -34,8 +35,9 @@
 
 namespace tb {
 
-constexpr int kQBWalkers = 16, kQBLeafWarps = 2, kQBProducers = 2;
+constexpr int kQBWalkers = 16, kQBLeafWarps = 4, kQBProducers = 2;
 constexpr int kQBThreads = 32 * (kQBWalkers + kQBLeafWarps + kQBProducers);
+constexpr int kQBMaxThreads = 768; // 22 warps are allocated as 24: 80 registers per thread
 constexpr int kQBMaxTiles = 16;   // tiles per batch: one per walker warp when the batch is staged
 constexpr int kQBBarBytes = 512;
 constexpr int kQBSlots = 4;       // ring slots per set
@@ -94,23 +96,24 @@ __device__ __forceinline__ void quant_full4_any(uint32_t depth, uint32_t (&A)[4]
   }
 }
 template <int UD, bool LEAF_IDS, bool MULTI>
-__global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kQBMaxThreads, 1) tb_walk_quant_batch_kernel(const QuantParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0); // uniform by construction
   const bool leafer = warp >= kQBWalkers && warp < kQBWalkers + kQBLeafWarps;
   const bool producer = warp >= kQBWalkers + kQBLeafWarps;
-  const int set = (warp >= kQBWalkers ? warp - kQBWalkers : warp / kQSetWarps) & 1;
+  const int set = (warp >= kQBWalkers ? warp - kQBWalkers : warp / kQSetWarps) & 1; // (leaf warps 16..19, producers 20, 21)
+  const int half = (warp - kQBWalkers) >> 1 & 1; // leaf warps: tiles half, half + 2, ... of the batch
   const int sw = warp % kQSetWarps;
   const int F = p.num_features, R = p.tiles_per_batch;
   const int KT = quant_key_tile_bytes(F);
   const uint32_t bars_s = smem_u32(smem_raw);
   // barriers: full[set][4] @0, empty[set][4] @64, table_full[set][2] @128, table_free[set][2] @160,
-  // keys_free @192, keys_ready @200, sum_ready @208, sum_free @216
+  // keys_free @192, keys_ready @200, sum_ready[half] @208, sum_free[half] @224
   const uint32_t full_s = bars_s + (uint32_t)set * 32u, empty_s = bars_s + 64u + (uint32_t)set * 32u;
   const uint32_t table_s = bars_s + 128u + (uint32_t)set * 16u, table_free_s = bars_s + 160u + (uint32_t)set * 16u;
   const uint32_t keys_free_s = bars_s + 192u, keys_ready_s = bars_s + 200u;
-  const uint32_t sum_ready_s = bars_s + 208u, sum_free_s = bars_s + 216u;
+  const uint32_t sum_ready_s = bars_s + 208u + (uint32_t)half * 8u, sum_free_s = bars_s + 224u + (uint32_t)half * 8u;
   unsigned char *ring = smem_raw + kQBBarBytes + (size_t)set * kQBSlots * kQPiece;
   const uint32_t ring_s = smem_u32(ring);
   const uint32_t ltab0_s = bars_s + kQBBarBytes + (uint32_t)kQBRingBytes;   // [set][table][tile][column][row] bytes
@@ -135,11 +138,11 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
     for (int i = 0; i < 8; ++i) mbar_init(bars + i, 1);             // full: the copy's bytes
     for (int i = 8; i < 16; ++i) mbar_init(bars + i, kQSetWarps);   // empty: one arrival per walker warp of the set
     for (int i = 16; i < 20; ++i) mbar_init(bars + i, kQSetWarps);  // table_full: every walker of the set has written
-    for (int i = 20; i < 24; ++i) mbar_init(bars + i, 1);           // table_free: the leaf warp has read the table
+    for (int i = 20; i < 24; ++i) mbar_init(bars + i, 2);           // table_free: both leaf warps of the set have read the table
     mbar_init(bars + 24, kQBWalkers);                               // keys_free: the previous batch is walked
     mbar_init(bars + 25, kQBWalkers);                               // keys_ready: the batch's keys are staged
-    mbar_init(bars + 26, 1);                                        // sum_ready: leaf warp 1 has written its sums
-    mbar_init(bars + 27, 1);                                        // sum_free: leaf warp 0 has read them
+    for (int i = 26; i < 28; ++i) mbar_init(bars + i, 1);           // sum_ready[half]: set 1's leaf warp has written its sums
+    for (int i = 28; i < 30; ++i) mbar_init(bars + i, 1);           // sum_free[half]: set 0's leaf warp has read them
     fence_barrier_init();
   }
   __syncthreads();
@@ -179,22 +182,23 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
       }
     }
   } else if (leafer) {
-    // ---- leaf warps: for every finished table of the set, gather the leaf values of every
-    // tile of the batch, add the group's 32 values pairwise and keep one running sum per tile
+    // ---- leaf warps: for every finished table of the set, gather the leaf values of this
+    // warp's tiles of the batch (every other one), add the group's 32 values pairwise and keep
+    // one running sum per tile
     uint32_t kk = 0; // groups of the set seen so far (tables alternate, their barriers change phase)
     for (int it = 0; it < my_batches && ok; ++it) {
       const long long batch = blockIdx.x + (long long)it * gridDim.x;
       const long long row0 = batch * R * 32 + lane;
-      float sums[kQBMaxTiles];
-      [[maybe_unused]] float best[kQBMaxTiles];  // multiclass: the largest class sum so far and its class
-      [[maybe_unused]] int best_class[kQBMaxTiles];
+      float sums[kQBMaxTiles / 2];
+      [[maybe_unused]] float best[kQBMaxTiles / 2];  // multiclass: the largest class sum so far and its class
+      [[maybe_unused]] int best_class[kQBMaxTiles / 2];
       [[maybe_unused]] int cur_class = -1;
 #pragma unroll
-      for (int r = 0; r < kQBMaxTiles; ++r) {
-        sums[r] = 0.f;
+      for (int q = 0; q < kQBMaxTiles / 2; ++q) {
+        sums[q] = 0.f;
         if constexpr (MULTI) {
-          best[r] = -INFINITY;
-          best_class[r] = 0;
+          best[q] = -INFINITY;
+          best_class[q] = 0;
         }
       }
       // the class whose sum has been running is complete: it is written out where per-class
@@ -202,16 +206,17 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
       // element is written once), and it wins against a smaller or equal best
       auto fold = [&]() {
 #pragma unroll
-        for (int r = 0; r < kQBMaxTiles; ++r) {
+        for (int q = 0; q < kQBMaxTiles / 2; ++q) {
+          const int r = 2 * q + half;
           if (p.write_partial) {
             const long long row = row0 + r * 32;
-            if (r < R && row < p.n_rows) p.partial[row * p.num_classes + cur_class] = sums[r];
+            if (r < R && row < p.n_rows) p.partial[row * p.num_classes + cur_class] = sums[q];
           }
-          if (sums[r] >= best[r]) {
-            best[r] = sums[r];
-            best_class[r] = cur_class;
+          if (sums[q] >= best[q]) {
+            best[q] = sums[q];
+            best_class[q] = cur_class;
           }
-          sums[r] = 0.f;
+          sums[q] = 0.f;
         }
       };
       for (int k = 0; k < NGs && ok; ++k, ++kk) {
@@ -230,7 +235,8 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
         const uint32_t tab0 = ltab_s + (kk & 1u) * (uint32_t)R * 1024u + (uint32_t)lane;
         // (element offsets fit 32 bits: the host refuses planes of 2^32 elements or more)
 #pragma unroll
-        for (int r = 0; r < kQBMaxTiles; ++r) {
+        for (int q = 0; q < kQBMaxTiles / 2; ++q) {
+          const int r = 2 * q + half;
           if (r < R) {
             const uint32_t tab = tab0 + (uint32_t)r * 1024u;
             uint32_t e[32];
@@ -257,7 +263,7 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
               for (int w = 16; w >= 1; w >>= 1)
 #pragma unroll
                 for (int c = 0; c < w; ++c) v[c] += v[c + w];
-              sums[r] += v[0];
+              sums[q] += v[0];
             }
           }
         }
@@ -273,10 +279,10 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
           if (it > 0) ok = wait(sum_free_s, (uint32_t)(it - 1) & 1u);
           if (!ok) break;
 #pragma unroll
-          for (int r = 0; r < kQBMaxTiles; ++r)
-            if (r < R) {
-              asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums1_s + (uint32_t)(r * 64 + lane) * 4u), "f"(best[r]) : "memory");
-              asm volatile("st.shared.u32 [%0], %1;" ::"r"(sums1_s + (uint32_t)(r * 64 + 32 + lane) * 4u), "r"(best_class[r]) : "memory");
+          for (int q = 0; q < kQBMaxTiles / 2; ++q)
+            if (const int r = 2 * q + half; r < R) {
+              asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums1_s + (uint32_t)(r * 64 + lane) * 4u), "f"(best[q]) : "memory");
+              asm volatile("st.shared.u32 [%0], %1;" ::"r"(sums1_s + (uint32_t)(r * 64 + 32 + lane) * 4u), "r"(best_class[q]) : "memory");
             }
           __syncwarp();
           if (lane == 0) mbar_arrive(sum_ready_s);
@@ -284,22 +290,23 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
           ok = wait(sum_ready_s, (uint32_t)it & 1u);
           if (!ok) break;
 #pragma unroll
-          for (int r = 0; r < kQBMaxTiles; ++r)
-            if (r < R) {
+          for (int q = 0; q < kQBMaxTiles / 2; ++q)
+            if (const int r = 2 * q + half; r < R) {
               const float b1 = lds_f32(sums1_s + (uint32_t)(r * 64 + lane) * 4u);
               const int c1 = (int)lds_u32(sums1_s + (uint32_t)(r * 64 + 32 + lane) * 4u);
-              if (b1 > best[r] || (b1 == best[r] && c1 > best_class[r])) best_class[r] = c1;
+              if (b1 > best[q] || (b1 == best[q] && c1 > best_class[q])) best_class[q] = c1;
             }
           __syncwarp();
           if (lane == 0) mbar_arrive(sum_free_s);
 #pragma unroll
-          for (int r = 0; r < kQBMaxTiles; ++r) {
+          for (int q = 0; q < kQBMaxTiles / 2; ++q) {
+            const int r = 2 * q + half;
             const long long row = row0 + r * 32;
             if (r < R && row < p.n_rows) {
               if (p.out_kind == 1)
-                reinterpret_cast<int8_t *>(p.out)[row] = (int8_t)best_class[r];
+                reinterpret_cast<int8_t *>(p.out)[row] = (int8_t)best_class[q];
               else
-                reinterpret_cast<float *>(p.out)[row] = (float)best_class[r];
+                reinterpret_cast<float *>(p.out)[row] = (float)best_class[q];
             }
           }
         }
@@ -309,26 +316,28 @@ __global__ void __launch_bounds__(kQBThreads, 1) tb_walk_quant_batch_kernel(cons
           if (it > 0) ok = wait(sum_free_s, (uint32_t)(it - 1) & 1u);
           if (!ok) break;
 #pragma unroll
-          for (int r = 0; r < kQBMaxTiles; ++r)
-            if (r < R) asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums1_s + (uint32_t)(r * 32 + lane) * 4u), "f"(sums[r]) : "memory");
+          for (int q = 0; q < kQBMaxTiles / 2; ++q)
+            if (const int r = 2 * q + half; r < R)
+              asm volatile("st.shared.f32 [%0], %1;" ::"r"(sums1_s + (uint32_t)(r * 32 + lane) * 4u), "f"(sums[q]) : "memory");
           __syncwarp();
           if (lane == 0) mbar_arrive(sum_ready_s);
         } else {
           ok = wait(sum_ready_s, (uint32_t)it & 1u);
           if (!ok) break;
 #pragma unroll
-          for (int r = 0; r < kQBMaxTiles; ++r)
-            if (r < R) sums[r] += lds_f32(sums1_s + (uint32_t)(r * 32 + lane) * 4u);
+          for (int q = 0; q < kQBMaxTiles / 2; ++q)
+            if (const int r = 2 * q + half; r < R) sums[q] += lds_f32(sums1_s + (uint32_t)(r * 32 + lane) * 4u);
           __syncwarp();
           if (lane == 0) mbar_arrive(sum_free_s);
 #pragma unroll
-          for (int r = 0; r < kQBMaxTiles; ++r) {
+          for (int q = 0; q < kQBMaxTiles / 2; ++q) {
+            const int r = 2 * q + half;
             const long long row = row0 + r * 32;
             if (r < R && row < p.n_rows) {
               if (p.write_partial)
-                p.partial[(long long)blockIdx.y * p.n_rows + row] = sums[r];
+                p.partial[(long long)blockIdx.y * p.n_rows + row] = sums[q];
               else
-                reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + sums[r], p.transform);
+                reinterpret_cast<float *>(p.out)[row] = apply_transform(p.initial_value + sums[q], p.transform);
             }
           }
         }
