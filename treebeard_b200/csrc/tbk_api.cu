@@ -181,7 +181,7 @@ int quant_batch_tiles(const tbk_forest *f, int num_features) {
 }
 
 // One prediction with a 15-bit-key kernel: rows whose key tiles fit shared memory several at a
-// time go to the batch kernel (persistent blocks of 20 warps over batches of up to 16 tiles),
+// time go to the batch kernel (persistent blocks of 22 warps over batches of up to 16 tiles),
 // wide rows to the kernel that holds one tile (persistent blocks of 24 warps over tiles of 32 rows).
 int run_quant(tbk_forest *f, Mode mode, const float *d_rows, int64_t n_rows, int64_t ld, void *d_out, int32_t out_kind,
               float *d_partial, int32_t *d_leaf_ids, cudaStream_t stream, int slot) {

@@ -4,7 +4,7 @@
 // of once per tile (walk_quant.cuh, the kernel for rows so wide that one key tile fills
 // shared memory, has to re-stream the forest for every 32 rows).
 //
-// A persistent block of 20 warps takes the batches blockIdx.x, blockIdx.x + gridDim.x, ...:
+// A persistent block of 22 warps takes the batches blockIdx.x, blockIdx.x + gridDim.x, ...:
 //  * 16 walkers in two sets of 8, as in walk_quant.cuh: set s takes the groups s, s+2, ... of
 //    the chunk; warp w of a set walks the four columns (lane + w + 8c) mod 32 of every group in
 //    lock-step, lane = row.  For a group the warp waits once for the two 16 KB pieces of the
