@@ -39,7 +39,7 @@ HBM_FALLBACK_GBS = 6650.0
 KERNEL_SOURCES = {"c3": ("walk_kernels.cuh", "walk_quant.cuh"),
                   "c2": ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh"),
                   "c4": ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh")}
-NCU_DRAM_BYTES_PER_ROW = {"c3": (8750.9, "a272d16cce04051e"), "c2": (131.8, "2ed7ffa4fd85a9ba"), "c4": (107.1, "2ed7ffa4fd85a9ba")}
+NCU_DRAM_BYTES_PER_ROW = {"c3": (8750.9, "a272d16cce04051e"), "c2": (131.6, "a37d85d1afd2a71f"), "c4": (106.9, "a37d85d1afd2a71f")}
 
 
 def kernel_source_hash(workload):
