@@ -161,6 +161,26 @@ def test_runner_api_on_golden_json(stem, rep, golden_dir):
     assert np.array_equal(on_dev, got)
 
 
+def test_runner_without_a_named_representation_gets_the_librarys_choice(golden_dir):
+    """No SetRepresentationType and the process-wide sparse switch untouched: "gpu_auto", which
+    lays this single-output forest out as keys; same predictions as the named layouts."""
+    from treebeard_b200 import kernels, treebeard
+    if treebeard.IsSparseRepresentationEnabled():
+        pytest.skip("the process-wide sparse switch is set")
+    z = np.load(os.path.join(golden_dir, "TestModel_Size2_13.npz"))
+    rows, expected = z["rows"], z["expected"]
+    options = treebeard.CompilerOptions(64, 1)
+    ctx = treebeard.TreebeardContext(os.path.join(golden_dir, "TestModel_Size2_13.json"), "", options)
+    ctx.SetInputFiletype("xgboost_json")
+    runner = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx)
+    got = runner.RunInference(np.ascontiguousarray(rows[:64]))
+    assert oracle.fp_equal(got, expected[:64]).all()
+    handle = runner.kernel_forest()
+    if handle:
+        df = kernels.DeviceForest.from_handle(handle, 0, 1, 0, rows.shape[1])
+        assert df.info().schedule.feature_bits in (16, 32)   # 16 unless an earlier test set the switch
+
+
 def test_runner_with_64_bit_types(golden_dir):
     """The reference's other tested type combination (f64 thresholds and values, i32 indices,
     src/test/GPUTests.cpp:682-840): host buffers hold doubles, the walk computes in fp32."""

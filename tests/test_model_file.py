@@ -39,7 +39,7 @@ def test_model_file_round_trip_on_host(tmp_path):
     entry, = g["TileSizeEntries"]
     assert entry == {"TileSize": 1, "ThresholdBitWidth": 32, "FeatureIndexBitWidth": 16}
     assert g["BatchSize"] == 64 and g["RowSize"] == forest.num_features
-    assert g["NumberOfTrees"] == forest.num_trees and g["Representation"] in ("gpu_array", "gpu_sparse")
+    assert g["NumberOfTrees"] == forest.num_trees and g["Representation"] in ("gpu_array", "gpu_sparse", "gpu_auto")
 
 
 def test_model_file_rejects_damage(tmp_path):
@@ -147,10 +147,11 @@ def test_runner_from_model_file_uses_the_packed_image(name, tmp_path):
     trees = {"c2": 52, "c3": 40, "c5": 12}[name]
     forest, X, out, glob = _write(tmp_path, name=name, trees=trees, batch=256)
     g = json.load(open(glob))
-    g["Representation"] = "gpu_auto"                      # wide rows / deep trees pick their key layouts
+    # ask for another representation than the file was written for (the process default:
+    # "gpu_auto" unless the sparse switch was touched): the forest is packed again
+    g["Representation"] = "gpu_sparse" if g["Representation"] == "gpu_auto" else "gpu_auto"
     json.dump(g, open(glob, "w"))
     want = oracle.predict(forest, X)
-    # written for the process default representation: the request differs, so the forest is packed again
     runner = treebeard.TreebeardInferenceRunner.FromSOFile(out, glob)
     assert not runner.used_packed_image()
     assert_predictions_close(runner.RunInference(X), want)

@@ -27,6 +27,7 @@ thread_local int32_t g_status = 0;
 thread_local std::string g_error;
 int32_t g_device = 0;
 bool g_use_sparse = false;  // process-wide default representation (src/mlir/Dialect.cpp:104-110)
+bool g_rep_flag_set = false; // ... once SetEnableSparseRepresentation has been called; until then the library chooses
 bool g_peeled_codegen = false;
 bool g_measure_kernel_time = false;
 int32_t g_kernel_runs = 1;
@@ -191,7 +192,9 @@ InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &o
     set_error(TBK_ERR_INVALID, "int8 return type needs a multiclass model");
     return nullptr;
   }
-  int rep = repName.empty() ? (g_use_sparse ? TBK_REP_SPARSE : TBK_REP_ARRAY) : rep_from_name(repName);
+  // no representation named and the sparse switch never touched: the library's own choice
+  // (every layout selects the same leaves; the reference's array default is a code-generation detail)
+  int rep = !repName.empty() ? rep_from_name(repName) : !g_rep_flag_set ? TBK_REP_AUTO : g_use_sparse ? TBK_REP_SPARSE : TBK_REP_ARRAY;
   if (rep < TBK_REP_AUTO) {
     set_error(TBK_ERR_INVALID, "unknown representation \"" + repName + "\"");
     return nullptr;
@@ -312,7 +315,7 @@ tb::ModelFileOptions to_file_options(const CompilerOptions &opt, const GPUAutoSc
   }
   // an unnamed representation is resolved now, so that the file does not depend on the
   // loading process's default
-  m.representation = repName.empty() ? (g_use_sparse ? "gpu_sparse" : "gpu_array") : repName;
+  m.representation = !repName.empty() ? repName : !g_rep_flag_set ? "gpu_auto" : g_use_sparse ? "gpu_sparse" : "gpu_array";
   return m;
 }
 
@@ -710,7 +713,10 @@ void TB_FreeForest(intptr_t forest) { delete reinterpret_cast<tb::Forest *>(fore
 
 // ---- process-wide switches ----
 
-void SetEnableSparseRepresentation(int32_t val) { g_use_sparse = val != 0; }
+void SetEnableSparseRepresentation(int32_t val) {
+  g_use_sparse = val != 0;
+  g_rep_flag_set = true;
+}
 int32_t IsSparseRepresentationEnabled(void) { return g_use_sparse; }
 void SetPeeledCodeGenForProbabilityBasedTiling(int32_t val) { g_peeled_codegen = val != 0; }
 int32_t IsPeeledCodeGenForProbabilityBasedTilingEnabled(void) { return g_peeled_codegen; }
