@@ -20,7 +20,7 @@ std::string pack_deep(const Forest &f, DeepForest *out) {
   q.initial_value = f.initial_value;
   q.num_trees = T;
   q.num_nodes = f.num_nodes();
-  err = quant_feature_ranges(f, kKey16Span, &q.lo, &q.scale);
+  err = quant_feature_ranges(f, kKey15Span, &q.lo, &q.scale);
   if (!err.empty()) return err;
 
   std::vector<int32_t> depth(T);
@@ -72,7 +72,7 @@ std::string pack_deep(const Forest &f, DeepForest *out) {
         }
         const int32_t ft = f.feat[a + it.node];
         const float thr = f.thr[a + it.node];
-        q.node_plane[base + it.heap] = ((uint32_t)ft << 16) | quant_key(thr, q.lo[ft], q.scale[ft]);
+            q.node_plane[base + it.heap] = ((uint32_t)ft << 16) | quant_key15(thr, q.lo[ft], q.scale[ft]);
         q.exact_plane[base + it.heap] = thr;
         stack.push_back({f.left[a + it.node], 2 * it.heap, it.level + 1});
         stack.push_back({f.right[a + it.node], 2 * it.heap + 1, it.level + 1});
@@ -89,8 +89,8 @@ void walk_deep_on_host(const DeepForest &q, const float *rows, int64_t n_rows, i
   std::vector<uint16_t> keys(F + 1);
   for (int64_t r = 0; r < n_rows; ++r) {
     const float *row = rows + r * ld;
-    for (int i = 0; i < F; ++i) keys[i] = quant_key(row[i], q.lo[i], q.scale[i]);
-    keys[F] = 65535;
+    for (int i = 0; i < F; ++i) keys[i] = quant_key15(row[i], q.lo[i], q.scale[i]);
+    keys[F] = (uint16_t)kKey15Max;
     float acc = 0.f;
     for (size_t g = 0; g < q.pairs.size(); ++g) {
       const QuantGroup &gm = q.pairs[g];

@@ -13,7 +13,7 @@
 //   leaf plane   f32 [2^D]  value of leaf j = i - 2^D after D steps
 //   exact plane  f32 [2^D]  fp32 thresholds, indexed like the node plane (global memory only)
 //
-// Rows are staged as the 16-bit order-preserving keys of quant_pack.h, so a block holds
+// Rows are staged as the 15-bit order-preserving keys of quant_pack.h, so a block holds
 // 32 x row_warps rows (512 for 128 features) next to a ring of whole-tree pieces; key ties
 // are resolved on the exact fp32 values, which keeps leaf selection that of the fp32 walk.
 // A leaf above the bottom level is a chain of pass-through nodes (sentinel feature, key 0:

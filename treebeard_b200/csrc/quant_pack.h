@@ -83,22 +83,10 @@ inline uint64_t quant_leaf_elem(const QuantGroup &g, uint64_t leaf, uint32_t col
   return g.elem_off + (uint64_t)col * g.slots + leaf;
 }
 
-// host restatement of the 16-bit key function of the deep-tree layout (deep_pack.h; the
-// device computes keys with the same arithmetic: one subtraction, one fused multiply-add,
-// one floor-and-saturate)
-inline uint16_t quant_key(float v, float lo, float scale) {
-  const float y = std::fmaf(v - lo, -scale, 65533.0f);
-  if (std::isnan(y)) return 0;
-  const float fl = std::floor(y);
-  if (fl <= 0.0f) return 0;
-  if (fl >= 65535.0f) return 65535;
-  return (uint16_t)fl;
-}
-
-// 15-bit keys of this layout (see the head of the file); same arithmetic on the device.
+// 15-bit keys of this layout and of the deep-tree layout (see the head of the file); same
+// arithmetic on the device.
 constexpr float kKey15Top = 31741.0f, kKey15Min = 1024.0f, kKey15Max = 31743.0f;
 constexpr float kKey15Span = 30715.0f; // keys between the smallest and the largest threshold
-constexpr float kKey16Span = 65531.0f;
 // A NEGATIVE scale marks a lattice feature (see quant_feature_ranges): every threshold is a
 // whole number and the slope |scale| is one too, so thresholds and whole-number row values
 // land EXACTLY on keys (value - lo, the product and the sum are exact in fp32).  A whole-number
@@ -128,8 +116,8 @@ inline uint32_t quant_feature_of_code(uint32_t code) { return (code >> 6) * 2u +
 
 // Per-feature key parameters (entries 0..num_features; the last belongs to the sentinel
 // feature): lo = smallest threshold of the feature, scale = span / (hi - lo), span being
-// the number of key steps between the smallest and the largest threshold (kKey15Span here,
-// kKey16Span in the deep-tree layout).  Fails on a non-finite threshold or leaf value.
+// the number of key steps between the smallest and the largest threshold (kKey15Span here
+// and in the deep-tree layout).  Fails on a non-finite threshold or leaf value.
 // lattice: features whose thresholds are all whole numbers no more than `span` apart get a
 // whole-number slope, stored NEGATED (see quant_key15): rows of integer-valued features, which
 // equal thresholds all the time, then never need the exact comparison.

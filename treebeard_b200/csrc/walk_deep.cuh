@@ -1,6 +1,6 @@
 // Walk kernel for the one-tree-per-stage layout (deep_pack.h): forests of deep trees.
 //
-// One block = RW warps = one tile of 32*RW rows, staged ONCE as 16-bit keys and kept for
+// One block = RW warps = one tile of 32*RW rows, staged ONCE as 15-bit keys and kept for
 // the whole forest.  Lane = row: every thread walks its own row through BOTH trees of a
 // pair in lock-step (two independent dependence chains per thread), so all threads of the
 // block read the same two node planes.  The node planes stream through a ring of whole-tree
@@ -54,35 +54,52 @@ struct DeepParams {
 
 constexpr int kDeepMaxSlots = 8;
 
-// Fast walk of DEPTH levels of two trees.  base0 / base1: shared-memory addresses of the
-// node planes; returns the heap indices reached (in [2^DEPTH, 2^(DEPTH+1))) and whether
-// any key comparison on either path tied.
+// Fast walk of DEPTH levels of two trees in lock-step, in PTX (the step of walk_quant.cuh: keys
+// are 15-bit integers that compare as fp16 numbers, so one half2 comparison of (key, node word)
+// picks the child and a second one accumulates the tie flag; the node's address itself is
+// tracked: the children of the node at address A = base + 4 i sit at 2A - base and 2A - base + 4).
+// base0 / base1: shared-memory addresses of the node planes; returns the heap indices reached
+// (in [2^DEPTH, 2^(DEPTH+1))) and whether any key comparison on either path tied.
+//   %0, %1  node addresses (updated)   %2, %3  node words (scratch)   %4  tie flags (out)
+//   %5  the thread's base in the key tile   %6  key-tile bytes per feature   %7, %8  -base
+#define TBD_DECL ".reg .b32 ka0, ka1, kx0, kx1;\n .reg .pred p0, p1, t0, t1, q;\n"
+#define TBD_LOAD "ld.shared.u32 %2, [%0];\n ld.shared.u32 %3, [%1];\n"
+#define TBD_KEY(i, n) "shr.u32 ka" #i ", " n ", 16;\n mad.lo.u32 ka" #i ", ka" #i ", %6, %5;\n ld.shared.u16 kx" #i ", [ka" #i "];\n"
+#define TBD_CMP0(i, n) "setp.lt.f16x2 p" #i "|q, kx" #i ", " n ";\n setp.eq.f16x2 t" #i "|q, kx" #i ", " n ";\n"
+#define TBD_CMP(i, n) "setp.lt.f16x2 p" #i "|q, kx" #i ", " n ";\n setp.eq.or.f16x2 t" #i "|q, kx" #i ", " n ", t" #i ";\n"
+#define TBD_ADV(i, a, c) "shl.b32 " a ", " a ", 1;\n add.u32 " a ", " a ", " c ";\n @p" #i " add.u32 " a ", " a ", 4;\n"
+#define TBD_KEYS TBD_KEY(0, "%2") TBD_KEY(1, "%3")
+#define TBD_ADVS TBD_ADV(0, "%0", "%7") TBD_ADV(1, "%1", "%8")
+#define TBD_FIRST TBD_KEYS TBD_CMP0(0, "%2") TBD_CMP0(1, "%3") TBD_ADVS
+#define TBD_NEXT TBD_LOAD TBD_KEYS TBD_CMP(0, "%2") TBD_CMP(1, "%3") TBD_ADVS
+#define TBD_TIES "selp.u32 %4, 1, 0, t0;\n @t1 or.b32 %4, %4, 2;\n"
+#define TBD_N2 TBD_NEXT TBD_NEXT
+#define TBD_N4 TBD_N2 TBD_N2
+#define TBD_N8 TBD_N4 TBD_N4
 template <int DEPTH>
 __device__ __forceinline__ void deep_walk(uint32_t base0, uint32_t base1, uint32_t key_lane, uint32_t ks,
                                           uint32_t *i0_out, uint32_t *i1_out, bool *tie0, bool *tie1) {
-  uint32_t i0 = 1, i1 = 1;
-  uint32_t n0 = lds_u32(base0 + 4), n1 = lds_u32(base1 + 4);
-  bool t0 = false, t1 = false;
-#pragma unroll
-  for (int d = 0; d < DEPTH; ++d) {
-    // one key load and one node load per tree and level (fetching both children ahead of
-    // the comparison measured slower: the load/store path is the scarcer resource)
-    const uint32_t kx0 = lds_u16(key_lane + (n0 >> 16) * ks);
-    const uint32_t kx1 = lds_u16(key_lane + (n1 >> 16) * ks);
-    const uint32_t kt0 = n0 & 0xffffu, kt1 = n1 & 0xffffu;
-    t0 |= kx0 == kt0;
-    t1 |= kx1 == kt1;
-    i0 = 2u * i0 + (kx0 < kt0 ? 1u : 0u);
-    i1 = 2u * i1 + (kx1 < kt1 ? 1u : 0u);
-    if (d + 1 < DEPTH) {
-      n0 = lds_u32(base0 + i0 * 4u);
-      n1 = lds_u32(base1 + i1 * 4u);
-    }
-  }
-  *i0_out = i0;
-  *i1_out = i1;
-  *tie0 = t0;
-  *tie1 = t1;
+  static_assert(DEPTH >= 2 && DEPTH <= 12, "two to twelve levels");
+  uint32_t a0 = base0 + 4u, a1 = base1 + 4u, tb; // the root is heap node 1
+  [[maybe_unused]] uint32_t n0, n1;
+#define TBD_OPERANDS : "+r"(a0), "+r"(a1), "=&r"(n0), "=&r"(n1), "=&r"(tb) : "r"(key_lane), "r"(ks), "r"(0u - base0), "r"(0u - base1)
+  // DEPTH levels = the first one and DEPTH - 1 more, each of which loads its node first
+  if constexpr (DEPTH == 2) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_NEXT TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 3) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N2 TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 4) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N2 TBD_NEXT TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 5) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N4 TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 6) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N4 TBD_NEXT TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 7) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N4 TBD_N2 TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 8) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N4 TBD_N2 TBD_NEXT TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 9) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N8 TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 10) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N8 TBD_NEXT TBD_TIES "}" TBD_OPERANDS);
+  else if constexpr (DEPTH == 11) asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N8 TBD_N2 TBD_TIES "}" TBD_OPERANDS);
+  else asm volatile("{\n" TBD_DECL TBD_LOAD TBD_FIRST TBD_N8 TBD_N2 TBD_NEXT TBD_TIES "}" TBD_OPERANDS);
+#undef TBD_OPERANDS
+  *i0_out = (a0 - base0) >> 2;
+  *i1_out = (a1 - base1) >> 2;
+  *tie0 = tb & 1u;
+  *tie1 = tb & 2u;
 }
 
 __device__ __forceinline__ void deep_walk_any(uint32_t depth, uint32_t base0, uint32_t base1, uint32_t key_lane,
@@ -186,16 +203,16 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
         const float4 x = live ? __ldg(reinterpret_cast<const float4 *>(rowp + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
         const float4 lo = __ldg(reinterpret_cast<const float4 *>(p.lo + f));
         const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + f));
-        sts_u16(key_lane + (uint32_t)f * ks, quant_key_dev(x.x, lo.x, sc.x));
-        sts_u16(key_lane + (uint32_t)(f + 1) * ks, quant_key_dev(x.y, lo.y, sc.y));
-        sts_u16(key_lane + (uint32_t)(f + 2) * ks, quant_key_dev(x.z, lo.z, sc.z));
-        sts_u16(key_lane + (uint32_t)(f + 3) * ks, quant_key_dev(x.w, lo.w, sc.w));
+        sts_u16(key_lane + (uint32_t)f * ks, quant_key15_dev(x.x, lo.x, sc.x));
+        sts_u16(key_lane + (uint32_t)(f + 1) * ks, quant_key15_dev(x.y, lo.y, sc.y));
+        sts_u16(key_lane + (uint32_t)(f + 2) * ks, quant_key15_dev(x.z, lo.z, sc.z));
+        sts_u16(key_lane + (uint32_t)(f + 3) * ks, quant_key15_dev(x.w, lo.w, sc.w));
       }
     } else {
       for (int f = 0; f < F; ++f)
-        sts_u16(key_lane + (uint32_t)f * ks, quant_key_dev(live ? __ldg(rowp + f) : 0.f, __ldg(p.lo + f), __ldg(p.scale + f)));
+        sts_u16(key_lane + (uint32_t)f * ks, quant_key15_dev(live ? __ldg(rowp + f) : 0.f, __ldg(p.lo + f), __ldg(p.scale + f)));
     }
-    sts_u16(key_lane + (uint32_t)F * ks, 65535u); // sentinel feature
+    sts_u16(key_lane + (uint32_t)F * ks, 0x7bffu); // sentinel feature: the largest key
   }
   // (each thread reads back only the keys it wrote: no barrier is needed for the tile)
 

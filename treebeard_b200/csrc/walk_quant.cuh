@@ -93,14 +93,8 @@ constexpr int kQRingBytes = 6 * 16384; // two walker sets x three 16 KB pieces
 constexpr int kQLeafTableBytes = 4096; // [2 sets][2 tables][32 columns][32 rows] leaf numbers
 constexpr uint32_t kQWaitTries = 1u << 20;
 
-// 16-bit keys of the deep-tree layout (walk_deep.cuh).
-__device__ __forceinline__ uint32_t quant_key_dev(float v, float lo, float sc) {
-  const float y = __fmaf_rn(__fsub_rn(v, lo), -sc, 65533.0f);
-  unsigned short h;
-  asm("cvt.rmi.u16.f32 %0, %1;" : "=h"(h) : "f"(y)); // floor, clamp to [0, 65535], NaN -> 0
-  return h;
-}
-// 15-bit keys of this layout: integers in [1024, 31743] (quant_pack.h); NaN -> 1024.
+// 15-bit keys of this layout and of the deep-tree layout (walk_deep.cuh): integers in
+// [1024, 31743] (quant_pack.h); NaN -> 1024.
 __device__ __forceinline__ uint32_t quant_key15_dev(float v, float lo, float sc) {
   float y = __fmaf_rn(__fsub_rn(v, lo), -sc, 31741.0f);
   y = fminf(fmaxf(y, 1024.0f), 31743.0f);
@@ -294,7 +288,7 @@ __device__ __noinline__ uint32_t quant_bottom_exact(uint32_t bot, uint32_t j, ui
 // Fills the key field of every split node from its exact threshold (run once at upload,
 // so that thresholds and row values are quantised by the very same device arithmetic).
 // wide = 1: the 15-bit keys and feature codes of the wide-row layout (quant_pack.h);
-// 0: the 16-bit keys and plain feature indices of the deep-tree layout (deep_pack.h).
+// 0: the same keys with plain feature indices, the deep-tree layout (deep_pack.h).
 __global__ void tb_quant_fill_keys(uint32_t *node_plane, const float *exact_plane, const float *lo,
                                    const float *scale, unsigned long long n, int num_features, int wide) {
   const unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -305,7 +299,7 @@ __global__ void tb_quant_fill_keys(uint32_t *node_plane, const float *exact_plan
     if (f < (uint32_t)num_features) node_plane[i] = (code << 16) | quant_threshold_key15_dev(exact_plane[i], lo[f], scale[f]);
   } else {
     const uint32_t f = node >> 16;
-    if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_key_dev(exact_plane[i], lo[f], scale[f]);
+    if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_key15_dev(exact_plane[i], lo[f], scale[f]);
   }
 }
 
