@@ -166,6 +166,11 @@ TREEBEARD_RUNTIME_EXPORT int32_t TB_GetLastStatus(void);
 TREEBEARD_RUNTIME_EXPORT const char *TB_GetLastError(void);
 /* CUDA device the next runner is built on (default 0). */
 TREEBEARD_RUNTIME_EXPORT void TB_SetDevice(int32_t device);
+/* Several devices for the next runner: it keeps a copy of the forest on each, cuts every HOST
+ * batch (RunInference / RunInferenceOnMultipleBatches) into one contiguous row range per device
+ * and predicts them concurrently; device-resident batches run on the first device. */
+TREEBEARD_RUNTIME_EXPORT void TB_SetDevices(const int32_t *devices, int32_t count);
+TREEBEARD_RUNTIME_EXPORT int32_t TB_RunnerDeviceCount(intptr_t inferenceRunner);
 /* The kernel-level forest handle (tbk_forest*, include/tbk.h) behind a runner, for
  * callers that hold device-resident inputs. */
 TREEBEARD_RUNTIME_EXPORT void *TB_GetKernelForest(intptr_t inferenceRunner);

@@ -181,6 +181,31 @@ def test_runner_without_a_named_representation_gets_the_librarys_choice(golden_d
         assert df.info().schedule.feature_bits in (16, 32)   # 16 unless an earlier test set the switch
 
 
+def test_runner_over_several_devices(tmp_path):
+    """One runner, a copy of the forest per device, host batches cut into one row range per
+    device and predicted concurrently (here the same device named twice, or two devices where
+    the box has them)."""
+    from treebeard_b200 import synth, treebeard
+    forest, X = small_config("c2", rows=17 * 256)
+    path = str(tmp_path / "c2.json")
+    synth.save_xgboost_json(forest, path)
+    want = oracle.predict(forest, X)
+    second = 1 if torch.cuda.device_count() > 1 else 0
+    treebeard.SetDevices([0, second])
+    try:
+        options = treebeard.CompilerOptions(256, 1)
+        ctx = treebeard.TreebeardContext(path, "", options)
+        ctx.SetRepresentationType("gpu_auto")
+        runner = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx)
+    finally:
+        treebeard.SetDevices([0])
+    assert runner.device_count() == 2
+    assert_predictions_close(runner.RunInferenceOnMultipleBatches(X), want)
+    assert_predictions_close(runner.RunInference(np.ascontiguousarray(X[:256])), want[:256])
+    single = treebeard.TreebeardInferenceRunner.GPUInferenceRunnerFromTBContext(ctx)
+    assert single.device_count() == 1
+
+
 def test_runner_with_64_bit_types(golden_dir):
     """The reference's other tested type combination (f64 thresholds and values, i32 indices,
     src/test/GPUTests.cpp:682-840): host buffers hold doubles, the walk computes in fp32."""

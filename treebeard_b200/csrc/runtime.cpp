@@ -16,6 +16,7 @@
 #include <cstring>
 #include <memory>
 #include <mutex>
+#include <thread>
 #include <set>
 #include <sstream>
 #include <string>
@@ -26,6 +27,7 @@ namespace {
 thread_local int32_t g_status = 0;
 thread_local std::string g_error;
 int32_t g_device = 0;
+std::vector<int32_t> g_more_devices; // further devices of the next runner (TB_SetDevices)
 bool g_use_sparse = false;  // process-wide default representation (src/mlir/Dialect.cpp:104-110)
 bool g_rep_flag_set = false; // ... once SetEnableSparseRepresentation has been called; until then the library chooses
 bool g_peeled_codegen = false;
@@ -126,6 +128,10 @@ struct InferenceRunner {
   bool returnFloat = true;
   int32_t numClasses = 0;
   int32_t device = 0;
+  // a runner over several devices: one more copy of the forest per further device; host batches
+  // are cut into one contiguous row range per device and predicted concurrently
+  std::vector<tbk_forest *> moreForests;
+  std::vector<int32_t> moreDevices;
   bool fromPackedImage = false; // built from the packed image of a compiled-model file
   int64_t kernelMicros = 0;
 };
@@ -276,6 +282,18 @@ InferenceRunner *build_runner(const tb::Forest &forest, const CompilerOptions &o
   r->device = g_device;
   r->fromPackedImage = from_image;
   if (g_measure_kernel_time) tbk_set_timing(kf, 1);
+  for (const int32_t dev : g_more_devices) {
+    tbk_forest *extra = nullptr;
+    if (tbk_forest_create(&fa, &sched, dev, opt.batchSize, &extra) != TBK_OK) {
+      set_error(TBK_ERR_CUDA, tbk_last_error());
+      for (tbk_forest *m : r->moreForests) tbk_forest_free(m);
+      tbk_forest_free(kf);
+      delete r;
+      return nullptr;
+    }
+    r->moreForests.push_back(extra);
+    r->moreDevices.push_back(dev);
+  }
   return r;
 }
 
@@ -446,6 +464,30 @@ void run_batch(InferenceRunner *r, void *inputs, void *results, int64_t rows) {
     cudaFree(d_in);
     cudaFree(d_out);
     if (rc == TBK_OK) rc = tbk_check_status(r->forest);
+  } else if (!r->moreForests.empty() && rows >= 64 * (int64_t)(1 + r->moreForests.size())) {
+    // one contiguous row range per device (multiples of 32 rows), predicted concurrently
+    const int64_t parts = 1 + (int64_t)r->moreForests.size();
+    const int64_t share = ((rows + parts - 1) / parts + 31) / 32 * 32;
+    const size_t out_elt = kind == TBK_OUT_I8 ? 1 : 4;
+    std::vector<int> codes((size_t)parts, TBK_OK);
+    std::vector<std::string> messages((size_t)parts);
+    std::vector<std::thread> workers;
+    for (int64_t k = 0; k < parts; ++k) {
+      const int64_t lo = std::min(rows, k * share), n = std::min(rows, lo + share) - lo;
+      if (n <= 0) continue;
+      tbk_forest *forest = k == 0 ? r->forest : r->moreForests[(size_t)k - 1];
+      workers.emplace_back([=, &codes, &messages] {
+        codes[(size_t)k] = tbk_predict_host(forest, static_cast<const float *>(inputs) + lo * r->rowSize, n, r->rowSize,
+                                            static_cast<unsigned char *>(results) + (size_t)lo * out_elt, kind);
+        if (codes[(size_t)k] != TBK_OK) messages[(size_t)k] = tbk_last_error(); // (the message is per thread)
+      });
+    }
+    for (std::thread &w : workers) w.join();
+    for (int64_t k = 0; k < parts; ++k)
+      if (codes[(size_t)k] != TBK_OK) {
+        set_error(codes[(size_t)k], messages[(size_t)k]);
+        return;
+      }
   } else {
     rc = tbk_predict_host(r->forest, static_cast<const float *>(inputs), rows, r->rowSize, results, kind);
   }
@@ -466,7 +508,19 @@ extern "C" {
 
 int32_t TB_GetLastStatus(void) { return g_status; }
 const char *TB_GetLastError(void) { return g_error.c_str(); }
-void TB_SetDevice(int32_t device) { g_device = device; }
+void TB_SetDevice(int32_t device) {
+  g_device = device;
+  g_more_devices.clear();
+}
+void TB_SetDevices(const int32_t *devices, int32_t count) {
+  if (!devices || count <= 0) return;
+  g_device = devices[0];
+  g_more_devices.assign(devices + 1, devices + count);
+}
+int32_t TB_RunnerDeviceCount(intptr_t runner) {
+  auto *r = reinterpret_cast<InferenceRunner *>(runner);
+  return r ? 1 + (int32_t)r->moreForests.size() : 0;
+}
 
 // ---- execution ----
 
@@ -528,6 +582,7 @@ void DeleteInferenceRunner(intptr_t runner) {
   auto *r = reinterpret_cast<InferenceRunner *>(runner);
   if (!r) return;
   tbk_forest_free(r->forest);
+  for (tbk_forest *m : r->moreForests) tbk_forest_free(m);
   delete r;
 }
 int32_t TB_RunnerUsedPackedImage(intptr_t runner) {

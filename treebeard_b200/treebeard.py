@@ -388,6 +388,10 @@ class TreebeardInferenceRunner:
                                                         results.ctypes.data, numRows)
         return results
 
+    def device_count(self) -> int:
+        """Devices this runner spreads host batches over (see SetDevices)."""
+        return int(_rt.TB_RunnerDeviceCount(self.inferenceRunner))
+
     def used_packed_image(self) -> bool:
         """True if this runner was built from the packed image cached in a compiled-model file."""
         return bool(_rt.TB_RunnerUsedPackedImage(self.inferenceRunner))
@@ -427,6 +431,15 @@ def GenerateLLVMIRForXGBoostModel(modelJSONPathStr, llvmIRPathStr, modelGlobalsJ
     _rt.GenerateLLVMIRForXGBoostModel(modelJSONPathStr.encode("ascii"), llvmIRPathStr.encode("ascii"),
                                       modelGlobalsJSONPathStr.encode("ascii"), options.optionsPtr)
     treebeardAPI.check()
+
+
+def SetDevices(devices):
+    """CUDA devices of the runners built from now on (no counterpart in the reference): one
+    device id, or several -- a runner then keeps the forest on each of them and splits every
+    host batch into one row range per device."""
+    devices = [int(d) for d in (devices if hasattr(devices, "__iter__") else [devices])]
+    arr = (ctypes.c_int32 * len(devices))(*devices)
+    _rt.TB_SetDevices(ctypes.addressof(arr), len(devices))
 
 
 def SetEnableSparseRepresentation(val):

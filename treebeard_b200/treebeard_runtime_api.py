@@ -80,6 +80,8 @@ _SIGNATURES = {
     "TB_GetLastStatus": ((), _I32),
     "TB_GetLastError": ((), _CP),
     "TB_SetDevice": ((_I32,), None),
+    "TB_SetDevices": ((_VP, _I32), None),
+    "TB_RunnerDeviceCount": ((_I64,), _I32),
     "TB_GetKernelForest": ((_I64,), _I64),
     "TB_CreateInferenceRunnerFromArrays": ((_VP, _I64, _I64, _CP), _I64),
     "TB_LoadForest": ((_CP, _CP, _I32), _I64),
