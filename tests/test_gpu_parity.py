@@ -580,6 +580,28 @@ def test_sixteen_bit_keys_refuse_what_they_do_not_cover():
     assert kernels.DeviceForest(wide, representation="auto").info().schedule.feature_bits == 32
 
 
+def test_batched_key_kernel_multiclass_on_continuous_features():
+    """Three classes over continuous features (ordinary keys, no lattice): an odd number of
+    classes (the two walker sets get two and one), rare ties resolved exactly."""
+    from treebeard_b200 import kernels, synth
+    marg = synth.Marginal("normal", 10)
+    forest = synth.generate_forest(77, 93, 6, 10, 0.1, 0.1, marg, num_classes=3)
+    rng = np.random.Generator(np.random.PCG64(5))
+    X = marg.sample_rows(rng, 40000)
+    split = np.nonzero(forest.left >= 0)[0]
+    for i in range(500):
+        g = split[(i * 37) % len(split)]
+        X[(i * 31) % len(X), forest.feat[g]] = forest.thr[g]
+    want, sums = oracle.predict(forest, X, class_sums=True)
+    _, want_ids = oracle.predict(forest, X, leaf_ids=True)
+    df = kernels.DeviceForest(forest, representation="auto", batch_hint=len(X))
+    assert df.info().schedule.feature_bits == 16
+    dX = _dev(X)
+    assert_predictions_close(df.predict(dX).cpu().numpy(), want, forest, sums)
+    assert np.array_equal(df.predict_leaf_ids(dX[:3000]).cpu().numpy(), want_ids[:3000])
+    assert df.info().reserved[0] > 0          # key ties were hit and resolved exactly
+
+
 @pytest.mark.parametrize("rows", [100003, 5000, 77])
 def test_batched_key_kernel_multiclass(rows):
     """Multiclass forests on the batch kernel: classes laid out group by group, one walker set
