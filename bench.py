@@ -39,7 +39,7 @@ HBM_FALLBACK_GBS = 6650.0
 KERNEL_SOURCES = {"c3": ("walk_kernels.cuh", "walk_quant.cuh"),
                   "c2": ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh"),
                   "c4": ("walk_kernels.cuh", "walk_quant.cuh", "walk_quant_batch.cuh")}
-NCU_DRAM_BYTES_PER_ROW = {"c3": (8745.4, "b733838d5a88eb21"), "c2": (131.6, "387bd5ef341ced22"), "c4": (106.9, "387bd5ef341ced22")}
+NCU_DRAM_BYTES_PER_ROW = {"c3": (8718.9, "9818290bfb5d6a18"), "c2": (131.6, "e10befea55613438"), "c4": (106.9, "e10befea55613438")}
 
 
 def kernel_source_hash(workload):

@@ -379,6 +379,30 @@ def test_batched_key_kernel_is_exact(name, rows, chunks):
     assert_predictions_close(again[ok[:rows - 13]], want[:rows - 13][ok[:rows - 13]])
 
 
+def test_deep_tree_kernel_with_whole_number_thresholds():
+    """Integer-valued features on deep trees: lattice features, exact without a tie on
+    whole-number rows; rows that are not whole numbers still select the oracle's leaves."""
+    import copy
+    from treebeard_b200 import kernels
+    forest, X = small_config("c5", rows=3000, trees=12)
+    rounded = copy.copy(forest)
+    rounded.thr = np.where(forest.left >= 0, np.round(forest.thr * 8), forest.thr).astype(np.float32)
+    Xr = np.round(X * 8).astype(np.float32)
+    df = kernels.DeviceForest(rounded, representation="auto", batch_hint=len(Xr))
+    assert df.info().schedule.feature_bits == 16
+    want, want_ids = oracle.predict(rounded, Xr, leaf_ids=True)
+    assert np.array_equal(df.predict_leaf_ids(_dev(Xr)).cpu().numpy(), want_ids)
+    assert_predictions_close(df.predict(_dev(Xr)).cpu().numpy(), want)
+    assert df.info().reserved[0] == 0
+    Y = Xr.copy()
+    split = np.nonzero(rounded.left >= 0)[0]
+    for i in range(3000):
+        g = split[(i * 53) % len(split)]
+        Y[i % len(Y), rounded.feat[g]] = rounded.thr[g] + ((-1) ** i) * [1e-5, 1e-2, 0.5][i % 3]
+    _, want_ids = oracle.predict(rounded, Y, leaf_ids=True)
+    assert np.array_equal(df.predict_leaf_ids(_dev(Y)).cpu().numpy(), want_ids)
+
+
 @pytest.mark.parametrize("trees,rows", [(1, 70), (24, 1500), (33, 20000)])
 def test_deep_tree_kernel_is_exact(trees, rows):
     """Deep trees (12 levels): whole trees staged through shared memory over a tile of

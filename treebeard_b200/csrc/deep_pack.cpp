@@ -20,7 +20,7 @@ std::string pack_deep(const Forest &f, DeepForest *out) {
   q.initial_value = f.initial_value;
   q.num_trees = T;
   q.num_nodes = f.num_nodes();
-  err = quant_feature_ranges(f, kKey15Span, &q.lo, &q.scale);
+  err = quant_feature_ranges(f, kKey15Span, &q.lo, &q.scale, /*lattice=*/true);
   if (!err.empty()) return err;
 
   std::vector<int32_t> depth(T);
@@ -72,7 +72,7 @@ std::string pack_deep(const Forest &f, DeepForest *out) {
         }
         const int32_t ft = f.feat[a + it.node];
         const float thr = f.thr[a + it.node];
-            q.node_plane[base + it.heap] = ((uint32_t)ft << 16) | quant_key15(thr, q.lo[ft], q.scale[ft]);
+            q.node_plane[base + it.heap] = ((uint32_t)ft << 16) | quant_threshold_key15(thr, q.lo[ft], q.scale[ft]);
         q.exact_plane[base + it.heap] = thr;
         stack.push_back({f.left[a + it.node], 2 * it.heap, it.level + 1});
         stack.push_back({f.right[a + it.node], 2 * it.heap + 1, it.level + 1});

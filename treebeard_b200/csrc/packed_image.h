@@ -30,7 +30,7 @@ struct PackedImage {
   DeepForest df;       // kDeep
 };
 
-constexpr uint32_t kPackedImageVersion = 5; // changes whenever a packer's output does
+constexpr uint32_t kPackedImageVersion = 6; // changes whenever a packer's output does
 
 void serialize_image(const PackedImage &im, std::vector<uint8_t> *out);
 uint64_t serialized_image_size(const PackedImage &im); // without serialising

@@ -95,8 +95,8 @@ constexpr float kKey15Span = 30715.0f; // keys between the smallest and the larg
 inline uint16_t quant_key15(float v, float lo, float scale) {
   if (scale < 0.f) {
     float y = std::fmaf(v - lo, scale, kKey15Top);
-    y = std::fmin(std::fmax(y, kKey15Min), kKey15Max - 1.0f);
-    return v == std::floor(v) ? (uint16_t)y : (uint16_t)(std::floor(y) + 1.0f);
+    y = std::fmin(std::fmax(y, kKey15Min), kKey15Max);
+    return v == std::floor(v) ? (uint16_t)y : (uint16_t)std::fmin(std::floor(y) + 1.0f, kKey15Max);
   }
   float y = std::fmaf(v - lo, -scale, kKey15Top);
   y = std::fmin(std::fmax(y, kKey15Min), kKey15Max); // fmax first: NaN becomes the smallest key

@@ -730,18 +730,22 @@ int tbk_image_create(const tbk_forest_arrays *fa, const tbk_schedule *schedule, 
     }
   }
   // ---- deep trees: whole-tree stages over a key tile (deep_pack.h); not chosen for forests
-  // whose thresholds are mostly whole numbers (integer-valued features tie on every equality)
+  // whose thresholds are mostly whole numbers on features that cannot be lattice features
+  // (integer-valued features then tie on every equality)
   bool deep_ok = !want_quant && host.num_classes == 0 && ts == 1 && bits != 32 &&
                  (bits == 16 || im.user.representation == TBK_REP_AUTO);
   if (deep_ok && bits == 0 && max_depth > tb::kQuantMaxDepth) {
-    int64_t splits = 0, whole = 0;
+    std::vector<float> lo, scale; // a negative scale marks a lattice feature
+    if (tb::quant_feature_ranges(host, tb::kKey15Span, &lo, &scale, true).empty()) {
+      int64_t splits = 0, whole = 0;
 #pragma omp parallel for reduction(+ : splits, whole) schedule(static) num_threads(tb::pack_threads())
-    for (int64_t g = 0; g < host.num_nodes(); ++g)
-      if (!host.is_leaf(g)) {
-        ++splits;
-        whole += host.thr[g] == std::floor(host.thr[g]) ? 1 : 0;
-      }
-    deep_ok = 2 * whole <= splits;
+      for (int64_t g = 0; g < host.num_nodes(); ++g)
+        if (!host.is_leaf(g)) {
+          ++splits;
+          whole += host.thr[g] == std::floor(host.thr[g]) && !(scale[host.feat[g]] < 0.f) ? 1 : 0;
+        }
+      deep_ok = 2 * whole <= splits;
+    }
   }
   if (deep_ok) {
     int rw = 0, slots = 0;

@@ -203,14 +203,14 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) tb_walk_deep_kernel(const Deep
         const float4 x = live ? __ldg(reinterpret_cast<const float4 *>(rowp + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
         const float4 lo = __ldg(reinterpret_cast<const float4 *>(p.lo + f));
         const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + f));
-        sts_u16(key_lane + (uint32_t)f * ks, quant_key15_dev(x.x, lo.x, sc.x));
-        sts_u16(key_lane + (uint32_t)(f + 1) * ks, quant_key15_dev(x.y, lo.y, sc.y));
-        sts_u16(key_lane + (uint32_t)(f + 2) * ks, quant_key15_dev(x.z, lo.z, sc.z));
-        sts_u16(key_lane + (uint32_t)(f + 3) * ks, quant_key15_dev(x.w, lo.w, sc.w));
+        sts_u16(key_lane + (uint32_t)f * ks, quant_key15_lattice_dev(x.x, lo.x, sc.x));
+        sts_u16(key_lane + (uint32_t)(f + 1) * ks, quant_key15_lattice_dev(x.y, lo.y, sc.y));
+        sts_u16(key_lane + (uint32_t)(f + 2) * ks, quant_key15_lattice_dev(x.z, lo.z, sc.z));
+        sts_u16(key_lane + (uint32_t)(f + 3) * ks, quant_key15_lattice_dev(x.w, lo.w, sc.w));
       }
     } else {
       for (int f = 0; f < F; ++f)
-        sts_u16(key_lane + (uint32_t)f * ks, quant_key15_dev(live ? __ldg(rowp + f) : 0.f, __ldg(p.lo + f), __ldg(p.scale + f)));
+        sts_u16(key_lane + (uint32_t)f * ks, quant_key15_lattice_dev(live ? __ldg(rowp + f) : 0.f, __ldg(p.lo + f), __ldg(p.scale + f)));
     }
     sts_u16(key_lane + (uint32_t)F * ks, 0x7bffu); // sentinel feature: the largest key
   }

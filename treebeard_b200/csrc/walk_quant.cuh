@@ -109,9 +109,8 @@ __device__ __forceinline__ uint32_t quant_key15_dev(float v, float lo, float sc)
 __device__ __forceinline__ uint32_t quant_key15_lattice_dev(float v, float lo, float sc) {
   if (sc < 0.f) {
     float y = __fmaf_rn(__fsub_rn(v, lo), sc, 31741.0f);
-    y = fminf(fmaxf(y, 1024.0f), 31742.0f);
-    const float fl = floorf(y);
-    return (uint32_t)(v == floorf(v) ? y : fl + 1.0f);
+    y = fminf(fmaxf(y, 1024.0f), 31743.0f);
+    return (uint32_t)(v == floorf(v) ? y : fminf(floorf(y) + 1.0f, 31743.0f));
   }
   return quant_key15_dev(v, lo, sc);
 }
@@ -299,7 +298,7 @@ __global__ void tb_quant_fill_keys(uint32_t *node_plane, const float *exact_plan
     if (f < (uint32_t)num_features) node_plane[i] = (code << 16) | quant_threshold_key15_dev(exact_plane[i], lo[f], scale[f]);
   } else {
     const uint32_t f = node >> 16;
-    if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_key15_dev(exact_plane[i], lo[f], scale[f]);
+    if (f < (uint32_t)num_features) node_plane[i] = (f << 16) | quant_threshold_key15_dev(exact_plane[i], lo[f], scale[f]);
   }
 }
 
